@@ -1,0 +1,428 @@
+// bf16 GEMM for sm_100a: C[M,N] = alpha * A[M,K] * B[N,K]^T with fp32 accumulation.
+//
+// Structure (one persistent CTA per SM, 192 threads):
+//   warp 0      TMA producer: fills a 4-stage ring of {A 128x64, B 256x64} bf16
+//               tiles in 128B-swizzled shared memory (non-multicast loads only).
+//   warp 1      MMA issuer: one thread issues tcgen05.mma 128x256x16 into one of
+//               two 256-column TMEM accumulators and commits to mbarriers.
+//   warps 2..5  epilogue: tcgen05.ld the finished accumulator (each warp owns a
+//               32-lane quarter) and apply the fused epilogue while the next tile's
+//               main loop already runs on the other accumulator.
+//
+// Either operand may be stored K-major ([rows][K]) or MN-major ([K][rows]); the
+// three GEMMs of a linear layer map onto it without a transpose:
+//   forward  Y = X W^T      A = X  (K-major)   B = W  (K-major)
+//   dgrad    dX = dY W      A = dY (K-major)   B = W  (MN-major, contraction over W's rows)
+//   wgrad    dW = dY^T X    A = dY (MN-major)  B = X  (MN-major), fp32 accumulate epilogue
+//
+// Every wait is bounded (common.cuh); on timeout the roles fall through to the
+// common exit, TMEM is released and the status block tells the host what happened.
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "tpb.h"
+
+namespace tpb {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2;                 // 16 KB
+constexpr int B_BYTES = BN * BK * 2;                 // 32 KB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 48 KB
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int GEMM_THREADS = 192;
+
+struct GemmParams {
+  int M, N, K;
+  void* C;
+  long long ldc;
+  const void* aux;   // residual (EPI_BF16_RES)
+  long long ldaux;
+  void* c2;          // pre-activation output (EPI_SWIGLU, optional)
+  long long ldc2;
+  int b_split;       // EPI_SWIGLU: row of B where the "up" half starts (= F)
+  float alpha;
+  int epi;
+  int group_m;       // rasterisation: m-tiles per group
+  int* status;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& tm,
+                                            int& tn) {
+  int per_group = group_m * n_tiles;
+  int g = t / per_group;
+  int first_m = g * group_m;
+  int gsize = min(group_m, m_tiles - first_m);
+  int within = t - g * per_group;
+  tm = first_m + within % gsize;
+  tn = within / gsize;
+}
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool swiglu = p.epi == TPB_EPI_SWIGLU;
+  const int tile_n_out = swiglu ? BN / 2 : BN;  // output columns covered by one tile
+  const int n_logical = swiglu ? p.N / 2 : p.N;
+  const int m_tiles = (p.M + BM - 1) / BM;
+  const int n_tiles = (n_logical + tile_n_out - 1) / tile_n_out;
+  const int num_tiles = m_tiles * n_tiles;
+  const int num_kb = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int tm, tn;
+        tile_coords(t, m_tiles, n_tiles, p.group_m, tm, tn);
+        const int m0 = tm * BM, n0 = tn * tile_n_out;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, p.status, kTimeoutStageFree, 1)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sB = sA + A_BYTES;
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sA, &tmA, &full[stage], k0, m0);  // box {64 k, 128 rows}
+          } else {
+#pragma unroll
+            for (int c = 0; c < BM / 64; ++c)  // box {64 m, 64 k}
+              tma_load_2d(sA + c * 8192, &tmA, &full[stage], m0 + c * 64, k0);
+          }
+          if (!B_MN) {
+            // two boxes {64 k, 128 rows}; for SwiGLU the second one comes from the "up" half
+            int r1 = swiglu ? p.b_split + n0 : n0 + 128;
+            tma_load_2d(sB, &tmB, &full[stage], k0, n0);
+            tma_load_2d(sB + 16384, &tmB, &full[stage], k0, r1);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c) {
+              int col = swiglu ? (c < 2 ? n0 + c * 64 : p.b_split + n0 + (c - 2) * 64) : n0 + c * 64;
+              tma_load_2d(sB + c * 8192, &tmB, &full[stage], col, k0);
+            }
+          }
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int local = 0;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.status, kTimeoutAccFree, 2)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, p.status, kTimeoutTmaFull, 3)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sB = sA + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc(sA + k * 2048, 8192, 1024)
+                                        : make_smem_desc(sA + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc(sB + k * 2048, 8192, 1024)
+                                        : make_smem_desc(sB + k * 32, 16, 1024);
+            mma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+          }
+          tc_commit(&empty[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) tc_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quarter this warp may access
+    int local = 0;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase, p.status, kTimeoutAccFull, 4)) break;
+      tc_fence_after();
+      int tm, tn;
+      tile_coords(t, m_tiles, n_tiles, p.group_m, tm, tn);
+      const int row = tm * BM + q * 32 + lane;
+      const int n0 = tn * tile_n_out;
+      const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
+      const bool row_ok = row < p.M;
+
+      if (swiglu) {
+        __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc;
+        __nv_bfloat16* C2 =
+            p.c2 ? reinterpret_cast<__nv_bfloat16*>(p.c2) + (long long)row * p.ldc2 : nullptr;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t g[32], u[32];
+          tmem_ld32(t_addr + c * 32, g);
+          tmem_ld32(t_addr + 128 + c * 32, u);
+          tmem_wait_ld();
+          const int col = n0 + c * 32;
+          if (row_ok && col < n_logical) {
+            uint32_t o[16], pg[16], pu[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float g0 = __uint_as_float(g[2 * j]) * p.alpha, g1 = __uint_as_float(g[2 * j + 1]) * p.alpha;
+              float u0 = __uint_as_float(u[2 * j]) * p.alpha, u1 = __uint_as_float(u[2 * j + 1]) * p.alpha;
+              o[j] = pack_bf16(silu_f(g0) * u0, silu_f(g1) * u1);
+              pg[j] = pack_bf16(g0, g1);
+              pu[j] = pack_bf16(u0, u1);
+            }
+            if (col + 32 <= n_logical) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                *reinterpret_cast<uint4*>(C + col + v * 8) =
+                    make_uint4(o[4 * v], o[4 * v + 1], o[4 * v + 2], o[4 * v + 3]);
+                if (C2) {
+                  *reinterpret_cast<uint4*>(C2 + col + v * 8) =
+                      make_uint4(pg[4 * v], pg[4 * v + 1], pg[4 * v + 2], pg[4 * v + 3]);
+                  *reinterpret_cast<uint4*>(C2 + p.b_split + col + v * 8) =
+                      make_uint4(pu[4 * v], pu[4 * v + 1], pu[4 * v + 2], pu[4 * v + 3]);
+                }
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < n_logical; ++j) {
+                float2 ov = unpack_bf16(o[j >> 1]), gv = unpack_bf16(pg[j >> 1]), uv = unpack_bf16(pu[j >> 1]);
+                C[col + j] = __float2bfloat16((j & 1) ? ov.y : ov.x);
+                if (C2) {
+                  C2[col + j] = __float2bfloat16((j & 1) ? gv.y : gv.x);
+                  C2[p.b_split + col + j] = __float2bfloat16((j & 1) ? uv.y : uv.x);
+                }
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(t_addr + c * 32, r);
+          tmem_wait_ld();
+          const int col = n0 + c * 32;
+          if (!row_ok || col >= p.N) continue;
+          const bool full_chunk = col + 32 <= p.N;
+          if (p.epi == TPB_EPI_F32 || p.epi == TPB_EPI_F32_ACC) {
+            float* C = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+            const bool accm = p.epi == TPB_EPI_F32_ACC;
+            if (full_chunk) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 o = make_float4(__uint_as_float(r[4 * v]) * p.alpha, __uint_as_float(r[4 * v + 1]) * p.alpha,
+                                       __uint_as_float(r[4 * v + 2]) * p.alpha, __uint_as_float(r[4 * v + 3]) * p.alpha);
+                if (accm) {
+                  float4 old = *reinterpret_cast<float4*>(C + 4 * v);
+                  o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *reinterpret_cast<float4*>(C + 4 * v) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < p.N; ++j) {
+                float o = __uint_as_float(r[j]) * p.alpha;
+                C[j] = accm ? C[j] + o : o;
+              }
+            }
+          } else {
+            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+            const __nv_bfloat16* R = nullptr;
+            if (p.epi == TPB_EPI_BF16_ACC) R = C;
+            if (p.epi == TPB_EPI_BF16_RES)
+              R = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + col;
+            if (full_chunk) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[8 * v + j]) * p.alpha;
+                if (R) {
+                  uint4 old = *reinterpret_cast<const uint4*>(R + 8 * v);
+                  float2 a = unpack_bf16(old.x), b = unpack_bf16(old.y), cc = unpack_bf16(old.z), d = unpack_bf16(old.w);
+                  f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+                  f[4] += cc.x; f[5] += cc.y; f[6] += d.x; f[7] += d.y;
+                }
+                *reinterpret_cast<uint4*>(C + 8 * v) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]),
+                                                                  pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+              }
+            } else {
+              for (int j = 0; j < 32 && col + j < p.N; ++j) {
+                float o = __uint_as_float(r[j]) * p.alpha;
+                if (R) o += __bfloat162float(R[j]);
+                C[j] = __float2bfloat16(o);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Host side
+// ----------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map: dims {inner, outer}, row pitch in elements, box {box_inner, box_outer}.
+int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t pitch_elems,
+                 uint32_t box_inner, uint32_t box_outer, int elem_bytes) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return -1;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {pitch_elems * elem_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+int sm_count();  // runtime.cu
+
+template <bool A_MN, bool B_MN>
+cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
+                        cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  gemm_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
+  return cudaGetLastError();
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+
+extern "C" int tpb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                             long long ldb, long long ldc, int a_mn, int b_mn, int epi, float alpha,
+                             const void* aux, long long ldaux, void* c2, long long ldc2, int max_ctas,
+                             void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const bool swiglu = epi == TPB_EPI_SWIGLU;
+  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16) ||
+      (reinterpret_cast<uintptr_t>(C) % 16))
+    return -2;
+  const bool f32out = epi == TPB_EPI_F32 || epi == TPB_EPI_F32_ACC;
+  if (ldc % (f32out ? 4 : 8)) return -2;
+  if (swiglu && ((N % 2) || ((N / 2) % 8))) return -2;
+  CUtensorMap ta, tb;
+  int r;
+  if (!a_mn) r = make_tmap_2d(&ta, A, K, M, lda, 64, 128, 2);
+  else       r = make_tmap_2d(&ta, A, M, K, lda, 64, 64, 2);
+  if (r) return r < 0 ? -3 : -4;
+  if (!b_mn) r = make_tmap_2d(&tb, B, K, N, ldb, 64, 128, 2);
+  else       r = make_tmap_2d(&tb, B, N, K, ldb, 64, 64, 2);
+  if (r) return r < 0 ? -3 : -5;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.aux = aux; p.ldaux = ldaux;
+  p.c2 = c2; p.ldc2 = ldc2;
+  p.b_split = N / 2;
+  p.alpha = alpha;
+  p.epi = epi;
+  p.status = status_block();
+  const int n_logical = swiglu ? N / 2 : N;
+  const int tile_n = swiglu ? BN / 2 : BN;
+  const int m_tiles = (M + BM - 1) / BM, n_tiles = (n_logical + tile_n - 1) / tile_n;
+  p.group_m = m_tiles < 16 ? m_tiles : 16;
+  int grid = m_tiles * n_tiles;
+  int cap = sm_count();
+  if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
+  if (grid > cap) grid = cap;
+  cudaError_t e;
+  if (!a_mn && !b_mn)      e = launch_gemm<false, false>(ta, tb, p, grid, stream);
+  else if (!a_mn && b_mn)  e = launch_gemm<false, true>(ta, tb, p, grid, stream);
+  else if (a_mn && !b_mn)  e = launch_gemm<true, false>(ta, tb, p, grid, stream);
+  else                     e = launch_gemm<true, true>(ta, tb, p, grid, stream);
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}

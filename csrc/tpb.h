@@ -1,0 +1,79 @@
+// C ABI of libtpb200.so: hand-written sm_100a kernels for the training hot path.
+// All pointers are device pointers unless stated otherwise; `stream` is a
+// cudaStream_t passed as void*.  Functions return 0 on success, a negative value
+// for rejected arguments and 1000 + cudaError_t for launch failures.
+#pragma once
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// GEMM epilogues (tpb_gemm_bf16 `epi`).
+enum {
+  TPB_EPI_BF16 = 0,      // C(bf16) = alpha * acc
+  TPB_EPI_F32 = 1,       // C(f32)  = alpha * acc
+  TPB_EPI_F32_ACC = 2,   // C(f32) += alpha * acc
+  TPB_EPI_BF16_ACC = 3,  // C(bf16) = C + alpha * acc
+  TPB_EPI_BF16_RES = 4,  // C(bf16) = aux + alpha * acc   (residual add)
+  TPB_EPI_SWIGLU = 5,    // B = [gate; up] rows, C[M, N/2] = silu(g) * u, optional c2[M, N] = [g | u]
+};
+
+// Status block: {code, site, block, thread}; code 0 = no kernel ever timed out.
+int tpb_status(int* out4);
+void tpb_status_clear(void);
+int tpb_sm_count(void);
+
+// C[M,N] = alpha * A[M,K] * B[N,K]^T.  a_mn / b_mn = 1 when that operand is stored
+// with its M/N index contiguous ([K][M] resp. [K][N]) instead of K contiguous.
+int tpb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                  long long ldb, long long ldc, int a_mn, int b_mn, int epi, float alpha,
+                  const void* aux, long long ldaux, void* c2, long long ldc2, int max_ctas,
+                  void* stream);
+
+// y = rmsnorm(x [+ res]) * w.  h_out (optional) receives x + res.  rstd: [rows] fp32.
+int tpb_rmsnorm_fwd(const void* x, const void* res, const void* w, void* y, void* h_out, float* rstd,
+                    int rows, int dim, float eps, void* stream);
+// dx = d/dx of the above (+ dres if given).  dw_f32 [dim] is accumulated with atomics.
+int tpb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                    void* dx, float* dw_f32, int rows, int dim, void* stream);
+
+// In-place rotate-half RoPE on `heads` heads of width `dim` starting at column
+// `col0` of a [tokens, ld] bf16 matrix.  cos/sin: fp32 [max_pos, dim/2].
+// pos: optional int32 [tokens] positions (else token % seq_len).  inverse=1 applies R^T.
+int tpb_rope(void* x, long long ld, int col0, int heads, int dim, const float* cos, const float* sin,
+             const int* pos, int tokens, int seq_len, int inverse, int interleaved, void* stream);
+
+// act[T,F] = silu(gu[:, :F]) * gu[:, F:]
+int tpb_swiglu_fwd(const void* gu, void* act, int rows, int f, void* stream);
+// dgu[T,2F] from dact[T,F] and gu
+int tpb_swiglu_bwd(const void* dact, const void* gu, void* dgu, int rows, int f, void* stream);
+
+// Row-wise softmax cross entropy on bf16 logits [rows, vocab] (row pitch ld).
+// loss_sum += sum_i loss_i (fp32 atomics), logits are overwritten with
+// (softmax - onehot) * *grad_scale; rows with target < 0 produce zeros.
+int tpb_ce_fwd_bwd(void* logits, long long ld, const long long* targets, float* loss_sum,
+                   const float* grad_scale, int rows, int vocab, void* stream);
+
+// Fused AdamW over flat fp32 state; grads bf16 (grad_is_bf16=1) or fp32.
+// clip_coef: optional device scalar multiplied into the gradient.
+int tpb_adamw(float* p32, float* m, float* v, const void* grad, void* p16, long long n, float lr,
+              float beta1, float beta2, float eps, float wd, float bc1, float bc2, const float* clip_coef,
+              int grad_is_bf16, void* stream);
+// *out += sum(g^2)   (out: fp32 device scalar)
+int tpb_sumsq(const void* g, long long n, int is_bf16, float* out, void* stream);
+// coef = min(1, max_norm / (sqrt(*sumsq) + 1e-6)); norm_out = sqrt(*sumsq)
+int tpb_clip_coef(const float* sumsq, float max_norm, float* coef, float* norm_out, void* stream);
+
+// out[t,:] = table[ids[t],:]
+int tpb_embedding_fwd(const void* table, const long long* ids, void* out, int tokens, int dim,
+                      long long vocab, long long row0, void* stream);
+// dtable[ids[t]-row0,:] += dout[t,:] for rows owned by this shard
+int tpb_embedding_bwd(const void* dout, const long long* ids, void* dtable, int tokens, int dim,
+                      long long rows_local, long long row0, int dtable_is_f32, void* stream);
+
+// bf16 <- fp32 with scale, and fp32 accumulate into bf16 destinations
+int tpb_cast_f32_to_bf16(const float* src, void* dst, long long n, float scale, int accumulate, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
