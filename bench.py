@@ -1,0 +1,251 @@
+"""Headline benchmark: Llama-3-8B FSDP training throughput (tokens/s, MFU) on N B200s.
+
+  python bench.py --gpus 1 --steps 10 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+      --master-port 29500 bench.py --gpus 8 --steps 10 --warmup 3
+
+Config: Llama-3-8B (32 layers, hidden 4096, 32/8 heads, FFN 14336, vocab 128256), sequence
+8192, one sequence per GPU (global batch = N, weak scaling), bf16 compute, fused AdamW with
+fp32 master weights and moments, per-layer rematerialisation, random-init weights and
+uniform-random token ids.  Two timed regions of exactly K steps each, both bracketed by a
+barrier + device synchronisation and timed with CUDA events (max over ranks):
+
+  value  device-resident inputs, no host read-back inside the region;
+  e2e    the public ``Trainer`` loop body: every step copies its batch from pinned host
+         memory to the device and reads the loss back to the host.
+
+``--impl reference`` reports why the unmodified reference cannot run here;
+``--impl baseline`` runs this framework's cuBLAS + SDPA + torch-eager mode (no hand-written
+kernels) as the same-box comparator.  Rank 0 prints one JSON line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+# Published reference throughput used for vs_baseline: Llama 3.0 8B, seq 8192 on TPU
+# v6e-256 = 6.91 k tokens/s per chip (torchprime/torch_xla_models/results.csv:2).
+REF_TOKENS_PER_SEC_PER_CHIP = 1024 * 8192 / 4.741 / 256
+
+
+def _reference_arm(args):
+  why = ("reference installs offline only with --no-deps and cannot run: its trainer imports torch_xla/hydra "
+         "(TPU SPMD runtime, torch_xla nightly + libtpu) which are not in this image; it has no CUDA code path")
+  print(json.dumps({"impl": "reference", "unavailable": why}))
+  return 0
+
+
+class ClockSampler:
+  """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+  FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+            "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+  def __init__(self, gpu_index: int):
+    self.gpu_index = gpu_index
+    self.proc = None
+    self.path = None
+
+  def start(self):
+    try:
+      fd, self.path = tempfile.mkstemp(suffix=".csv")
+      os.close(fd)
+      self.proc = subprocess.Popen(
+        ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+         "-i", str(self.gpu_index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+    except OSError:
+      self.proc = None
+
+  def stop(self) -> dict:
+    if self.proc is None:
+      return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=5)
+    except subprocess.TimeoutExpired:
+      self.proc.kill()
+    sm, mx, reasons = [], [], set()
+    names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+    try:
+      for line in open(self.path):
+        parts = [p.strip() for p in line.split(",")]
+        if len(parts) < 9:
+          continue
+        try:
+          sm.append(float(parts[1]))
+          mx.append(float(parts[2]))
+        except ValueError:
+          continue
+        for name, val in zip(names, parts[5:9]):
+          if val.lower().startswith("active"):
+            reasons.add(name)
+    finally:
+      try:
+        os.remove(self.path)
+      except OSError:
+        pass
+    return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+            "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=8)
+  ap.add_argument("--warmup", type=int, default=3)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference", "baseline"])
+  ap.add_argument("--model", default="llama-3-8b")
+  ap.add_argument("--seq-len", type=int, default=8192)
+  ap.add_argument("--per-gpu-batch", type=int, default=1)
+  ap.add_argument("--override", action="append", default=[], help="extra config overrides (key=value)")
+  args = ap.parse_args()
+  if args.impl == "reference":
+    return _reference_arm(args)
+
+  import torch
+  import torch.distributed as dist
+  from torchprime_b200.config import compose, to_container
+  from torchprime_b200.data.loader import ShardedBatchLoader
+  from torchprime_b200.data.synthetic import make_synthetic_dataset
+  from torchprime_b200.dist import runtime as rt
+  from torchprime_b200.metrics.mfu import compute_mfu, measured_peak_tflops
+  from torchprime_b200.models.model_utils import initialize_model_class
+  from torchprime_b200.ops import _lib, kernels
+  from torchprime_b200.trainer import Trainer
+
+  n = args.gpus
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  if world != n:
+    if world == 1 and n > 1:
+      # convenience: re-launch under torchrun when called as plain `python bench.py --gpus N`
+      cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+             "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29517"),
+             os.path.abspath(__file__)] + sys.argv[1:]
+      return subprocess.call(cmd)
+    raise SystemExit(f"--gpus {n} but WORLD_SIZE={world}")
+  if args.warmup < 3:
+    args.warmup = 3
+
+  device = rt.init()
+  global_batch = args.per_gpu_batch * n
+  overrides = [
+    f"model={args.model}", "dataset=synthetic", f"dataset.block_size={args.seq_len}",
+    f"task.global_batch_size={global_batch}", f"task.max_steps={args.steps * 2 + args.warmup + 8}",
+    "task.optimizer.type=adamw", "task.max_grad_norm=1.0", f"ici_mesh.fsdp={n}", "profile_start_step=-1",
+    "logging_steps=1000000", f"output_dir={tempfile.mkdtemp(prefix='tpb_bench_')}",
+    f"dataset.num_samples={max(64, global_batch * 8)}",
+  ]
+  if args.impl == "baseline":
+    overrides.append("engine.kernels=torch")
+  overrides += args.override
+  config = compose("default", overrides)
+
+  torch.manual_seed(int(config.seed))
+  model = initialize_model_class(config.model, device="meta")
+  data = make_synthetic_dataset(vocab_size=config.model.vocab_size, block_size=args.seq_len,
+                                num_samples=int(config.dataset.num_samples), seed=int(config.seed))
+  trainer = Trainer(model=model, config=config, train_dataset=data)
+  trainer.model.train()
+  loader = trainer._get_train_dataloader()
+
+  def sync():
+    rt.barrier()
+    torch.cuda.synchronize()
+
+  # ---------------- warm-up (untimed) ----------------
+  last = None
+  for _ in range(args.warmup):
+    last = trainer._prepare_batch(loader.next_batch())
+    loss, _ = trainer.train_step(last)
+  sync()
+  fixed = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in last.items()}
+
+  # ---------------- region 1: device-resident inputs ----------------
+  sampler = ClockSampler(torch.cuda.current_device())
+  if rt.is_main():
+    sampler.start()
+  launches0 = kernels.launch_count()
+  sync()
+  t_wall0 = time.perf_counter()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(args.steps):
+    loss, gnorm = trainer.train_step(fixed)
+  e1.record()
+  sync()
+  t_wall1 = time.perf_counter()
+  launches = kernels.launch_count() - launches0
+  dev_ms = rt.all_reduce_max_float(e0.elapsed_time(e1)) / args.steps
+
+  # ---------------- region 2: end to end through the public API ----------------
+  h2d = d2h = 0
+  sync()
+  f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  f0.record()
+  loss_host = 0.0
+  for _ in range(args.steps):
+    batch = trainer._prepare_batch(loader.next_batch())   # pinned host -> device copy of this step's inputs
+    h2d = loader.h2d_bytes_last
+    loss, gnorm = trainer.train_step(batch)
+    loss_host = float(loss.item())                        # device -> host read of the step's result
+    d2h = loss.element_size() * loss.numel()
+  f1.record()
+  sync()
+  e2e_ms = rt.all_reduce_max_float(f0.elapsed_time(f1)) / args.steps
+  clocks = sampler.stop() if rt.is_main() else None
+  _lib.raise_on_device_timeout() if _lib.available() else None
+
+  tokens = global_batch * args.seq_len
+  value = tokens / (dev_ms / 1e3)
+  e2e_value = tokens / (e2e_ms / 1e3)
+  if rt.is_main():
+    mcfg = to_container(config.model)
+    mfu = compute_mfu(mcfg, global_batch, args.seq_len, dev_ms / 1e3, f"b200-{n}")
+    peaks = measured_peak_tflops() or {}
+    sustained = peaks.get("bf16_tflops_sustained")
+    out = {
+      "metric": "Llama-3-8B FSDP train tokens/sec (max over ranks)" if args.model == "llama-3-8b"
+                else f"{args.model} train tokens/sec (max over ranks)",
+      "value": round(value, 2), "unit": "tokens/s", "n_gpus": n, "steps": args.steps, "warmup": args.warmup,
+      "ms_per_step": round(dev_ms, 3), "higher_is_better": True, "scaling": "weak",
+      "vs_baseline": round(value / (REF_TOKENS_PER_SEC_PER_CHIP * n), 4), "dtype": "bf16", "data": "synthetic",
+      "impl": args.impl,
+      "mfu_of_spec_peak": round(mfu.mfu, 4),
+      "mfu_of_measured_sustained_cublas": round(mfu.per_chip_tflops_per_sec / sustained, 4) if sustained else None,
+      "model_tflops_per_gpu_per_s": round(mfu.per_chip_tflops_per_sec, 1),
+      "final_loss": round(loss_host, 4),
+      "wall_ms_per_step": round((t_wall1 - t_wall0) * 1e3 / args.steps, 3),
+      "e2e": {"value": round(e2e_value, 2), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 3),
+              "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+      "gpu_launches": int(launches),
+      "clocks": clocks,
+      "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq_len,
+                 "parallelism": f"fsdp{n}", "remat": "per-layer", "optimizer": "adamw fp32 master+moments",
+                 "l2": "no flush needed: each step streams >16 GB of weights/optimizer state, far above the 126 MB L2",
+                 "baseline": "vs_baseline = value / (6.91k tok/s/chip x n_gpus), Llama-3-8B seq 8192 on TPU v6e-256",
+                 "attention": trainer_attention_impl()},
+    }
+    print(json.dumps(out), flush=True)
+  rt.barrier()
+  rt.shutdown()
+  return 0
+
+
+def trainer_attention_impl() -> str:
+  from torchprime_b200.ops import functional as ops
+  return ops.attention_impl_in_use()
+
+
+if __name__ == "__main__":
+  sys.exit(main())

@@ -1,0 +1,193 @@
+"""Llama 3 / 3.1 decoder-only transformer.
+
+Module and parameter names follow the HuggingFace checkpoint layout
+(``model.layers.N.self_attn.q_proj.weight`` ...), like the reference's
+torchprime/torch_xla_models/model/llama/model.py:125-398, so exported and
+pretrained safetensors load without renaming.  The computation is organised for
+the B200 kernels instead of for a tracing compiler:
+
+* activations stay token-major ``[B, S, H*D]``; q/k/v come out of one GEMM over the
+  row-adjacent q/k/v weights and RoPE rotates the q and k heads of that buffer in
+  place;
+* residual adds ride in the epilogue of the o_proj / down_proj GEMMs, SiLU*mul in
+  the epilogue of the fused gate/up GEMM;
+* the head (final norm + lm_head + loss) runs as a chunked GEMM + cross-entropy that
+  never materialises fp32 logits when only the loss is needed.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..ops import functional as ops
+from ..ops import reference as ref
+from ..utils.profiling import trace_scope
+from . import rope
+from .base import BaseCausalLM
+
+
+class LlamaRMSNorm(nn.Module):
+  def __init__(self, hidden_size: int, eps: float = 1e-6):
+    super().__init__()
+    self.weight = nn.Parameter(torch.ones(hidden_size))
+    self.variance_epsilon = eps
+
+  def forward(self, x):
+    return ops.rms_norm(x, self.weight, self.variance_epsilon)
+
+
+class LlamaMLP(nn.Module):
+  def __init__(self, config):
+    super().__init__()
+    self.hidden_size = config.hidden_size
+    self.intermediate_size = config.intermediate_size
+    self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+    self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+    self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
+    assert config.get("hidden_act", "silu") == "silu", "only SiLU-gated MLPs are implemented"
+
+  def forward(self, x, residual=None):
+    with trace_scope("LlamaMLP"):
+      act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight)
+      return ops.linear(act, self.down_proj.weight, residual=residual)
+
+
+class LlamaAttention(nn.Module):
+  def __init__(self, config, layer_idx: int | None = None):
+    super().__init__()
+    self.config = config
+    self.layer_idx = layer_idx
+    self.hidden_size = config.hidden_size
+    self.num_heads = config.num_attention_heads
+    self.head_dim = config.get("head_dim", None) or self.hidden_size // self.num_heads
+    self.num_key_value_heads = config.num_key_value_heads
+    bias = bool(config.get("attention_bias", False))
+    self.q_proj = nn.Linear(self.hidden_size, self.num_heads * self.head_dim, bias=bias)
+    self.k_proj = nn.Linear(self.hidden_size, self.num_key_value_heads * self.head_dim, bias=bias)
+    self.v_proj = nn.Linear(self.hidden_size, self.num_key_value_heads * self.head_dim, bias=bias)
+    self.o_proj = nn.Linear(self.num_heads * self.head_dim, self.hidden_size, bias=bias)
+    self.attention_kernel = config.get("attention_kernel", None)
+
+  def forward(self, x, rope_cos, rope_sin, residual=None, position_ids=None, segment_ids=None, cp=None):
+    with trace_scope("LlamaAttention"):
+      b, s, _ = x.shape
+      hq, hkv, d = self.num_heads, self.num_key_value_heads, self.head_dim
+      bias = None
+      if self.q_proj.bias is not None:
+        bias = torch.cat([self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
+      qkv = ops.linear(x, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], bias=bias)
+      qkv = ops.rope_inplace(qkv, rope_cos, rope_sin, hq + hkv, d, s, pos=position_ids)
+      q = qkv[..., : hq * d].view(b, s, hq, d)
+      k = qkv[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+      v = qkv[..., (hq + hkv) * d:].view(b, s, hkv, d)
+      if cp is not None:
+        o = cp.attention(q, k, v, segment_ids=segment_ids)
+      elif self.attention_kernel is None and not x.is_cuda:
+        o = ref.attention(q, k, v, causal=True, q_segment_ids=segment_ids)
+      else:
+        o = ops.attention(q, k, v, causal=True, q_segment_ids=segment_ids)
+      o = o.reshape(b, s, hq * d)
+      if self.o_proj.bias is not None:
+        out = ops.linear(o, self.o_proj.weight, bias=self.o_proj.bias)
+        return out if residual is None else out + residual
+      return ops.linear(o, self.o_proj.weight, residual=residual)
+
+
+class LlamaDecoderLayer(nn.Module):
+  def __init__(self, config, layer_idx: int):
+    super().__init__()
+    self.self_attn = LlamaAttention(config, layer_idx)
+    self.mlp = LlamaMLP(config)
+    self.input_layernorm = LlamaRMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+    self.post_attention_layernorm = LlamaRMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+
+  def forward(self, hidden_states, rope_cos, rope_sin, position_ids=None, segment_ids=None, cp=None):
+    with trace_scope("LlamaDecoderLayer"):
+      x = self.input_layernorm(hidden_states)
+      h = self.self_attn(x, rope_cos, rope_sin, residual=hidden_states, position_ids=position_ids,
+                         segment_ids=segment_ids, cp=cp)
+      x = self.post_attention_layernorm(h)
+      return self.mlp(x, residual=h)
+
+
+class LlamaEmbedding(nn.Embedding):
+  def forward(self, ids):
+    return ops.embedding(ids, self.weight)
+
+
+class CausalLMHead(nn.Module):
+  """Final norm + lm_head + next-token loss, the last FSDP unit of every model."""
+
+  def __init__(self, norm: nn.Module, lm_head: nn.Linear, vocab_size: int):
+    super().__init__()
+    self.norm = norm
+    self.lm_head = lm_head
+    self.vocab_size = vocab_size
+
+  def forward(self, hidden, targets=None, want_logits=True):
+    """targets are already shifted (position t holds token t+1, -100 = ignore)."""
+    with trace_scope("CausalLMHead"):
+      h = self.norm(hidden)
+      if targets is not None and not want_logits:
+        return None, ops.linear_cross_entropy(h, self.lm_head.weight, targets)
+      logits = ops.linear(h, self.lm_head.weight).float()
+      loss = None
+      if targets is not None:
+        loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1),
+                                                 ignore_index=ref.IGNORE_INDEX)
+      return logits, loss
+
+
+class LlamaModel(nn.Module):
+  def __init__(self, config):
+    super().__init__()
+    self.vocab_size = config.vocab_size
+    self.embed_tokens = LlamaEmbedding(config.vocab_size, config.hidden_size)
+    self.layers = nn.ModuleList([LlamaDecoderLayer(config, i) for i in range(config.num_hidden_layers)])
+    self.norm = LlamaRMSNorm(config.hidden_size, eps=config.rms_norm_eps)
+    head_dim = config.get("head_dim", None) or config.hidden_size // config.num_attention_heads
+    scaling = config.get("rope_scaling", None)
+    if scaling is not None:
+      scaling = rope.RopeScaling(**{k: scaling[k] for k in ("factor", "low_freq_factor", "high_freq_factor",
+                                                           "original_context_len") if k in scaling})
+    self.register_buffer("inv_freq", rope.llama3_rope_frequencies(head_dim, config.rope_theta, scaling),
+                         persistent=False)
+    self._rope_cache = None
+
+  def rope_tables(self, seq_len: int, device, position_ids=None):
+    # with explicit positions (context parallel) the table must cover the un-split sequence
+    need = seq_len if position_ids is None else max(seq_len, int(getattr(self, "max_rope_positions", 0)) or
+                                                    int(position_ids.max().item()) + 1)
+    c = self._rope_cache
+    if c is None or c[0].shape[0] < need or c[0].device != device:
+      n = max(need, 1)
+      self._rope_cache = rope.rope_tables(self.inv_freq.float(), n, device)
+    return self._rope_cache
+
+
+class LlamaForCausalLM(BaseCausalLM):
+  def __init__(self, config):
+    super().__init__()
+    self.config = config
+    self.model = LlamaModel(config)
+    self.vocab_size = config.vocab_size
+    self.lm_head = nn.Linear(config.hidden_size, config.vocab_size, bias=False)
+    object.__setattr__(self, "_head", CausalLMHead(self.model.norm, self.lm_head, config.vocab_size))
+    self.apply(self._init_weights)
+    self.return_logits = True   # trainers switch this off to use the chunked loss path
+    self.cp = None              # context-parallel attention adaptor, set by the engine
+
+  def forward(self, input_ids, labels=None, attention_mask=None, position_ids=None, segment_ids=None,
+              labels_are_shifted=False):
+    with trace_scope("LlamaForCausalLM"):
+      b, s = input_ids.shape
+      h = self.model.embed_tokens(input_ids)
+      cos, sin = self.model.rope_tables(s, h.device, position_ids)
+      pos = position_ids.reshape(-1).to(torch.int32).contiguous() if position_ids is not None else None
+      for layer in self.model.layers:
+        h = layer(h, cos, sin, pos, segment_ids, self.cp)
+      targets = None
+      if labels is not None:
+        targets = labels if labels_are_shifted else ref.shift_labels(labels)
+      return self._head(h, targets, want_logits=self.return_logits or labels is None)

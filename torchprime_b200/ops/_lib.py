@@ -110,7 +110,16 @@ def ptr(t: torch.Tensor | None):
   return None if t is None else t.data_ptr()
 
 
+_LAUNCHES = [0]
+
+
+def launch_count() -> int:
+  """Number of kernel launches issued through this binding so far."""
+  return _LAUNCHES[0]
+
+
 def check(rc: int, what: str):
+  _LAUNCHES[0] += 1
   if rc != 0:
     if rc == -2:
       raise KernelError(f"{what}: arguments rejected (alignment / shape constraints)")

@@ -106,15 +106,18 @@ class _LinearFn(torch.autograd.Function):
     from . import kernels as k
     w = _fused_view(list(weights))
     x2 = x.reshape(-1, x.shape[-1])
+    # the result is allocated in its final shape (not returned as a view) so that later
+    # in-place operators such as RoPE may modify it
+    y = torch.empty(*x.shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
+    y2 = y.view(-1, w.shape[0])
     if residual is not None:
-      r2 = residual.reshape(-1, w.shape[0])
-      y = k.gemm(x2, w, epi=k.EPI_BF16_RES, aux=r2)
+      k.gemm(x2, w, out=y2, epi=k.EPI_BF16_RES, aux=residual.reshape(-1, w.shape[0]))
     else:
-      y = k.gemm(x2, w)
+      k.gemm(x2, w, out=y2)
     ctx.save_for_backward(x2, *weights)
     ctx.has_res = residual is not None
     ctx.x_shape = x.shape
-    return y.view(*x.shape[:-1], w.shape[0])
+    return y
 
   @staticmethod
   def backward(ctx, dy):
@@ -166,11 +169,12 @@ class _LinearSwigluFn(torch.autograd.Function):
     x2 = x.reshape(-1, x.shape[-1])
     need_grad = any(ctx.needs_input_grad)
     gu = torch.empty(x2.shape[0], w.shape[0], dtype=x.dtype, device=x.device) if need_grad else None
-    act = k.gemm(x2, w, epi=k.EPI_SWIGLU, c2=gu)
+    act = torch.empty(*x.shape[:-1], w_gate.shape[0], dtype=x.dtype, device=x.device)
+    k.gemm(x2, w, out=act.view(-1, w_gate.shape[0]), epi=k.EPI_SWIGLU, c2=gu)
     if need_grad:
       ctx.save_for_backward(x2, gu, w_gate, w_up)
     ctx.x_shape = x.shape
-    return act.view(*x.shape[:-1], w_gate.shape[0])
+    return act
 
   @staticmethod
   def backward(ctx, dact):
@@ -367,6 +371,14 @@ def set_attention_impl(name: str):
   _STATE["attention"] = name
 
 
+_ATTN_USED = {"last": "none"}
+
+
+def attention_impl_in_use() -> str:
+  """Which implementation the last attention call ran (for benchmark records)."""
+  return _ATTN_USED["last"]
+
+
 def attention(q, k, v, causal=True, scale=None, window=None, q_segment_ids=None, kv_segment_ids=None,
               softcap=None, q_positions=None, kv_positions=None):
   """softmax(q k^T * scale + mask) v on ``[B, S, H, D]`` tensors, GQA-native."""
@@ -376,15 +388,18 @@ def attention(q, k, v, causal=True, scale=None, window=None, q_segment_ids=None,
   if impl in ("auto", "sm100") and q.is_cuda and q.dtype == torch.bfloat16 and _STATE["backend"] != "torch":
     from . import attention_sm100
     if attention_sm100.supported(q, k, v, causal, window, q_segment_ids, softcap, q_positions, kv_positions):
+      _ATTN_USED["last"] = "sm100 tcgen05 kernel"
       return attention_sm100.attention(q, k, v, causal=causal, scale=scale, window=window,
                                        q_segment_ids=q_segment_ids, kv_segment_ids=kv_segment_ids,
                                        softcap=softcap, q_positions=q_positions, kv_positions=kv_positions)
     if impl == "sm100":
       raise _lib.KernelError(f"attention_sm100 does not support q{tuple(q.shape)} k{tuple(k.shape)} v{tuple(v.shape)}")
   if impl != "eager" and plain and q.is_cuda and q.shape[-1] == v.shape[-1]:
+    _ATTN_USED["last"] = "torch SDPA (library)"
     o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal,
                                        scale=scale, enable_gqa=q.shape[2] != k.shape[2])
     return o.transpose(1, 2)
+  _ATTN_USED["last"] = "eager fp32 reference"
   return ref.attention(q, k, v, causal=causal, scale=scale, window=window, q_segment_ids=q_segment_ids,
                        kv_segment_ids=kv_segment_ids, softcap=softcap, q_positions=q_positions,
                        kv_positions=kv_positions)

@@ -19,6 +19,10 @@ __all__ = [
 ]
 
 
+def launch_count() -> int:
+  return _lib.launch_count()
+
+
 def _row_major_2d(t: torch.Tensor, name: str):
   assert t.dim() == 2 and t.stride(1) == 1, f"{name} must be 2-D with unit inner stride, got {t.shape} {t.stride()}"
   return t.shape[0], t.shape[1], t.stride(0) if t.shape[0] > 1 else max(t.stride(0), t.shape[1])

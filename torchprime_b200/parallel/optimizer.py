@@ -1,0 +1,265 @@
+"""Optimizers over the engine's flat shards, learning-rate schedules and gradient clipping.
+
+The reference builds ``torch.optim.AdamW`` or HF ``Adafactor(relative_step=False,
+scale_parameter=False)`` directly on bf16 parameters and clips with
+``clip_grad_norm_`` / ``clip_grad_value_`` inside the compiled step
+(torchprime/torch_xla_models/trainer/base_trainer.py:127-156,368-380).  Here the
+optimizer state is sharded with the parameters (ZeRO-3): one fused AdamW launch updates
+the fp32 master copy and both moments of this rank's shard and writes the bf16 compute
+copy; the global gradient norm is a flat sum of squares plus a scalar all-reduce, and the
+clip coefficient stays on the device (no host round trip inside the step).
+"""
+
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..ops import functional as ops
+
+
+_CHUNK = 1 << 27   # elements per slice in the plain-PyTorch optimizer path
+
+
+def lr_lambda(kind: str, step: int, warmup: int, total: int) -> float:
+  """Multiplier of the base learning rate at optimizer step ``step`` (0-based), matching
+  ``transformers.get_scheduler`` for linear / cosine / constant(_with_warmup)."""
+  if kind in ("constant",):
+    return 1.0
+  if step < warmup:
+    return step / max(1, warmup)
+  if kind == "constant_with_warmup":
+    return 1.0
+  if kind == "linear":
+    return max(0.0, (total - step) / max(1, total - warmup))
+  if kind == "cosine":
+    prog = (step - warmup) / max(1, total - warmup)
+    return max(0.0, 0.5 * (1.0 + math.cos(math.pi * prog)))
+  raise ValueError(f"Unsupported lr_scheduler type: {kind}")
+
+
+class LRScheduler:
+  def __init__(self, base_lr: float, kind: str = "linear", warmup_steps: int = 0, total_steps: int = 1):
+    self.base_lr, self.kind, self.warmup, self.total = base_lr, kind, warmup_steps, total_steps
+    self.step_count = 0
+    lr_lambda(kind, 0, warmup_steps, total_steps)  # validates `kind`
+
+  def get_last_lr(self):
+    return [self.base_lr * lr_lambda(self.kind, self.step_count, self.warmup, self.total)]
+
+  def step(self):
+    self.step_count += 1
+
+  def state_dict(self):
+    return {"step_count": self.step_count}
+
+  def load_state_dict(self, sd):
+    self.step_count = sd["step_count"]
+
+
+class ShardedOptimizerBase:
+  def __init__(self, engine):
+    self.engine = engine
+    dev = engine.device
+    self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+    self._coef = torch.ones(1, dtype=torch.float32, device=dev)
+    self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+    self.step_count = 0
+
+  # ----------------------------------------------------------------- clipping
+  def clip_gradients(self, max_norm: float | None, max_value: float | None = None) -> torch.Tensor:
+    """Global L2 norm of all gradients (device scalar).  With ``max_norm`` > 0 the clip
+    coefficient is stored for the next ``step``; ``max_value`` clamps element-wise first."""
+    e = self.engine
+    g = e.flat_grad
+    use_k = e.is_cuda and ops.get_backend() != "torch"
+    if max_value is not None and max_value > 0:
+      g.clamp_(-max_value, max_value)
+    self._sumsq.zero_()
+    if use_k:
+      from ..ops import kernels as k
+      k.sumsq_(g, self._sumsq)
+    else:
+      for lo in range(0, g.numel(), _CHUNK):   # bounded temporaries
+        self._sumsq.add_(torch.linalg.vector_norm(g[lo:lo + _CHUNK], dtype=torch.float32).pow(2))
+    # shards are disjoint over fsdp (and tensor); replicas hold identical values
+    if dist.is_initialized():
+      for axes in (("fsdp",), ("tensor",)):
+        grp = e.mesh.group(axes) if e.mesh is not None else None
+        if grp is not None:
+          dist.all_reduce(self._sumsq, group=grp)
+    if use_k:
+      from ..ops import kernels as k
+      k.clip_coef_(self._sumsq, max_norm or 0.0, self._coef, self._norm)
+    else:
+      self._norm.copy_(self._sumsq.sqrt())
+      if max_norm is not None and max_norm > 0:
+        self._coef.copy_(torch.clamp(max_norm / (self._norm + 1e-6), max=1.0))
+      else:
+        self._coef.fill_(1.0)
+    return self._norm
+
+  def zero_grad(self):
+    self.engine.zero_grad()
+
+
+class ShardedAdamW(ShardedOptimizerBase):
+  def __init__(self, engine, lr: float, betas=(0.9, 0.999), eps: float = 1e-8, weight_decay: float = 0.01):
+    super().__init__(engine)
+    self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+    n = engine.total_shard
+    self.exp_avg = torch.zeros(n, dtype=torch.float32, device=engine.device)
+    self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=engine.device)
+
+  def step(self, lr: float | None = None):
+    e = self.engine
+    lr = self.lr if lr is None else lr
+    self.step_count += 1
+    master = e.flat_master if e.flat_master is not None else e.flat_param
+    p16 = e.flat_param if e.master_weights else None
+    if e.is_cuda and ops.get_backend() != "torch" and master.dtype == torch.float32 and master.numel() % 4 == 0:
+      from ..ops import kernels as k
+      k.adamw_(master, self.exp_avg, self.exp_avg_sq, e.flat_grad, p16, lr, self.betas[0], self.betas[1],
+               self.eps, self.weight_decay, self.step_count, clip_coef=self._coef)
+    else:
+      from ..ops import reference as ref
+      for lo in range(0, master.numel(), _CHUNK):   # bounded temporaries
+        sl = slice(lo, lo + _CHUNK)
+        p32 = master[sl] if master.dtype == torch.float32 else master[sl].float()
+        ref.adamw_step(p32, e.flat_grad[sl], self.exp_avg[sl], self.exp_avg_sq[sl], lr, self.betas[0],
+                       self.betas[1], self.eps, self.weight_decay, self.step_count, grad_scale=self._coef)
+        if master.dtype != torch.float32:
+          master[sl].copy_(p32)
+        if p16 is not None:
+          p16[sl].copy_(master[sl])
+
+  def state_dict(self):
+    return {"exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq, "step": self.step_count}
+
+  def load_state_dict(self, sd):
+    self.exp_avg.copy_(sd["exp_avg"])
+    self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+    self.step_count = int(sd["step"])
+
+
+class ShardedAdafactor(ShardedOptimizerBase):
+  """Adafactor with a fixed learning rate (``relative_step=False, scale_parameter=False``,
+  no momentum, ``clip_threshold=1.0``, ``decay_rate=-0.8``, eps (1e-30, 1e-3)) as the
+  reference configures HF's implementation (base_trainer.py:143-152).
+
+  Second moments are factored per parameter *shard piece*: the piece of a >=2-D parameter
+  that lives in this rank's flat shard is viewed as whole rows of its last dimension;
+  row statistics are local and column statistics are summed over the fsdp group, so the
+  factored estimate equals the un-sharded one.  Ragged leftovers (a shard boundary that
+  cuts a row) and 1-D parameters use the un-factored second moment."""
+
+  def __init__(self, engine, lr: float, eps=(1e-30, 1e-3), clip_threshold: float = 1.0, decay_rate: float = -0.8,
+               weight_decay: float = 0.0):
+    super().__init__(engine)
+    if weight_decay:
+      raise ValueError("Adafactor does not support weight decay.")
+    self.lr, self.eps, self.clip_threshold, self.decay_rate = lr, eps, clip_threshold, decay_rate
+    self.pieces = self._plan_pieces()
+
+  def _plan_pieces(self):
+    e = self.engine
+    pieces = []
+    for u in e.units:
+      lo, hi = e.fsdp_rank * u.shard_size, (e.fsdp_rank + 1) * u.shard_size
+      for s in u.slots:
+        a, b = max(lo, s.offset), min(hi, s.offset + s.numel)
+        if a >= b:
+          continue
+        cols = s.shape[-1] if len(s.shape) >= 2 else None
+        start = u.shard_offset + (a - lo)
+        rel0, rel1 = a - s.offset, b - s.offset
+        if cols is None:
+          pieces.append({"kind": "flat", "start": start, "n": b - a, "v": None, "slot": s})
+          continue
+        first_row = -(-rel0 // cols)
+        last_row = rel1 // cols
+        head_n = min(first_row * cols, rel1) - rel0
+        if head_n > 0:
+          pieces.append({"kind": "flat", "start": start, "n": head_n, "v": None, "slot": s})
+        if last_row > first_row:
+          pieces.append({"kind": "rows", "start": start + head_n, "rows": last_row - first_row, "cols": cols,
+                         "row0": first_row, "total_rows": s.numel // cols, "vr": None, "vc": None, "slot": s})
+        tail0 = max(last_row, first_row) * cols
+        if rel1 > tail0 and tail0 >= rel0 + head_n:
+          pieces.append({"kind": "flat", "start": start + (tail0 - rel0), "n": rel1 - tail0, "v": None, "slot": s})
+    return pieces
+
+  def step(self, lr: float | None = None):
+    e = self.engine
+    lr = self.lr if lr is None else lr
+    self.step_count += 1
+    beta2t = 1.0 - math.pow(self.step_count, self.decay_rate)
+    master = e.flat_master if e.flat_master is not None else e.flat_param
+    coef = self._coef
+    grp = e.fsdp_group if e.fsdp > 1 else None
+    for pc in self.pieces:
+      if pc["kind"] == "flat":
+        sl = slice(pc["start"], pc["start"] + pc["n"])
+        g = e.flat_grad[sl].float() * coef
+        upd = g * g + self.eps[0]
+        if pc["v"] is None:
+          pc["v"] = torch.zeros_like(upd)
+        pc["v"].mul_(beta2t).add_(upd, alpha=1.0 - beta2t)
+        upd = g * pc["v"].rsqrt()
+        denom_n = pc["n"]
+      else:
+        r, c = pc["rows"], pc["cols"]
+        sl = slice(pc["start"], pc["start"] + r * c)
+        g = (e.flat_grad[sl].float() * coef).view(r, c)
+        sq = g * g + self.eps[0]
+        if pc["vr"] is None:
+          pc["vr"] = torch.zeros(r, dtype=torch.float32, device=g.device)
+          pc["vc"] = torch.zeros(c, dtype=torch.float32, device=g.device)
+        col_sum = sq.sum(0)
+        if grp is not None:
+          dist.all_reduce(col_sum, group=grp)
+        pc["vr"].mul_(beta2t).add_(sq.mean(-1), alpha=1.0 - beta2t)
+        pc["vc"].mul_(beta2t).add_(col_sum / pc["total_rows"], alpha=1.0 - beta2t)
+        row_mean = pc["vr"].sum()
+        if grp is not None:
+          dist.all_reduce(row_mean, group=grp)
+        row_mean = row_mean / pc["total_rows"]
+        r_factor = (pc["vr"] / row_mean).rsqrt().unsqueeze(-1)
+        c_factor = pc["vc"].rsqrt().unsqueeze(0)
+        upd = (g * r_factor * c_factor).reshape(-1)
+        denom_n = r * c
+      rms = upd.norm(2) / math.sqrt(denom_n)
+      upd = upd / torch.clamp(rms / self.clip_threshold, min=1.0)
+      master[sl].add_(upd.to(master.dtype), alpha=-lr)
+    if e.master_weights:
+      e.flat_param.copy_(master)
+
+  def state_dict(self):
+    return {"step": self.step_count, "pieces": [{k: v for k, v in p.items() if k in ("v", "vr", "vc")}
+                                                for p in self.pieces]}
+
+  def load_state_dict(self, sd):
+    self.step_count = int(sd["step"])
+    for p, saved in zip(self.pieces, sd["pieces"]):
+      p.update(saved)
+
+
+def create_optimizer(task_config, engine):
+  """``adamw`` or ``adafactor`` from ``task.optimizer`` (same keys and errors as the
+  reference's ``Trainer._create_optimizer``)."""
+  oc = task_config.optimizer
+  kind = str(oc.type).lower()
+  if kind == "adamw":
+    kw = {}
+    if oc.get("weight_decay", None) is not None:
+      kw["weight_decay"] = float(oc.weight_decay)
+    if oc.get("betas", None) is not None:
+      kw["betas"] = tuple(oc.betas)
+    return ShardedAdamW(engine, lr=float(oc.learning_rate), **kw)
+  if kind == "adafactor":
+    if oc.get("weight_decay", None):
+      raise ValueError("Adafactor does not support weight decay.")
+    return ShardedAdafactor(engine, lr=float(oc.learning_rate))
+  raise ValueError(f"Unsupported optimizer type: {oc.type}. Supported types are 'adafactor' and 'adamw'.")
