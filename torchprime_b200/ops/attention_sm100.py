@@ -1,11 +1,155 @@
-"""Python side of the sm_100a flash-attention kernels (csrc/attention_sm100.cu)."""
+"""Python side of the sm_100a flash-attention kernels (csrc/attention_fwd_sm100.cu,
+csrc/attention_bwd_sm100.cu): argument checking, launch and the autograd Function.
+
+Tensors are token-major ``[B, S, H, D]`` views (for example slices of a fused QKV
+projection): unit stride over D, stride D over heads, one row pitch per token and
+batches laid out back to back.  Supported: head dim 128 (and 192 for q/k with 128 for v:
+the MLA shape), bf16, GQA, causal / full / sliding-window masks, segment ids, explicit
+query positions (context-parallel shards).
+"""
 
 from __future__ import annotations
 
+import math
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import _lib
+from ._lib import check, lib, ptr, stream_ptr
+
+P, I, LL, F = c_void_p, c_int, c_longlong, c_float
+_lib.register_signature("tpb_attn_fwd", [P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, F, I, I, P, P, P, P])
+_lib.register_signature("tpb_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, LL,
+                                         LL, LL, F, I, I, P, P, P, P])
+
+
+def _token_major(t: torch.Tensor) -> bool:
+  b, s, h, d = t.shape
+  return (t.stride(3) == 1 and t.stride(2) == d and t.stride(1) % 8 == 0 and (b == 1 or t.stride(0) == s * t.stride(1))
+          and t.data_ptr() % 16 == 0)
+
 
 def supported(q, k, v, causal, window, q_segment_ids, softcap, q_positions, kv_positions) -> bool:
-  return False
+  if softcap or kv_positions is not None:
+    return False
+  if q.dtype != torch.bfloat16 or not (q.is_cuda and k.is_cuda and v.is_cuda):
+    return False
+  dq, dv = q.shape[-1], v.shape[-1]
+  if dv != 128 or dq not in (128, 192) or k.shape[-1] != dq:
+    return False
+  if q.shape[2] % k.shape[2] != 0 or k.shape[2] != v.shape[2]:
+    return False
+  return _token_major(q) and _token_major(k) and _token_major(v)
 
 
-def attention(q, k, v, **kwargs):
-  raise NotImplementedError
+def _i32(t):
+  return None if t is None else t.reshape(-1).to(torch.int32).contiguous()
+
+
+def attn_fwd(q, k, v, causal=True, scale=None, window=None, q_pos=None, q_seg=None, kv_seg=None):
+  """Returns (o [B,Sq,Hq,128] contiguous, lse [B,Hq,Sq] fp32 in natural-log units)."""
+  b, sq, hq, dqk = q.shape
+  sk, hkv, dv = k.shape[1], k.shape[2], v.shape[-1]
+  scale = scale if scale is not None else 1.0 / math.sqrt(dqk)
+  o = torch.empty(b, sq, hq, dv, dtype=q.dtype, device=q.device)
+  lse = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
+  rc = lib().tpb_attn_fwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), b, sq, sk, hq, hkv, dqk, dv, q.stride(1),
+                          k.stride(1), v.stride(1), hq * dv, float(scale), int(bool(causal)), int(window or 0),
+                          ptr(q_pos), ptr(q_seg), ptr(kv_seg), stream_ptr())
+  check(rc, f"attn_fwd q{tuple(q.shape)} k{tuple(k.shape)}")
+  return o, lse
+
+
+def attn_bwd(do, q, k, v, o, lse, causal=True, scale=None, window=None, q_pos=None, q_seg=None, kv_seg=None,
+             dq=None, dk=None, dv=None):
+  """Gradients of :func:`attn_fwd`.  dq/dk/dv may be preallocated token-major views (for
+  example slices of one fused dQKV buffer); they are fully overwritten."""
+  b, sq, hq, dqk = q.shape
+  sk, hkv, dvd = k.shape[1], k.shape[2], v.shape[-1]
+  scale = scale if scale is not None else 1.0 / math.sqrt(dqk)
+  dq = torch.empty(b, sq, hq, dqk, dtype=q.dtype, device=q.device) if dq is None else dq
+  dk = torch.empty(b, sk, hkv, dqk, dtype=q.dtype, device=q.device) if dk is None else dk
+  dv = torch.empty(b, sk, hkv, dvd, dtype=q.dtype, device=q.device) if dv is None else dv
+  do = do.contiguous()
+  o = o.contiguous()
+  if dqk != 128:
+    return _eager_bwd(do, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk, dv)
+  sq_pad = (sq + 63) // 64 * 64
+  dq_acc = torch.zeros(b, hq, sq_pad, dqk, dtype=torch.float32, device=q.device)
+  delta = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
+  rc = lib().tpb_attn_bwd(ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(delta), ptr(dq_acc), ptr(dq),
+                          ptr(dk), ptr(dv), b, sq, sk, hq, hkv, dqk, dvd, q.stride(1), k.stride(1), v.stride(1),
+                          do.stride(1), dq.stride(1), dk.stride(1), dv.stride(1), float(scale), int(bool(causal)),
+                          int(window or 0), ptr(q_pos), ptr(q_seg), ptr(kv_seg), stream_ptr())
+  check(rc, f"attn_bwd q{tuple(q.shape)} k{tuple(k.shape)}")
+  return dq, dk, dv
+
+
+def _eager_bwd(do, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk, dv):
+  """Gradient through the fp32 eager definition, one batch element at a time.  Used for
+  shapes the backward kernel does not cover yet (q/k head dim 192)."""
+  from . import reference as ref
+  b, sq = q.shape[0], q.shape[1]
+  sk = k.shape[1]
+  for i in range(b):
+    qf, kf, vf = (t[i:i + 1].detach().float().requires_grad_(True) for t in (q, k, v))
+    o = ref.attention(
+      qf, kf, vf, causal=causal, scale=scale, window=window,
+      q_segment_ids=None if q_seg is None else q_seg.view(b, sq)[i:i + 1],
+      kv_segment_ids=None if kv_seg is None else kv_seg.view(b, sk)[i:i + 1],
+      q_positions=None if q_pos is None else q_pos.view(b, sq)[i:i + 1].long())
+    gq, gk, gv = torch.autograd.grad(o, (qf, kf, vf), do[i:i + 1].float())
+    dq[i:i + 1].copy_(gq)
+    dk[i:i + 1].copy_(gk)
+    dv[i:i + 1].copy_(gv)
+  return dq, dk, dv
+
+
+class _AttentionFn(torch.autograd.Function):
+  @staticmethod
+  def forward(ctx, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg):
+    o, lse = attn_fwd(q, k, v, causal, scale, window, q_pos, q_seg, kv_seg)
+    ctx.save_for_backward(q, k, v, o, lse, q_pos, q_seg, kv_seg)
+    ctx.args = (causal, scale, window)
+    return o
+
+  @staticmethod
+  def backward(ctx, do):
+    q, k, v, o, lse, q_pos, q_seg, kv_seg = ctx.saved_tensors
+    causal, scale, window = ctx.args
+    dq = dk = dv = None
+    fused = _fused_qkv_layout(q, k, v)
+    if fused is not None:
+      # q, k, v are column slices of one [B, S, (Hq + 2 Hkv) * D] projection: write the three
+      # gradients into the matching slices of one buffer so autograd's slice-backward can
+      # hand the GEMM a single contiguous dQKV.
+      b, s, hq, d = q.shape
+      hkv = k.shape[2]
+      buf = torch.empty(b, s, (hq + 2 * hkv) * d, dtype=q.dtype, device=q.device)
+      dq = buf[..., : hq * d].view(b, s, hq, d)
+      dk = buf[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+      dv = buf[..., (hq + hkv) * d:].view(b, s, hkv, d)
+    dq, dk, dv = attn_bwd(do, q, k, v, o, lse, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk, dv)
+    return dq, dk, dv, None, None, None, None, None, None
+
+
+def _fused_qkv_layout(q, k, v):
+  if q.shape[-1] != v.shape[-1] or q.shape[1] != k.shape[1]:
+    return None
+  same = (q.untyped_storage().data_ptr() == k.untyped_storage().data_ptr() == v.untyped_storage().data_ptr())
+  if not same or not (q.stride(1) == k.stride(1) == v.stride(1)):
+    return None
+  hq, hkv, d = q.shape[2], k.shape[2], q.shape[3]
+  if q.stride(1) != (hq + 2 * hkv) * d:
+    return None
+  if k.storage_offset() - q.storage_offset() != hq * d or v.storage_offset() - k.storage_offset() != hkv * d:
+    return None
+  return True
+
+
+def attention(q, k, v, causal=True, scale=None, window=None, q_segment_ids=None, kv_segment_ids=None, softcap=None,
+              q_positions=None, kv_positions=None):
+  q_seg = _i32(q_segment_ids)
+  kv_seg = _i32(kv_segment_ids if kv_segment_ids is not None else q_segment_ids)
+  return _AttentionFn.apply(q, k, v, causal, scale, window, _i32(q_positions), q_seg, kv_seg)
