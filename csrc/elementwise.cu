@@ -168,7 +168,7 @@ rmsnorm_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, co
 // RoPE (rotate-half; optional interleaved-pair input layout), in place.
 // One thread handles 8 consecutive elements of the first half and their partners.
 // ----------------------------------------------------------------------------
-__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long ld, int col0, int heads, int dim,
+__global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long ld, int col0, int heads, int dim, int head_stride,
                             const float* __restrict__ cosT, const float* __restrict__ sinT,
                             const int* __restrict__ pos, long long tokens, int seq_len, float sign,
                             int interleaved) {
@@ -182,7 +182,7 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ x, long long ld, int col
     const int h = (int)(th % heads);
     const long long t = th / heads;
     const int p = pos ? pos[t] : (int)(t % seq_len);
-    __nv_bfloat16* base = x + t * ld + col0 + h * dim;
+    __nv_bfloat16* base = x + t * ld + col0 + h * head_stride;
     const float* c = cosT + (size_t)p * half + v * 8;
     const float* s = sinT + (size_t)p * half + v * 8;
     float a[8], b[8];
@@ -488,15 +488,21 @@ extern "C" int tpb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
   return rc(cudaGetLastError());
 }
 
-extern "C" int tpb_rope(void* x, long long ld, int col0, int heads, int dim, const float* cos, const float* sin,
-                        const int* pos, int tokens, int seq_len, int inverse, int interleaved, void* stream) {
-  if (dim % 16 || ld % 8 || col0 % 8) return -2;
+extern "C" int tpb_rope_strided(void* x, long long ld, int col0, int heads, int dim, int head_stride,
+                                const float* cos, const float* sin, const int* pos, int tokens, int seq_len,
+                                int inverse, int interleaved, void* stream) {
+  if (dim % 16 || ld % 8 || col0 % 8 || head_stride % 8 || head_stride < dim) return -2;
   if (tokens <= 0 || heads <= 0) return 0;
   long long total = (long long)tokens * heads * (dim / 16);
-  rope_kernel<<<grid_for(total, 256), 256, 0, STREAM(stream)>>>((__nv_bfloat16*)x, ld, col0, heads, dim, cos, sin,
-                                                                pos, tokens, seq_len, inverse ? -1.f : 1.f,
-                                                                interleaved);
+  rope_kernel<<<grid_for(total, 256), 256, 0, STREAM(stream)>>>((__nv_bfloat16*)x, ld, col0, heads, dim, head_stride,
+                                                                cos, sin, pos, tokens, seq_len,
+                                                                inverse ? -1.f : 1.f, interleaved);
   return rc(cudaGetLastError());
+}
+
+extern "C" int tpb_rope(void* x, long long ld, int col0, int heads, int dim, const float* cos, const float* sin,
+                        const int* pos, int tokens, int seq_len, int inverse, int interleaved, void* stream) {
+  return tpb_rope_strided(x, ld, col0, heads, dim, dim, cos, sin, pos, tokens, seq_len, inverse, interleaved, stream);
 }
 
 extern "C" int tpb_swiglu_fwd(const void* gu, void* act, int rows, int f, void* stream) {
@@ -585,3 +591,4 @@ extern "C" int tpb_cast_f32_to_bf16(const float* src, void* dst, long long n, fl
                                                                 accumulate);
   return rc(cudaGetLastError());
 }
+

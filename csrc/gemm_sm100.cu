@@ -41,11 +41,28 @@ struct GemmParams {
   long long ldaux;
   void* c2;          // pre-activation output (EPI_SWIGLU, optional)
   long long ldc2;
-  int b_split;       // EPI_SWIGLU: row of B where the "up" half starts (= F)
+  int b_split;       // EPI_SWIGLU: column of c2 where the "up" half starts (= F)
+  int b2_off;        // EPI_SWIGLU: row/column offset of the "up" half inside the second B map
   float alpha;
   int epi;
   int group_m;       // rasterisation: m-tiles per group
   int* status;
+  // Grouped (mixture-of-experts) modes.  0: dense.
+  // 1: rows of A/C are grouped by expert in 128-row aligned segments; tile_expert[m_tile] is the
+  //    expert whose weights (3rd coordinate of the B maps) that tile uses, -1 = tile unused.
+  // 2: per-expert wgrad: E independent [M,N] outputs, expert e contracts over rows
+  //    [k_offsets[e], k_offsets[e+1]) (multiples of 64) of A and B; C of expert e is at
+  //    C + e * c_stride elements.
+  int mode;
+  int num_experts;
+  const int* tile_expert;
+  const int* k_offsets;
+  long long c_stride;
+};
+
+struct TileInfo {
+  int tm, tn, e, kb0, kb1;
+  bool skip;
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int group_m, int& tm,
@@ -59,12 +76,31 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
   tn = within / gsize;
 }
 
+__device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int t, int m_tiles, int n_tiles, int num_kb) {
+  TileInfo ti;
+  ti.e = 0; ti.kb0 = 0; ti.kb1 = num_kb; ti.skip = false;
+  if (p.mode == 2) {
+    const int per = m_tiles * n_tiles;
+    ti.e = t / per;
+    tile_coords(t - ti.e * per, m_tiles, n_tiles, p.group_m, ti.tm, ti.tn);
+    ti.kb0 = p.k_offsets[ti.e] / BK;
+    ti.kb1 = p.k_offsets[ti.e + 1] / BK;
+  } else {
+    tile_coords(t, m_tiles, n_tiles, p.group_m, ti.tm, ti.tn);
+    if (p.mode == 1) {
+      ti.e = p.tile_expert[ti.tm];
+      ti.skip = ti.e < 0;
+    }
+  }
+  return ti;
+}
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -80,7 +116,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int n_logical = swiglu ? p.N / 2 : p.N;
   const int m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = (n_logical + tile_n_out - 1) / tile_n_out;
-  const int num_tiles = m_tiles * n_tiles;
+  const int num_tiles = m_tiles * n_tiles * (p.mode == 2 ? p.num_experts : 1);
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
@@ -108,14 +144,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (lane == 0) {
       tma_prefetch_desc(&tmA);
       tma_prefetch_desc(&tmB);
+      tma_prefetch_desc(&tmB2);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        int tm, tn;
-        tile_coords(t, m_tiles, n_tiles, p.group_m, tm, tn);
-        const int m0 = tm * BM, n0 = tn * tile_n_out;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        const TileInfo ti = tile_info(p, t, m_tiles, n_tiles, num_kb);
+        if (ti.skip) continue;
+        const int m0 = ti.tm * BM, n0 = ti.tn * tile_n_out;
+        const int ez = p.mode == 1 ? ti.e : 0;
+        for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, p.status, kTimeoutStageFree, 1)) {
             ok = false;
             break;
@@ -133,14 +171,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           if (!B_MN) {
             // two boxes {64 k, 128 rows}; for SwiGLU the second one comes from the "up" half
-            int r1 = swiglu ? p.b_split + n0 : n0 + 128;
-            tma_load_2d(sB, &tmB, &full[stage], k0, n0);
-            tma_load_2d(sB + 16384, &tmB, &full[stage], k0, r1);
+            // (with two B maps the "up" half is the same rows of the second tensor)
+            tma_load_3d(sB, &tmB, &full[stage], k0, n0, ez);
+            tma_load_3d(sB + 16384, &tmB2, &full[stage], k0, swiglu ? p.b2_off + n0 : n0 + 128, ez);
           } else {
 #pragma unroll
             for (int c = 0; c < BN / 64; ++c) {
-              int col = swiglu ? (c < 2 ? n0 + c * 64 : p.b_split + n0 + (c - 2) * 64) : n0 + c * 64;
-              tma_load_2d(sB + c * 8192, &tmB, &full[stage], col, k0);
+              if (swiglu && c >= 2)
+                tma_load_3d(sB + c * 8192, &tmB2, &full[stage], p.b2_off + n0 + (c - 2) * 64, k0, ez);
+              else
+                tma_load_3d(sB + c * 8192, &tmB, &full[stage], n0 + c * 64, k0, ez);
             }
           }
           if (++stage == STAGES) {
@@ -158,13 +198,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const TileInfo ti = tile_info(p, t, m_tiles, n_tiles, num_kb);
+        if (ti.skip) continue;
         const int acc = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
+        ++local;
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.status, kTimeoutAccFree, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, p.status, kTimeoutTmaFull, 3)) {
             ok = false;
             break;
@@ -178,7 +221,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                         : make_smem_desc(sA + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(sB + k * 2048, 8192, 1024)
                                         : make_smem_desc(sB + k * 32, 16, 1024);
-            mma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+            mma_ss(d_tmem, adesc, bdesc, idesc, ((kb - ti.kb0) | k) != 0);
           }
           tc_commit(&empty[stage]);
           if (++stage == STAGES) {
@@ -193,20 +236,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int local = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x, ++local) {
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      const TileInfo ti = tile_info(p, t, m_tiles, n_tiles, num_kb);
+      if (ti.skip) continue;
       const int acc = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      ++local;
       if (!mbar_wait(&acc_full[acc], acc_phase, p.status, kTimeoutAccFull, 4)) break;
       tc_fence_after();
-      int tm, tn;
-      tile_coords(t, m_tiles, n_tiles, p.group_m, tm, tn);
+      const int tm = ti.tm, tn = ti.tn;
+      const bool empty_k = ti.kb1 <= ti.kb0;   // nothing was accumulated: the tile is all zeros
+      const long long c_off = p.mode == 2 ? (long long)ti.e * p.c_stride : 0;
       const int row = tm * BM + q * 32 + lane;
       const int n0 = tn * tile_n_out;
       const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       const bool row_ok = row < p.M;
 
       if (swiglu) {
-        __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc;
+        __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + (long long)row * p.ldc;
         __nv_bfloat16* C2 =
             p.c2 ? reinterpret_cast<__nv_bfloat16*>(p.c2) + (long long)row * p.ldc2 : nullptr;
 #pragma unroll 1
@@ -256,11 +303,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           uint32_t r[32];
           tmem_ld32(t_addr + c * 32, r);
           tmem_wait_ld();
+          if (empty_k) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = 0;
+          }
           const int col = n0 + c * 32;
           if (!row_ok || col >= p.N) continue;
           const bool full_chunk = col + 32 <= p.N;
           if (p.epi == TPB_EPI_F32 || p.epi == TPB_EPI_F32_ACC) {
-            float* C = reinterpret_cast<float*>(p.C) + (long long)row * p.ldc + col;
+            float* C = reinterpret_cast<float*>(p.C) + c_off + (long long)row * p.ldc + col;
             const bool accm = p.epi == TPB_EPI_F32_ACC;
             if (full_chunk) {
 #pragma unroll
@@ -280,7 +331,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               }
             }
           } else {
-            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)row * p.ldc + col;
+            __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + (long long)row * p.ldc + col;
             const __nv_bfloat16* R = nullptr;
             if (p.epi == TPB_EPI_BF16_ACC) R = C;
             if (p.epi == TPB_EPI_BF16_RES)
@@ -329,19 +380,97 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 // ----------------------------------------------------------------------------
 int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t pitch_elems,
                  uint32_t box_inner, uint32_t box_outer, int elem_bytes);  // tma.cu
+int make_tmap_3d(CUtensorMap* map, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_elems,
+                 uint64_t stride2_elems, uint32_t box0, uint32_t box1);
 int sm_count();  // runtime.cu
 
 template <bool A_MN, bool B_MN>
-cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid,
-                        cudaStream_t stream) {
+cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
+                        int grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(gemm_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  gemm_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, p);
+  gemm_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, tb2, p);
   return cudaGetLastError();
+}
+
+
+
+struct GemmCall {
+  const void* A; const void* B; const void* B2; void* C;
+  int M, N, K, E;
+  long long lda, ldb, b_expert_stride, ldc;
+  int a_mn, b_mn, epi;
+  float alpha;
+  const void* aux; long long ldaux;
+  void* c2; long long ldc2;
+  int max_ctas;
+  int mode; const int* tile_expert; const int* k_offsets; long long c_stride;
+};
+
+static int run_gemm(const GemmCall& g, cudaStream_t stream) {
+  if (g.M <= 0 || g.N <= 0 || g.K <= 0) return 0;
+  const bool swiglu = g.epi == TPB_EPI_SWIGLU;
+  auto misaligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) % 16) != 0; };
+  if ((g.lda % 8) || (g.ldb % 8) || (g.b_expert_stride % 8) || misaligned(g.A) || misaligned(g.B) || misaligned(g.C) ||
+      (g.B2 && misaligned(g.B2)))
+    return -2;
+  const bool f32out = g.epi == TPB_EPI_F32 || g.epi == TPB_EPI_F32_ACC;
+  if (g.ldc % (f32out ? 4 : 8)) return -2;
+  if (swiglu && ((g.N % 2) || ((g.N / 2) % 8))) return -2;
+  if (g.mode == 2 && !(g.a_mn && g.b_mn)) return -2;
+  if (g.mode == 1 && g.a_mn) return -2;
+  const bool two_b = swiglu && g.B2 != nullptr && g.B2 != g.B;
+  const int b_extent = two_b ? g.N / 2 : g.N;       // rows (K-major) or columns (MN-major) of one B tensor
+  const int b_experts = g.mode == 1 ? g.E : 1;
+  CUtensorMap ta, tb, tb2;
+  int r;
+  if (!g.a_mn) r = make_tmap_2d(&ta, g.A, g.K, g.M, g.lda, 64, 128, 2);
+  else         r = make_tmap_2d(&ta, g.A, g.M, g.K, g.lda, 64, 64, 2);
+  if (r) return r < 0 ? -3 : -4;
+  const uint64_t estride = b_experts > 1 ? (uint64_t)g.b_expert_stride : (uint64_t)g.ldb * (g.b_mn ? g.K : b_extent);
+  auto make_b = [&](CUtensorMap* m, const void* ptr) {
+    return !g.b_mn ? make_tmap_3d(m, ptr, g.K, b_extent, b_experts, g.ldb, estride, 64, 128)
+                   : make_tmap_3d(m, ptr, b_extent, g.K, b_experts, g.ldb, estride, 64, 64);
+  };
+  r = make_b(&tb, g.B);
+  if (r) return r < 0 ? -3 : -5;
+  if (two_b) {
+    r = make_b(&tb2, g.B2);
+    if (r) return r < 0 ? -3 : -5;
+  } else {
+    tb2 = tb;
+  }
+
+  GemmParams p;
+  p.M = g.M; p.N = g.N; p.K = g.K;
+  p.C = g.C; p.ldc = g.ldc;
+  p.aux = g.aux; p.ldaux = g.ldaux;
+  p.c2 = g.c2; p.ldc2 = g.ldc2;
+  p.b_split = g.N / 2;
+  p.b2_off = two_b ? 0 : g.N / 2;
+  p.alpha = g.alpha;
+  p.epi = g.epi;
+  p.status = status_block();
+  p.mode = g.mode; p.num_experts = g.E; p.tile_expert = g.tile_expert; p.k_offsets = g.k_offsets;
+  p.c_stride = g.c_stride;
+  const int n_logical = swiglu ? g.N / 2 : g.N;
+  const int tile_n = swiglu ? BN / 2 : BN;
+  const int m_tiles = (g.M + BM - 1) / BM, n_tiles = (n_logical + tile_n - 1) / tile_n;
+  p.group_m = m_tiles < 16 ? m_tiles : 16;
+  long long tiles = (long long)m_tiles * n_tiles * (g.mode == 2 ? g.E : 1);
+  int cap = sm_count();
+  if (g.max_ctas > 0 && g.max_ctas < cap) cap = g.max_ctas;
+  const int grid = tiles > cap ? cap : (int)tiles;
+  cudaError_t e;
+  if (!g.a_mn && !g.b_mn)      e = launch_gemm<false, false>(ta, tb, tb2, p, grid, stream);
+  else if (!g.a_mn && g.b_mn)  e = launch_gemm<false, true>(ta, tb, tb2, p, grid, stream);
+  else if (g.a_mn && !g.b_mn)  e = launch_gemm<true, false>(ta, tb, tb2, p, grid, stream);
+  else                         e = launch_gemm<true, true>(ta, tb, tb2, p, grid, stream);
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
 }
 
 }  // namespace tpb
@@ -352,45 +481,30 @@ extern "C" int tpb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
                              long long ldb, long long ldc, int a_mn, int b_mn, int epi, float alpha,
                              const void* aux, long long ldaux, void* c2, long long ldc2, int max_ctas,
                              void* stream_) {
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  const bool swiglu = epi == TPB_EPI_SWIGLU;
-  if ((lda % 8) || (ldb % 8) || (reinterpret_cast<uintptr_t>(A) % 16) || (reinterpret_cast<uintptr_t>(B) % 16) ||
-      (reinterpret_cast<uintptr_t>(C) % 16))
-    return -2;
-  const bool f32out = epi == TPB_EPI_F32 || epi == TPB_EPI_F32_ACC;
-  if (ldc % (f32out ? 4 : 8)) return -2;
-  if (swiglu && ((N % 2) || ((N / 2) % 8))) return -2;
-  CUtensorMap ta, tb;
-  int r;
-  if (!a_mn) r = make_tmap_2d(&ta, A, K, M, lda, 64, 128, 2);
-  else       r = make_tmap_2d(&ta, A, M, K, lda, 64, 64, 2);
-  if (r) return r < 0 ? -3 : -4;
-  if (!b_mn) r = make_tmap_2d(&tb, B, K, N, ldb, 64, 128, 2);
-  else       r = make_tmap_2d(&tb, B, N, K, ldb, 64, 64, 2);
-  if (r) return r < 0 ? -3 : -5;
+  GemmCall g{};
+  g.A = A; g.B = B; g.B2 = nullptr; g.C = C;
+  g.M = M; g.N = N; g.K = K; g.E = 1;
+  g.lda = lda; g.ldb = ldb; g.b_expert_stride = 0; g.ldc = ldc;
+  g.a_mn = a_mn; g.b_mn = b_mn; g.epi = epi; g.alpha = alpha;
+  g.aux = aux; g.ldaux = ldaux; g.c2 = c2; g.ldc2 = ldc2; g.max_ctas = max_ctas;
+  g.mode = 0;
+  return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
+}
 
-  GemmParams p;
-  p.M = M; p.N = N; p.K = K;
-  p.C = C; p.ldc = ldc;
-  p.aux = aux; p.ldaux = ldaux;
-  p.c2 = c2; p.ldc2 = ldc2;
-  p.b_split = N / 2;
-  p.alpha = alpha;
-  p.epi = epi;
-  p.status = status_block();
-  const int n_logical = swiglu ? N / 2 : N;
-  const int tile_n = swiglu ? BN / 2 : BN;
-  const int m_tiles = (M + BM - 1) / BM, n_tiles = (n_logical + tile_n - 1) / tile_n;
-  p.group_m = m_tiles < 16 ? m_tiles : 16;
-  int grid = m_tiles * n_tiles;
-  int cap = sm_count();
-  if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
-  if (grid > cap) grid = cap;
-  cudaError_t e;
-  if (!a_mn && !b_mn)      e = launch_gemm<false, false>(ta, tb, p, grid, stream);
-  else if (!a_mn && b_mn)  e = launch_gemm<false, true>(ta, tb, p, grid, stream);
-  else if (a_mn && !b_mn)  e = launch_gemm<true, false>(ta, tb, p, grid, stream);
-  else                     e = launch_gemm<true, true>(ta, tb, p, grid, stream);
-  return e == cudaSuccess ? 0 : 1000 + (int)e;
+extern "C" int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B2, void* C, int M, int N, int K,
+                                     int E, long long lda, long long ldb, long long b_expert_stride, long long ldc,
+                                     int a_mn, int b_mn, int epi, float alpha, void* c2, long long ldc2, int mode,
+                                     const int* tile_expert, const int* k_offsets, long long c_stride,
+                                     void* stream_) {
+  if (mode != 1 && mode != 2) return -2;
+  if (mode == 1 && !tile_expert) return -2;
+  if (mode == 2 && !k_offsets) return -2;
+  GemmCall g{};
+  g.A = A; g.B = B; g.B2 = B2; g.C = C;
+  g.M = M; g.N = N; g.K = K; g.E = E;
+  g.lda = lda; g.ldb = ldb; g.b_expert_stride = b_expert_stride; g.ldc = ldc;
+  g.a_mn = a_mn; g.b_mn = b_mn; g.epi = epi; g.alpha = alpha;
+  g.aux = nullptr; g.ldaux = 0; g.c2 = c2; g.ldc2 = ldc2; g.max_ctas = 0;
+  g.mode = mode; g.tile_expert = tile_expert; g.k_offsets = k_offsets; g.c_stride = c_stride;
+  return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
 }

@@ -1,0 +1,285 @@
+// Mixture-of-experts support kernels: fused router top-k (softmax / sigmoid with
+// group-limited selection), row gather into the expert-grouped layout, weighted combine
+// back to token order and the routing-weight gradient.  The grouped GEMMs themselves are
+// the grouped modes of gemm_sm100.cu.
+
+#include "common.cuh"
+#include "tpb.h"
+
+namespace tpb {
+
+int sm_count();
+
+constexpr int ROUTER_MAX_PER_LANE = 8;  // experts per lane -> up to 256 experts
+
+struct ArgMax {
+  float v;
+  int i;
+};
+__device__ __forceinline__ ArgMax warp_argmax(float v, int i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+  return {v, i};
+}
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// One warp per token.  Expert e lives in register e / 32 of lane e % 32.
+//   mode 0: p = softmax(logits); top-k of p; weights renormalised to sum 1 (if norm_topk).
+//   mode 1: s = sigmoid(logits); selection score = s + bias, restricted to the topk_group
+//           groups with the largest (sum of top-2 selection scores); weights = s at the
+//           selected experts, normalised (if norm_topk) and multiplied by `scale`.
+template <typename T>
+__global__ void router_topk_kernel(const T* __restrict__ logits, const float* __restrict__ bias,
+                                   float* __restrict__ w_out, int* __restrict__ idx_out,
+                                   float* __restrict__ scores_out, int tokens, int E, int K, int mode, int n_group,
+                                   int topk_group, int norm_topk, float scale) {
+  const int lane = threadIdx.x & 31;
+  const int per_lane = (E + 31) / 32;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < tokens; t += (gridDim.x * blockDim.x) >> 5) {
+    float s[ROUTER_MAX_PER_LANE], sel[ROUTER_MAX_PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+      const int e = j * 32 + lane;
+      float x = -INFINITY;
+      if (j < per_lane && e < E) x = (float)logits[(long long)t * E + e];
+      s[j] = x;
+      mx = fmaxf(mx, x);
+    }
+    if (mode == 0) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+        s[j] = (s[j] == -INFINITY) ? 0.f : __expf(s[j] - mx);
+        sum += s[j];
+      }
+      sum = warp_sum_f(sum);
+      const float inv = 1.f / sum;
+#pragma unroll
+      for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+        s[j] *= inv;
+        const int e = j * 32 + lane;
+        sel[j] = (j < per_lane && e < E) ? s[j] : -INFINITY;
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+        const int e = j * 32 + lane;
+        const bool ok = j < per_lane && e < E;
+        s[j] = ok ? 1.f / (1.f + __expf(-s[j])) : 0.f;
+        sel[j] = ok ? s[j] + (bias ? bias[e] : 0.f) : -INFINITY;
+      }
+      if (n_group > 1) {
+        const int gs = E / n_group;
+        float gscore = -INFINITY;  // lane g keeps the score of group g
+        for (int g = 0; g < n_group; ++g) {
+          float best = -INFINITY;
+          int besti = 0x7fffffff;
+#pragma unroll
+          for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+            const int e = j * 32 + lane;
+            if (j < per_lane && e < E && e / gs == g && sel[j] > best) { best = sel[j]; besti = e; }
+          }
+          const ArgMax a1 = warp_argmax(best, besti);
+          float second = -INFINITY;
+          int secondi = 0x7fffffff;
+#pragma unroll
+          for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+            const int e = j * 32 + lane;
+            if (j < per_lane && e < E && e / gs == g && e != a1.i && sel[j] > second) { second = sel[j]; secondi = e; }
+          }
+          const ArgMax a2 = warp_argmax(second, secondi);
+          const float sc = a1.v + (gs > 1 ? a2.v : 0.f);
+          if (lane == g) gscore = sc;
+        }
+        unsigned keep_groups = 0;
+        for (int r = 0; r < topk_group; ++r) {
+          const ArgMax a = warp_argmax(gscore, lane);
+          keep_groups |= 1u << a.i;
+          if (lane == a.i) gscore = -INFINITY;
+        }
+#pragma unroll
+        for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+          const int e = j * 32 + lane;
+          if (j < per_lane && e < E && !((keep_groups >> (e / gs)) & 1u)) sel[j] = 0.f;
+        }
+      }
+    }
+    if (scores_out) {
+#pragma unroll
+      for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+        const int e = j * 32 + lane;
+        if (j < per_lane && e < E) scores_out[(long long)t * E + e] = s[j];
+      }
+    }
+    // top-k by repeated warp arg-max (ties go to the lower expert index)
+    float wsum = 0.f;
+    float my_w = 0.f;   // lane r keeps the r-th weight
+    int my_i = 0;
+    for (int r = 0; r < K; ++r) {
+      float best = -INFINITY;
+      int besti = 0x7fffffff;
+#pragma unroll
+      for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+        const int e = j * 32 + lane;
+        if (j < per_lane && e < E && (sel[j] > best || (sel[j] == best && e < besti))) { best = sel[j]; besti = e; }
+      }
+      const ArgMax a = warp_argmax(best, besti);
+      float val = 0.f;
+#pragma unroll
+      for (int j = 0; j < ROUTER_MAX_PER_LANE; ++j) {
+        const int e = j * 32 + lane;
+        if (e == a.i) { val = s[j]; sel[j] = -INFINITY; }
+      }
+      val = warp_sum_f(val);   // only the owning lane contributed
+      wsum += val;
+      if (lane == r) { my_w = val; my_i = a.i; }
+    }
+    float norm = 1.f;
+    if (norm_topk) norm = (mode == 0) ? 1.f / wsum : 1.f / (wsum + 1e-20f);
+    if (lane < K) {
+      w_out[(long long)t * K + lane] = my_w * norm * scale;
+      idx_out[(long long)t * K + lane] = my_i;
+    }
+  }
+}
+
+// out[r, :] = (src_row[r] >= 0) ? scale[r] * x[src_row[r], :] : 0       (rows of 16-byte vectors)
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, const int* __restrict__ src_row,
+                                  const float* __restrict__ row_scale, uint4* __restrict__ out, long long rows,
+                                  int nvec) {
+  const long long total = rows * nvec;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / nvec;
+    const int c = (int)(i % nvec);
+    const int src = src_row[r];
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (src >= 0) {
+      v = x[(long long)src * nvec + c];
+      if (row_scale) {
+        const float sc = row_scale[r];
+        float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), cc = unpack_bf16(v.z), d = unpack_bf16(v.w);
+        v = make_uint4(pack_bf16(a.x * sc, a.y * sc), pack_bf16(b.x * sc, b.y * sc), pack_bf16(cc.x * sc, cc.y * sc),
+                       pack_bf16(d.x * sc, d.y * sc));
+      }
+    }
+    out[i] = v;
+  }
+}
+
+// out[t, :] = sum_k w[t,k] * rows[dest[t,k], :]   (dest < 0: dropped pair; w null: weight 1)
+__global__ void moe_combine_kernel(const uint4* __restrict__ rows, const int* __restrict__ dest,
+                                   const float* __restrict__ w, uint4* __restrict__ out, long long tokens, int K,
+                                   int nvec) {
+  const long long total = tokens * nvec;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / nvec;
+    const int c = (int)(i % nvec);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int k = 0; k < K; ++k) {
+      const int r = dest[t * K + k];
+      if (r < 0) continue;
+      const float wk = w ? w[t * K + k] : 1.f;
+      const uint4 v = rows[(long long)r * nvec + c];
+      float2 a = unpack_bf16(v.x), b = unpack_bf16(v.y), cc = unpack_bf16(v.z), d = unpack_bf16(v.w);
+      acc[0] += wk * a.x; acc[1] += wk * a.y; acc[2] += wk * b.x; acc[3] += wk * b.y;
+      acc[4] += wk * cc.x; acc[5] += wk * cc.y; acc[6] += wk * d.x; acc[7] += wk * d.y;
+    }
+    out[i] = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
+                        pack_bf16(acc[6], acc[7]));
+  }
+}
+
+// dw[t,k] = <rows[dest[t,k], :], dout[t, :]>     (one warp per (t,k) pair)
+__global__ void moe_combine_dw_kernel(const uint4* __restrict__ rows, const int* __restrict__ dest,
+                                      const uint4* __restrict__ dout, float* __restrict__ dw, long long pairs, int K,
+                                      int nvec) {
+  const int lane = threadIdx.x & 31;
+  for (long long pr = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; pr < pairs;
+       pr += ((long long)gridDim.x * blockDim.x) >> 5) {
+    const int r = dest[pr];
+    float acc = 0.f;
+    if (r >= 0) {
+      const long long t = pr / K;
+      for (int c = lane; c < nvec; c += 32) {
+        const uint4 a = rows[(long long)r * nvec + c], b = dout[t * nvec + c];
+        float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), a2 = unpack_bf16(a.z), a3 = unpack_bf16(a.w);
+        float2 b0 = unpack_bf16(b.x), b1 = unpack_bf16(b.y), b2 = unpack_bf16(b.z), b3 = unpack_bf16(b.w);
+        acc += a0.x * b0.x + a0.y * b0.y + a1.x * b1.x + a1.y * b1.y + a2.x * b2.x + a2.y * b2.y + a3.x * b3.x +
+               a3.y * b3.y;
+      }
+    }
+    acc = warp_sum_f(acc);
+    if (lane == 0) dw[pr] = acc;
+  }
+}
+
+static inline int grid_for_items(long long items, int threads, int waves = 8) {
+  long long blocks = (items + threads - 1) / threads;
+  const long long cap = (long long)sm_count() * waves;
+  if (blocks > cap) blocks = cap;
+  return blocks < 1 ? 1 : (int)blocks;
+}
+
+}  // namespace tpb
+
+using namespace tpb;
+#define STREAM(s) reinterpret_cast<cudaStream_t>(s)
+static inline int rc_of(cudaError_t e) { return e == cudaSuccess ? 0 : 1000 + (int)e; }
+
+extern "C" int tpb_router_topk(const void* logits, int logits_is_bf16, const float* bias, float* w_out, int* idx_out,
+                               float* scores_out, int tokens, int E, int K, int mode, int n_group, int topk_group,
+                               int norm_topk, float scale, void* stream) {
+  if (E > 32 * ROUTER_MAX_PER_LANE || K > 32 || K > E || E <= 0) return -2;
+  if (mode == 1 && n_group > 1 && (E % n_group || n_group > 32 || topk_group > n_group)) return -2;
+  if (tokens <= 0) return 0;
+  const int grid = grid_for_items((long long)tokens * 32, 256);
+  if (logits_is_bf16)
+    router_topk_kernel<__nv_bfloat16><<<grid, 256, 0, STREAM(stream)>>>(
+        (const __nv_bfloat16*)logits, bias, w_out, idx_out, scores_out, tokens, E, K, mode, n_group, topk_group,
+        norm_topk, scale);
+  else
+    router_topk_kernel<float><<<grid, 256, 0, STREAM(stream)>>>((const float*)logits, bias, w_out, idx_out, scores_out,
+                                                                tokens, E, K, mode, n_group, topk_group, norm_topk,
+                                                                scale);
+  return rc_of(cudaGetLastError());
+}
+
+extern "C" int tpb_moe_gather(const void* x, const int* src_row, const float* row_scale, void* out, long long rows,
+                              int dim, void* stream) {
+  if (dim % 8) return -2;
+  if (rows <= 0) return 0;
+  moe_gather_kernel<<<grid_for_items(rows * (dim / 8), 256), 256, 0, STREAM(stream)>>>(
+      (const uint4*)x, src_row, row_scale, (uint4*)out, rows, dim / 8);
+  return rc_of(cudaGetLastError());
+}
+
+extern "C" int tpb_moe_combine(const void* rows, const int* dest, const float* w, void* out, long long tokens, int K,
+                               int dim, void* stream) {
+  if (dim % 8) return -2;
+  if (tokens <= 0) return 0;
+  moe_combine_kernel<<<grid_for_items(tokens * (dim / 8), 256), 256, 0, STREAM(stream)>>>(
+      (const uint4*)rows, dest, w, (uint4*)out, tokens, K, dim / 8);
+  return rc_of(cudaGetLastError());
+}
+
+extern "C" int tpb_moe_combine_dw(const void* rows, const int* dest, const void* dout, float* dw, long long tokens,
+                                  int K, int dim, void* stream) {
+  if (dim % 8) return -2;
+  if (tokens <= 0) return 0;
+  moe_combine_dw_kernel<<<grid_for_items(tokens * K * 32, 256), 256, 0, STREAM(stream)>>>(
+      (const uint4*)rows, dest, (const uint4*)dout, dw, tokens * K, K, dim / 8);
+  return rc_of(cudaGetLastError());
+}

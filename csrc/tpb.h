@@ -43,6 +43,11 @@ int tpb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
 int tpb_rope(void* x, long long ld, int col0, int heads, int dim, const float* cos, const float* sin,
              const int* pos, int tokens, int seq_len, int inverse, int interleaved, void* stream);
 
+// Same with heads `head_stride` elements apart (rotating a `dim`-wide slice of wider heads).
+int tpb_rope_strided(void* x, long long ld, int col0, int heads, int dim, int head_stride, const float* cos,
+                     const float* sin, const int* pos, int tokens, int seq_len, int inverse, int interleaved,
+                     void* stream);
+
 // act[T,F] = silu(gu[:, :F]) * gu[:, F:]
 int tpb_swiglu_fwd(const void* gu, void* act, int rows, int f, void* stream);
 // dgu[T,2F] from dact[T,F] and gu
@@ -73,6 +78,42 @@ int tpb_embedding_bwd(const void* dout, const long long* ids, void* dtable, int 
 
 // bf16 <- fp32 with scale, and fp32 accumulate into bf16 destinations
 int tpb_cast_f32_to_bf16(const float* src, void* dst, long long n, float scale, int accumulate, void* stream);
+
+// Grouped (mixture-of-experts) GEMM, see GemmParams::mode in gemm_sm100.cu.
+//  mode 1: C[rows of expert e] = A[rows of e] * B[e]^T; rows are grouped in 128-row aligned
+//          segments, tile_expert[m_tile] names the expert of each 128-row tile (-1: unused).
+//          B (and B2 for the "up" half of a SwiGLU epilogue) hold E matrices b_expert_stride apart.
+//  mode 2: per-expert wgrad C[e] = A[:, rows of e] * B[:, rows of e]^T with both operands stored
+//          row-major over the grouped rows (a_mn = b_mn = 1); k_offsets[E+1] are 64-aligned.
+int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B2, void* C, int M, int N, int K, int E,
+                          long long lda, long long ldb, long long b_expert_stride, long long ldc, int a_mn, int b_mn,
+                          int epi, float alpha, void* c2, long long ldc2, int mode, const int* tile_expert,
+                          const int* k_offsets, long long c_stride, void* stream);
+
+// Router: one warp per token.  mode 0 softmax-top-k(-renormalise); mode 1 sigmoid + bias with
+// group-limited selection.  w_out [T,K] fp32, idx_out [T,K] int32, scores_out [T,E] fp32 (optional).
+int tpb_router_topk(const void* logits, int logits_is_bf16, const float* bias, float* w_out, int* idx_out,
+                    float* scores_out, int tokens, int E, int K, int mode, int n_group, int topk_group, int norm_topk,
+                    float scale, void* stream);
+// out[r,:] = src_row[r] >= 0 ? row_scale[r] * x[src_row[r],:] : 0
+int tpb_moe_gather(const void* x, const int* src_row, const float* row_scale, void* out, long long rows, int dim,
+                   void* stream);
+// out[t,:] = sum_k w[t,k] * rows[dest[t,k],:]
+int tpb_moe_combine(const void* rows, const int* dest, const float* w, void* out, long long tokens, int K, int dim,
+                    void* stream);
+// dw[t,k] = <rows[dest[t,k],:], dout[t,:]>
+int tpb_moe_combine_dw(const void* rows, const int* dest, const void* dout, float* dw, long long tokens, int K,
+                       int dim, void* stream);
+
+// Flash attention (attention_fwd_sm100.cu / attention_bwd_sm100.cu); token-major [B*S, heads*dim] views.
+int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int Hq,
+                 int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv, long long ldo, float scale,
+                 int causal, int window, const int* q_pos, const int* q_seg, const int* kv_seg, void* stream);
+int tpb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                 float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq, int Sk, int Hq, int Hkv,
+                 int dqk, int dvd, long long ldq, long long ldk, long long ldv, long long lddo, long long lddq,
+                 long long lddk, long long lddv, float scale, int causal, int window, const int* q_pos,
+                 const int* q_seg, const int* kv_seg, void* stream);
 
 #ifdef __cplusplus
 }

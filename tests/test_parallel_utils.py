@@ -1,0 +1,143 @@
+"""Mesh geometry, shard plan, zig-zag permutations, safetensors layout."""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+
+from torchprime_b200.checkpoint import safetensors_io as sio
+from torchprime_b200.config import compose, to_container
+from torchprime_b200.dist.mesh import Mesh, get_mesh, is_1d_sharding, maybe_get_custom_mesh
+from torchprime_b200.models.model_utils import extract_model_size_from_model_name, initialize_model_class
+from torchprime_b200.parallel.shard_plan import ShardPlan, ShardedModule, shard_model_from_config
+from torchprime_b200.utils.parallelism_utils import (LoadBalancedCausalMask, chunk_permutation, reorder_mask,
+                                                     reorder_sequence)
+
+
+def test_reorder_golden_and_roundtrip():
+  x = torch.arange(8)[None]
+  y = reorder_sequence(x, cp_size=2, seq_dim=1)
+  assert y.tolist() == [[0, 1, 6, 7, 2, 3, 4, 5]]
+  assert reorder_sequence(y, cp_size=2, seq_dim=1, to_contiguous=True).tolist() == x.tolist()
+  for cp in (2, 4, 8):
+    t = torch.randn(2, 16 * cp, 3)
+    back = reorder_sequence(reorder_sequence(t, cp, 1), cp, 1, to_contiguous=True)
+    assert torch.equal(back, t)
+  assert chunk_permutation(2, True) == [0, 2, 3, 1]
+  with pytest.raises(ValueError, match="multiple of 2"):
+    reorder_sequence(x, cp_size=3, seq_dim=1)
+  with pytest.raises(ValueError, match="not a multiple"):
+    reorder_sequence(torch.arange(6)[None], cp_size=2, seq_dim=1)
+  assert reorder_mask(np.arange(8), 2, 0).tolist() == [0, 1, 6, 7, 2, 3, 4, 5]
+  m = LoadBalancedCausalMask((8, 8), cp_size=2)
+  assert m.q_sequence.tolist() == [0, 1, 6, 7, 2, 3, 4, 5]
+  assert m.as_array()[2].tolist() == [True] * 7 + [False]
+  assert m == LoadBalancedCausalMask((8, 8), cp_size=2) and hash(m) == hash(LoadBalancedCausalMask((8, 8), cp_size=2))
+
+
+def test_mesh_geometry_and_groups():
+  shape = {"data": 1, "fsdp": 4, "tensor": 2, "expert": 1, "context": 1}
+  m = Mesh(shape, rank=5, world_size=8)
+  assert m.coords["fsdp"] == 2 and m.coords["tensor"] == 1
+  assert m.ranks_in_group("fsdp") == [1, 3, 5, 7] and m.ranks_in_group("tensor") == [4, 5]
+  assert m.index(("data", "fsdp")) == 2 and m.size(("fsdp", "tensor")) == 8
+  for r in range(8):
+    assert m.rank_of(m.coords_of(r)) == r
+  f = Mesh({"data": 1, "fsdp": 8, "tensor": 1, "expert": 4, "context": 1}, rank=5, world_size=8, expert_mode="folded")
+  assert f.ranks_in_group("expert") == [4, 5, 6, 7] and f.coords["expert"] == 1
+  assert is_1d_sharding((1, 4, 1, 1, 1)) and not is_1d_sharding((1, 2, 2, 1, 1))
+  assert maybe_get_custom_mesh() is None
+
+
+def test_get_mesh_checks():
+  c = compose("default", ["ici_mesh.fsdp=4"])
+  with pytest.raises(AssertionError, match="not using all the available devices"):
+    get_mesh(c, rank=0, world_size=8)
+  assert get_mesh(c, rank=0, world_size=4).size("fsdp") == 4
+  c = compose("default", ["ici_mesh.fsdp=8", "ici_mesh.expert=8", "expert_axis_mode=folded"])
+  assert get_mesh(c, rank=3, world_size=8).ranks_in_group("expert") == list(range(8))
+
+
+class _Toy(nn.Module):
+  def __init__(self):
+    super().__init__()
+    self.embed = nn.Embedding(8, 4)
+    self.layers = nn.ModuleList([nn.Linear(4, 4) for _ in range(3)])
+
+  def forward(self, x):
+    h = self.embed(x)
+    for l in self.layers:
+      h = l(h)
+    return h
+
+
+def test_shard_plan_and_functional_api():
+  toy = _Toy()
+  cfg = {"embed.weight": ["fsdp", None], "layers.*.weight": ["tensor", "fsdp"], "layers.*": [["data", "fsdp"], None]}
+  plan = ShardPlan.from_config(toy, cfg)
+  assert plan.tp_dim("layers.1.weight") == 0 and plan.tp_dim("embed.weight") is None
+  assert plan.modules["layers.2"][0] == (("data", "fsdp"), None)
+  assert plan.uses_axis("tensor") and not plan.uses_axis("context")
+  with pytest.raises(AssertionError, match="not found in the model"):
+    ShardPlan.from_config(toy, {"nope.weight": ["fsdp"]})
+  calls = []
+  out = shard_model_from_config(_Toy(), cfg, lambda t, spec: (calls.append(("out", spec)), t)[1],
+                                lambda t, spec: (calls.append(("param", spec)), t)[1])
+  assert sum(1 for c in calls if c[0] == "param") == 4
+  assert isinstance(out.layers[0], ShardedModule)
+  out(torch.tensor([[1, 2]]))
+  assert sum(1 for c in calls if c[0] == "out") == 3
+  # [i] suffix shards one element of a tuple output
+  class Tup(nn.Module):
+    def __init__(self):
+      super().__init__()
+      self.inner = nn.Linear(2, 2)
+    def forward(self, x):
+      return self.inner(x), x
+  class Wrap(nn.Module):
+    def __init__(self):
+      super().__init__()
+      self.t = Tup()
+    def forward(self, x):
+      return self.t(x)
+  seen = []
+  w = shard_model_from_config(Wrap(), {"t[0]": ["fsdp", None]}, lambda t, spec: (seen.append(t.shape), t * 2)[1])
+  a, b = w(torch.ones(1, 2))
+  assert len(seen) == 1 and torch.equal(b, torch.ones(1, 2))
+
+
+def test_real_sharding_configs_match_models():
+  for model in ("llama-tiny", "mixtral-tiny", "deepseek-tiny"):
+    cfg = compose("default", ["model=" + model])
+    m = initialize_model_class(cfg.model, device="meta")
+    ShardPlan.from_config(m, to_container(cfg.model.sharding))
+
+
+def test_group_keys_and_roundtrip(tmp_path):
+  assert sio.get_param_group_key("model.layers.12.mlp.up_proj.weight") == "layers_12"
+  assert sio.get_param_group_key("model.embed_tokens.weight") == "model"
+  assert sio.get_param_group_key("model.norm.weight") == "model"
+  assert sio.get_param_group_key("lm_head.weight") == "lm_head"
+  assert sio.get_param_group_key("module.layer1.0.conv.weight") == "layer1_0"
+  state = {"model.embed_tokens.weight": torch.randn(4, 2), "model.layers.0.a._orig_mod.weight": torch.randn(2, 2),
+           "model.layers.1.a.weight": torch.randn(2, 2).to(torch.bfloat16), "lm_head.weight": torch.randn(4, 2)}
+  sio.save_sharded_safetensors_by_layer(state, str(tmp_path))
+  files = sorted(os.listdir(tmp_path))
+  assert files == ["layers_0.safetensors", "layers_1.safetensors", "lm_head.safetensors", "model.safetensors",
+                   "model.safetensors.index.json"]
+  index = json.load(open(tmp_path / "model.safetensors.index.json"))
+  assert set(index) == {"weight_map"} and index["weight_map"]["model.layers.0.a.weight"] == "layers_0.safetensors"
+  back = sio.load_safetensors_to_state_dict(str(tmp_path))
+  assert torch.equal(back["model.layers.0.a.weight"], state["model.layers.0.a._orig_mod.weight"])
+  assert back["model.layers.1.a.weight"].dtype == torch.bfloat16
+  with pytest.raises(FileNotFoundError):
+    sio.load_safetensors_to_state_dict(str(tmp_path / "missing"))
+
+
+def test_model_size_parsing():
+  assert extract_model_size_from_model_name("llama-3.1-70b") == 70
+  assert extract_model_size_from_model_name("mixtral-8x7b") == 56
+  assert extract_model_size_from_model_name("llama-tiny") == -1

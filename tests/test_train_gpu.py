@@ -1,0 +1,69 @@
+"""End-to-end Llama training on the GPU: kernels vs the cuBLAS/SDPA/eager backend."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(backend, tmp_path, steps=4, extra=()):
+  from torchprime_b200.config import compose
+  from torchprime_b200.data.synthetic import make_synthetic_dataset
+  from torchprime_b200.models.model_utils import initialize_model_class
+  from torchprime_b200.ops import functional as ops
+  from torchprime_b200.trainer import Trainer
+  ops.set_backend(backend)
+  try:
+    cfg = compose("default", ["model=llama-3-8b", "model.num_hidden_layers=2", "model.hidden_size=512",
+                              "model.intermediate_size=1024", "model.num_attention_heads=4",
+                              "model.num_key_value_heads=2", "model.vocab_size=4096", "dataset=synthetic",
+                              "dataset.block_size=512", "task.global_batch_size=2", f"task.max_steps={steps}",
+                              "task.optimizer.type=adamw", "task.optimizer.learning_rate=1e-3", "ici_mesh.fsdp=1",
+                              "profile_start_step=-1", f"output_dir={tmp_path}/{backend}"] + list(extra))
+    m = initialize_model_class(cfg.model, device="meta")
+    data = make_synthetic_dataset(vocab_size=4096, block_size=512, num_samples=32)
+    tr = Trainer(model=m, config=cfg, train_dataset=data)
+    loader = tr._get_train_dataloader()
+    out = []
+    for _ in range(steps):
+      loss, gn = tr.train_step(tr._prepare_batch(loader.next_batch()))
+      out.append((loss.item(), gn.item()))
+    return out, tr
+  finally:
+    ops.set_backend("auto")
+
+
+def test_llama_kernels_track_torch_backend(cuda_lib, tmp_path):
+  from torchprime_b200.ops import functional as ops, kernels
+  n0 = kernels.launch_count()
+  mine, _ = _run("auto", tmp_path)
+  assert kernels.launch_count() - n0 > 50
+  assert ops.attention_impl_in_use().startswith("sm100")
+  base, _ = _run("torch", tmp_path)
+  for (la, ga), (lb, gb) in zip(mine, base):
+    assert abs(la - lb) < 0.03, (mine, base)
+    assert abs(ga - gb) / gb < 0.08, (mine, base)
+
+
+def test_train_loop_writes_metrics_and_profile(cuda_lib, tmp_path):
+  import json, os
+  from torchprime_b200.config import compose
+  from torchprime_b200.data.synthetic import make_synthetic_dataset
+  from torchprime_b200.metrics.metrics import MetricsLogger
+  from torchprime_b200.models.model_utils import initialize_model_class
+  from torchprime_b200.trainer import Trainer
+  cfg = compose("default", ["model=llama-3-8b", "model.num_hidden_layers=2", "model.hidden_size=256",
+                            "model.intermediate_size=512", "model.num_attention_heads=2",
+                            "model.num_key_value_heads=1", "model.vocab_size=1024", "dataset=synthetic",
+                            "dataset.block_size=256", "task.global_batch_size=2", "task.max_steps=8",
+                            "task.optimizer.type=adafactor", "ici_mesh.fsdp=1", "profile_start_step=2",
+                            "profile_end_step=3", f"profile_dir={tmp_path}/profile", f"output_dir={tmp_path}/out"])
+  ml = MetricsLogger()
+  m = initialize_model_class(cfg.model, device="meta")
+  tr = Trainer(model=m, config=cfg, train_dataset=make_synthetic_dataset(vocab_size=1024, block_size=256, num_samples=32))
+  tr.train_loop()
+  tr.finalize_training(ml)
+  metrics = json.load(open(tmp_path / "out" / "train_metrics.json"))
+  assert metrics["num_steps"] == 8 and metrics["step_execution_time"] > 0 and metrics["tokens_per_second"] > 0
+  assert os.path.exists(tmp_path / "out" / "train_config.json")
+  assert any(f.endswith(".json") for f in os.listdir(tmp_path / "profile"))

@@ -63,6 +63,7 @@ def _declare(L):
     "tpb_rmsnorm_fwd": [P, P, P, P, P, P, I, I, F, P],
     "tpb_rmsnorm_bwd": [P, P, P, P, P, P, P, I, I, P],
     "tpb_rope": [P, LL, I, I, I, P, P, P, I, I, I, I, P],
+    "tpb_rope_strided": [P, LL, I, I, I, I, P, P, P, I, I, I, I, P],
     "tpb_swiglu_fwd": [P, P, I, I, P],
     "tpb_swiglu_bwd": [P, P, P, I, I, P],
     "tpb_ce_fwd_bwd": [P, LL, P, P, P, I, I, P],

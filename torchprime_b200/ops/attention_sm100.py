@@ -93,13 +93,14 @@ def _eager_bwd(do, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk,
   b, sq = q.shape[0], q.shape[1]
   sk = k.shape[1]
   for i in range(b):
-    qf, kf, vf = (t[i:i + 1].detach().float().requires_grad_(True) for t in (q, k, v))
-    o = ref.attention(
-      qf, kf, vf, causal=causal, scale=scale, window=window,
-      q_segment_ids=None if q_seg is None else q_seg.view(b, sq)[i:i + 1],
-      kv_segment_ids=None if kv_seg is None else kv_seg.view(b, sk)[i:i + 1],
-      q_positions=None if q_pos is None else q_pos.view(b, sq)[i:i + 1].long())
-    gq, gk, gv = torch.autograd.grad(o, (qf, kf, vf), do[i:i + 1].float())
+    with torch.enable_grad():
+      qf, kf, vf = (t[i:i + 1].detach().float().requires_grad_(True) for t in (q, k, v))
+      o = ref.attention(
+        qf, kf, vf, causal=causal, scale=scale, window=window,
+        q_segment_ids=None if q_seg is None else q_seg.view(b, sq)[i:i + 1],
+        kv_segment_ids=None if kv_seg is None else kv_seg.view(b, sk)[i:i + 1],
+        q_positions=None if q_pos is None else q_pos.view(b, sq)[i:i + 1].long())
+      gq, gk, gv = torch.autograd.grad(o, (qf, kf, vf), do[i:i + 1].float())
     dq[i:i + 1].copy_(gq)
     dk[i:i + 1].copy_(gk)
     dv[i:i + 1].copy_(gv)

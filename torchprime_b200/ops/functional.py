@@ -145,12 +145,21 @@ class _LinearFn(torch.autograd.Function):
     return (dx, dres, None, *wgrads)
 
 
+def _gemm_friendly(x, ws) -> bool:
+  """Shapes the TMA-fed GEMM accepts: 16-byte aligned rows for every operand."""
+  n = sum(w.shape[0] for w in ws)
+  k = ws[0].shape[1]
+  return (n % 8 == 0 and k % 8 == 0 and all(w.dim() == 2 and w.is_contiguous() for w in ws)
+          and x.shape[-1] == k and x.reshape(-1, k).stride(-1) == 1 and x.reshape(-1, k).stride(0) % 8 == 0)
+
+
 def linear(x, weights, bias=None, residual=None):
   """y = x @ cat(weights)^T (+ bias) (+ residual).  ``weights`` is one tensor or a list of
   row-adjacent tensors (q/k/v or gate/up laid out back to back) which then run as
   one GEMM."""
   ws = list(weights) if isinstance(weights, (list, tuple)) else [weights]
-  if use_kernels(x, *ws) and bias is None and (len(ws) == 1 or _adjacent(ws)):
+  if (use_kernels(x, *ws) and bias is None and (len(ws) == 1 or _adjacent(ws)) and _gemm_friendly(x, ws)
+      and (residual is None or residual.dtype == x.dtype)):
     return _LinearFn.apply(x, residual, len(ws), *ws)
   if len(ws) == 1:
     y = F.linear(x, ws[0], bias)
@@ -196,7 +205,8 @@ class _LinearSwigluFn(torch.autograd.Function):
 
 def linear_swiglu(x, w_gate, w_up):
   """silu(x @ w_gate^T) * (x @ w_up^T) as one GEMM with a fused epilogue."""
-  if use_kernels(x, w_gate, w_up) and _adjacent([w_gate, w_up]) and w_gate.shape[0] % 8 == 0:
+  if (use_kernels(x, w_gate, w_up) and _adjacent([w_gate, w_up]) and w_gate.shape[0] % 8 == 0
+      and _gemm_friendly(x, [w_gate, w_up])):
     return _LinearSwigluFn.apply(x, w_gate, w_up)
   return F.silu(F.linear(x, w_gate)) * F.linear(x, w_up)
 
@@ -269,25 +279,40 @@ def add_rms_norm(x, res, w, eps):
 # --------------------------------------------------------------------------- rope
 class _RopeInplaceFn(torch.autograd.Function):
   @staticmethod
-  def forward(ctx, qkv, cos, sin, heads, dim, seq_len, pos, interleaved):
+  def forward(ctx, qkv, cos, sin, heads, dim, seq_len, pos, interleaved, col0=0, head_stride=None):
     from . import kernels as k
     q2 = qkv.view(-1, qkv.shape[-1])
-    k.rope_(q2, 0, heads, dim, cos, sin, seq_len, pos=pos, interleaved=interleaved)
+    k.rope_(q2, col0, heads, dim, cos, sin, seq_len, pos=pos, interleaved=interleaved, head_stride=head_stride)
     ctx.mark_dirty(qkv)
     ctx.save_for_backward(cos, sin, pos) if pos is not None else ctx.save_for_backward(cos, sin)
-    ctx.args = (heads, dim, seq_len, interleaved, pos is not None)
+    ctx.args = (heads, dim, seq_len, interleaved, pos is not None, col0, head_stride)
     return qkv
 
   @staticmethod
   def backward(ctx, dqkv):
     from . import kernels as k
-    heads, dim, seq_len, interleaved, has_pos = ctx.args
+    heads, dim, seq_len, interleaved, has_pos, col0, head_stride = ctx.args
     saved = ctx.saved_tensors
     pos = saved[2] if has_pos else None
     d = dqkv.contiguous().clone() if not dqkv.is_contiguous() else dqkv.clone()
-    k.rope_(d.view(-1, d.shape[-1]), 0, heads, dim, saved[0], saved[1], seq_len, pos=pos, inverse=True,
-            interleaved=interleaved)
-    return d, None, None, None, None, None, None, None
+    k.rope_(d.view(-1, d.shape[-1]), col0, heads, dim, saved[0], saved[1], seq_len, pos=pos, inverse=True,
+            interleaved=interleaved, head_stride=head_stride)
+    return d, None, None, None, None, None, None, None, None, None
+
+
+def rope_slices(x, cos_half, sin_half, heads, dim, seq_len, col0, head_stride, pos=None, interleaved=False):
+  """Rotate ``heads`` slices of width ``dim`` that start at column ``col0`` and lie ``head_stride``
+  apart in the last dimension of ``x`` [B,S,C] (the rope part of MLA heads).  In place on CUDA."""
+  if use_kernels(x):
+    return _RopeInplaceFn.apply(x, cos_half, sin_half, heads, dim, seq_len, pos, interleaved, col0, head_stride)
+  b, s, c = x.shape
+  cols = (col0 + torch.arange(heads, device=x.device)[:, None] * head_stride
+          + torch.arange(dim, device=x.device)[None, :]).reshape(-1)
+  part = x[..., cols]
+  rot = rope_inplace(part, cos_half, sin_half, heads, dim, seq_len, pos=pos, interleaved=interleaved)
+  out = x.clone()
+  out[..., cols] = rot
+  return out
 
 
 def rope_inplace(qkv, cos_half, sin_half, heads, dim, seq_len, pos=None, interleaved=False):

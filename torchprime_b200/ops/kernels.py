@@ -96,14 +96,15 @@ def rmsnorm_bwd(dy, x, w, rstd, dres=None, dw_f32=None):
   return dx.view(x.shape), dw_f32
 
 
-def rope_(x2d, col0, heads, dim, cos, sin, seq_len, pos=None, inverse=False, interleaved=False):
-  """In-place RoPE on columns [col0, col0 + heads*dim) of a [tokens, ld] bf16 matrix."""
+def rope_(x2d, col0, heads, dim, cos, sin, seq_len, pos=None, inverse=False, interleaved=False, head_stride=None):
+  """In-place RoPE on ``heads`` slices of width ``dim`` (``head_stride`` apart, default ``dim``)
+  starting at column ``col0`` of a [tokens, ld] bf16 matrix."""
   assert x2d.dim() == 2 and x2d.stride(1) == 1 and x2d.dtype == torch.bfloat16
   assert cos.dtype == torch.float32 and cos.is_contiguous() and cos.shape[-1] == dim // 2
   if pos is not None:
     assert pos.dtype == torch.int32 and pos.numel() == x2d.shape[0]
-  check(lib().tpb_rope(ptr(x2d), x2d.stride(0), col0, heads, dim, ptr(cos), ptr(sin), ptr(pos), x2d.shape[0],
-                       seq_len, int(inverse), int(interleaved), stream_ptr()), "rope")
+  check(lib().tpb_rope_strided(ptr(x2d), x2d.stride(0), col0, heads, dim, head_stride or dim, ptr(cos), ptr(sin),
+                               ptr(pos), x2d.shape[0], seq_len, int(inverse), int(interleaved), stream_ptr()), "rope")
   return x2d
 
 
