@@ -592,3 +592,64 @@ extern "C" int tpb_cast_f32_to_bf16(const float* src, void* dst, long long n, fl
   return rc(cudaGetLastError());
 }
 
+// ----------------------------------------------------------------------------
+// Allocation-free variant of the RMSNorm backward (see tpb_noalloc.h).
+// ----------------------------------------------------------------------------
+#include "tpb_noalloc.h"
+
+namespace tpb {
+// fp32 weight-gradient accumulator shared by every call on this device.  In host code this
+// name is only a handle; the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_dw_scratch[TPB_NOALLOC_MAX_DIM];
+
+constexpr int kMaxDevices = 64;
+static float* g_noalloc_dw_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the scratch array for the current device (looked up once per device).
+static float* noalloc_scratch_for_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (g_noalloc_dw_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_noalloc_dw_scratch) != cudaSuccess) return nullptr;
+    g_noalloc_dw_ptr[dev] = ptr;
+  }
+  return g_noalloc_dw_ptr[dev];
+}
+
+__global__ void noalloc_store_dw_kernel(const float* __restrict__ acc, __nv_bfloat16* __restrict__ out, int dim) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < dim; i += gridDim.x * blockDim.x)
+    out[i] = __float2bfloat16(acc[i]);
+}
+}  // namespace tpb
+
+extern "C" int tpb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                       const void* dres, void* dx, void* dw_bf16, int rows, int dim, void* stream) {
+  if (dim <= 0 || dim % 8) return -2;
+  if (dim > TPB_NOALLOC_MAX_DIM) return -6;
+  float* scratch = noalloc_scratch_for_current_device();
+  if (!scratch) return -7;
+  cudaStream_t s = STREAM(stream);
+  // the accumulator keeps the previous call's sums: clear what this call will add into
+  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(float) * dim, s);
+  if (e != cudaSuccess) return 1000 + (int)e;
+  if (rows > 0) {
+    int grid = rows < sm_count() * 4 ? rows : sm_count() * 4;
+    rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, s>>>((const uint4*)dy, (const uint4*)x, (const uint4*)w, rstd,
+                                                     (const uint4*)dres, (uint4*)dx, scratch, rows, dim / 8);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return 1000 + (int)e;
+  }
+  noalloc_store_dw_kernel<<<(dim + 255) / 256, 256, 0, s>>>(scratch, (__nv_bfloat16*)dw_bf16, dim);
+  return rc(cudaGetLastError());
+}
+
+extern "C" const char* tpb_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -2: return "dim must be a positive multiple of 8";
+    case -6: return "dim exceeds TPB_NOALLOC_MAX_DIM (8192): the built-in scratch accumulator is too small";
+    case -7: return "could not resolve the device address of the built-in scratch (cudaGetSymbolAddress failed)";
+    default: return code >= 1000 ? "CUDA launch failed (code - 1000 is the cudaError_t)" : "unknown error";
+  }
+}
