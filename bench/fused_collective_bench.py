@@ -1,0 +1,101 @@
+"""Micro-benchmark of the fused compute+collective kernels against NCCL + GEMM and their roofline.
+
+  python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 bench/fused_collective_bench.py
+
+Shapes are one Llama-3-8B decoder layer on one 8192-token sequence per GPU: the FSDP gather of the
+layer's 218 M bf16 parameters fused into the QKV projection, and the gate/up weight-gradient GEMM
+fused with its reduce-scatter.  Roofline = max(FLOPs / measured cuBLAS peak, bytes that cross NVLink /
+770 GB/s per direction).  Times are CUDA-event times, max over ranks.
+"""
+
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from torchprime_b200.dist import runtime as rt
+from torchprime_b200.dist.symm import SymmetricBuffer
+from torchprime_b200.metrics.mfu import measured_peak_tflops
+from torchprime_b200.ops import _lib, fused_collective as fc, kernels as k
+
+NVLINK_GBS = 770.0
+
+
+def timed(fn, pre=None, n=10, warm=3):
+  ts = []
+  for i in range(warm + n):
+    if pre:
+      pre()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    fn()
+    e.record()
+    torch.cuda.synchronize()
+    if i >= warm:
+      ts.append(s.elapsed_time(e))
+  ts.sort()
+  return rt.all_reduce_max_float(ts[len(ts) // 2])
+
+
+def main():
+  dev = rt.init()
+  world, rank = rt.world_size(), rt.rank()
+  peak = (measured_peak_tflops() or {}).get("bf16_tflops", 1590.0)
+  T, D, F, HQKV = 8192, 4096, 14336, 6144
+  unit = HQKV * D + D * D + 2 * F * D + F * D + 2 * D          # parameters of one decoder layer
+  shard = (unit + world * 8 - 1) // (world * 8) * 8
+  sb = SymmetricBuffer(shard, torch.bfloat16, dev)
+  sb.local.normal_(0, 0.02)
+  gathered = torch.empty(shard * world, dtype=torch.bfloat16, device=dev)
+  x = torch.randn(T, D, device=dev, dtype=torch.bfloat16)
+  out = {}
+
+  # ---- F1: all-gather fused into the QKV GEMM
+  ag = fc.AllGatherGemm(sb, shard, copiers=8)
+  t_fused = timed(lambda: ag(x, gathered, 0, HQKV, D), pre=sb.barrier)
+  def nccl_then_gemm():
+    dist.all_gather_into_tensor(gathered, sb.local)
+    k.gemm(x, gathered[:HQKV * D].view(HQKV, D))
+  t_nccl = timed(nccl_then_gemm)
+  t_gemm = timed(lambda: k.gemm(x, gathered[:HQKV * D].view(HQKV, D)))
+  flops = 2.0 * T * HQKV * D
+  link_bytes = (world - 1) * shard * 2
+  roof = max(flops / (peak * 1e12), link_bytes / (NVLINK_GBS * 1e9)) * 1e3
+  out["ag_gemm"] = {"fused_ms": t_fused, "nccl_allgather_plus_gemm_ms": t_nccl, "gemm_only_ms": t_gemm,
+                    "roofline_ms": roof, "fraction_of_roofline": roof / t_fused, "nvlink_bytes_in": link_bytes}
+
+  # ---- F2: gate/up weight gradient fused with its reduce-scatter
+  N2 = 2 * F
+  gsz = (N2 * D + world * 8 - 1) // (world * 8) * 8
+  gs = SymmetricBuffer(gsz, torch.bfloat16, dev)
+  dy = torch.randn(T, N2, device=dev, dtype=torch.bfloat16)
+  def pre_rs():
+    gs.local.zero_()
+    gs.barrier()
+  t_rs = timed(lambda: fc.gemm_rs(dy, x, a_mn=True, b_mn=True, m=N2, n=D, ldc=D, grad_shards=gs, shard_elems=gsz,
+                                  c_offset=0, alpha=1.0 / world), pre=pre_rs)
+  full = torch.empty(gsz * world, dtype=torch.bfloat16, device=dev)
+  shard_out = torch.empty(gsz, dtype=torch.bfloat16, device=dev)
+  def nccl_rs():
+    k.gemm(dy, x, a_mn=True, b_mn=True, out=full[:N2 * D].view(N2, D))
+    dist.reduce_scatter_tensor(shard_out, full, op=dist.ReduceOp.AVG)
+  t_nccl_rs = timed(nccl_rs)
+  flops2 = 2.0 * T * N2 * D
+  link2 = (world - 1) * gsz * 2
+  roof2 = max(flops2 / (peak * 1e12), link2 / (NVLINK_GBS * 1e9)) * 1e3
+  out["gemm_rs"] = {"fused_ms": t_rs, "gemm_plus_nccl_reduce_scatter_ms": t_nccl_rs, "roofline_ms": roof2,
+                    "fraction_of_roofline": roof2 / t_rs, "nvlink_bytes_out": link2}
+  torch.cuda.synchronize()
+  _lib.raise_on_device_timeout()
+  if rank == 0:
+    print(json.dumps({"world": world, "peak_tflops_used": peak, **out}))
+  rt.barrier()
+  rt.shutdown()
+
+
+if __name__ == "__main__":
+  main()

@@ -31,6 +31,7 @@ constexpr int A_BYTES = BM * BK * 2;                 // 16 KB
 constexpr int B_BYTES = BN * BK * 2;                 // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 48 KB
 constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+static_assert(6 * 32768 + 64 <= STAGES * STAGE_BYTES + 256, "copier ring must fit the GEMM shared memory");
 constexpr int GEMM_THREADS = 192;
 
 struct GemmParams {
@@ -58,6 +59,25 @@ struct GemmParams {
   const int* tile_expert;
   const int* k_offsets;
   long long c_stride;
+  // All-gather fusion: the flat buffer that contains B is sharded over ag_world GPUs.  The
+  // first ag_copiers CTAs pull every shard (peer memory, plain bulk copies) into the local
+  // gathered buffer chunk by chunk and publish one flag per chunk; the TMA producer of a GEMM
+  // CTA waits (bounded) for the chunks that hold its B tile before loading it locally.
+  int ag_copiers;
+  int ag_world;
+  const void* ag_src[8];        // shard base of every rank (symmetric memory), bf16
+  void* ag_dst;                 // local gathered buffer (ag_world * ag_shard_elems)
+  long long ag_shard_elems;
+  long long ag_chunk_elems;
+  long long ag_b_offset;        // element offset of B inside the gathered buffer
+  unsigned* ag_flags;           // [ag_world * chunks_per_shard], value = epoch when ready
+  unsigned ag_epoch;
+  // Reduce-scatter fusion (TPB_EPI_RS_BF16): the epilogue adds alpha * acc straight into the
+  // owner's bf16 gradient shard over P2P with vector red.add.
+  int rs_world;
+  void* rs_dst[8];              // gradient shard base of every rank (symmetric memory), bf16
+  long long rs_shard_elems;
+  long long rs_c_offset;        // element offset of C inside the sharded flat buffer
 };
 
 struct TileInfo {
@@ -97,6 +117,100 @@ __device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int t, int m_
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
+__device__ __forceinline__ long long ag_chunks_per_shard(const GemmParams& p) {
+  return (p.ag_shard_elems + p.ag_chunk_elems - 1) / p.ag_chunk_elems;
+}
+
+// Wait until every chunk that overlaps flat elements [lo, hi] has been published.
+__device__ __forceinline__ bool ag_wait_range(const GemmParams& p, long long lo, long long hi) {
+  const long long cps = ag_chunks_per_shard(p);
+  const long long total = p.ag_shard_elems * p.ag_world;
+  if (hi >= total) hi = total - 1;
+  long long e = lo;
+  while (e <= hi) {
+    const long long owner = e / p.ag_shard_elems;
+    const long long j = (e - owner * p.ag_shard_elems) / p.ag_chunk_elems;
+    const unsigned* f = p.ag_flags + owner * cps + j;
+    unsigned v;
+    long long t0 = 0;
+    int spins = 0;
+    while (true) {
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      if (v == p.ag_epoch) break;
+      if (++spins == 64) {
+        spins = 0;
+        if (t0 == 0) t0 = clock64();
+        else if (clock64() - t0 > kSpinBudgetCycles) { report(p.status, kTimeoutPeerFlag, 5); return false; }
+        __nanosleep(100);
+      }
+    }
+    const long long chunk_end = owner * p.ag_shard_elems + min(p.ag_shard_elems, (j + 1) * p.ag_chunk_elems);
+    e = chunk_end;
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");   // the data was written through the async proxy
+  return true;
+}
+
+// Copier CTA: one thread drives a ring of bulk copies  peer shard -> shared memory -> local
+// gathered buffer and publishes a flag per chunk.  Loads are plain (non-multicast) bulk copies.
+__device__ void ag_copier(const GemmParams& p, uint8_t* smem) {
+  constexpr int SLOTS = 6;
+  const long long chunk_bytes_max = p.ag_chunk_elems * 2;   // <= 32 KB (host checks)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SLOTS * 32768);
+  if (threadIdx.x != 0) return;
+  for (int i = 0; i < SLOTS; ++i) mbar_init(&bars[i], 1);
+  fence_barrier_init();
+  const long long cps = ag_chunks_per_shard(p);
+  const long long n_chunks = cps * p.ag_world;
+  const int G = p.ag_copiers, c = blockIdx.x;
+  const long long mine = (n_chunks - c + G - 1) / G;   // chunks c, c+G, ...
+  auto chunk_geom = [&](long long k, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, long long& id) {
+    id = c + k * G;
+    const long long owner = id / cps, j = id % cps;
+    const long long off = j * p.ag_chunk_elems;
+    const long long n = min(p.ag_chunk_elems, p.ag_shard_elems - off);
+    src = reinterpret_cast<const uint8_t*>(p.ag_src[owner]) + off * 2;
+    dst = reinterpret_cast<uint8_t*>(p.ag_dst) + (owner * p.ag_shard_elems + off) * 2;
+    bytes = (uint32_t)(n * 2);
+  };
+  auto issue_load = [&](long long k) {
+    const uint8_t* src; uint8_t* dst; uint32_t bytes; long long id;
+    chunk_geom(k, src, dst, bytes, id);
+    const int slot = (int)(k % SLOTS);
+    mbar_expect_tx(&bars[slot], bytes);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem + slot * 32768)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(&bars[slot]))
+                 : "memory");
+  };
+  auto publish = [&](long long k) {
+    const uint8_t* src; uint8_t* dst; uint32_t bytes; long long id;
+    chunk_geom(k, src, dst, bytes, id);
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence();
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p.ag_flags + id), "r"(p.ag_epoch) : "memory");
+  };
+  (void)chunk_bytes_max;
+  for (long long k = 0; k < mine && k < SLOTS; ++k) issue_load(k);
+  for (long long k = 0; k < mine; ++k) {
+    const int slot = (int)(k % SLOTS);
+    if (!mbar_wait(&bars[slot], (uint32_t)((k / SLOTS) & 1), p.status, kTimeoutTmaFull, 6)) return;
+    const uint8_t* src; uint8_t* dst; uint32_t bytes; long long id;
+    chunk_geom(k, src, dst, bytes, id);
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                 "r"(smem_u32(smem + slot * 32768)), "r"(bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    if (k >= 1) {
+      asm volatile("cp.async.bulk.wait_group 1;" ::: "memory");   // store of chunk k-1 is complete
+      publish(k - 1);
+      if (k - 1 + SLOTS < mine) issue_load(k - 1 + SLOTS);
+    }
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (mine > 0) publish(mine - 1);
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -111,6 +225,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if ((int)blockIdx.x < p.ag_copiers) {
+    ag_copier(p, smem);
+    return;
+  }
+  const int cta = (int)blockIdx.x - p.ag_copiers;
+  const int n_ctas = (int)gridDim.x - p.ag_copiers;
   const bool swiglu = p.epi == TPB_EPI_SWIGLU;
   const int tile_n_out = swiglu ? BN / 2 : BN;  // output columns covered by one tile
   const int n_logical = swiglu ? p.N / 2 : p.N;
@@ -148,11 +268,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += n_ctas) {
         const TileInfo ti = tile_info(p, t, m_tiles, n_tiles, num_kb);
         if (ti.skip) continue;
         const int m0 = ti.tm * BM, n0 = ti.tn * tile_n_out;
         const int ez = p.mode == 1 ? ti.e : 0;
+        if (p.ag_world > 0) {
+          // B rows [n0, n0 + BN) of a dense [N, ldb = K] matrix occupy one flat range
+          const long long lo = p.ag_b_offset + (long long)n0 * p.K;
+          const long long hi = p.ag_b_offset + (long long)min(p.N, n0 + BN) * p.K - 1;
+          if (!ag_wait_range(p, lo, hi)) { ok = false; break; }
+        }
         for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, p.status, kTimeoutStageFree, 1)) {
             ok = false;
@@ -198,7 +324,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t phase = 0;
       bool ok = true;
       int local = 0;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = cta; t < num_tiles && ok; t += n_ctas) {
         const TileInfo ti = tile_info(p, t, m_tiles, n_tiles, num_kb);
         if (ti.skip) continue;
         const int acc = local & 1;
@@ -236,7 +362,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ---------------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quarter this warp may access
     int local = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    for (int t = cta; t < num_tiles; t += n_ctas) {
       const TileInfo ti = tile_info(p, t, m_tiles, n_tiles, num_kb);
       if (ti.skip) continue;
       const int acc = local & 1;
@@ -310,7 +436,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int col = n0 + c * 32;
           if (!row_ok || col >= p.N) continue;
           const bool full_chunk = col + 32 <= p.N;
-          if (p.epi == TPB_EPI_F32 || p.epi == TPB_EPI_F32_ACC) {
+          if (p.epi == TPB_EPI_RS_BF16) {
+            // owner of each 8-element vector from its flat offset; 16-byte vector red over P2P
+            const long long flat0 = p.rs_c_offset + (long long)row * p.ldc + col;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              if (col + 8 * v + 8 > p.N) break;   // host guarantees N % 8 == 0
+              const long long flat = flat0 + 8 * v;
+              const long long owner = flat / p.rs_shard_elems;
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) + (flat - owner * p.rs_shard_elems);
+              const uint32_t a0 = pack_bf16(__uint_as_float(r[8 * v]) * p.alpha, __uint_as_float(r[8 * v + 1]) * p.alpha);
+              const uint32_t a1 = pack_bf16(__uint_as_float(r[8 * v + 2]) * p.alpha, __uint_as_float(r[8 * v + 3]) * p.alpha);
+              const uint32_t a2 = pack_bf16(__uint_as_float(r[8 * v + 4]) * p.alpha, __uint_as_float(r[8 * v + 5]) * p.alpha);
+              const uint32_t a3 = pack_bf16(__uint_as_float(r[8 * v + 6]) * p.alpha, __uint_as_float(r[8 * v + 7]) * p.alpha);
+              asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(a0),
+                           "r"(a1), "r"(a2), "r"(a3)
+                           : "memory");
+            }
+          } else if (p.epi == TPB_EPI_F32 || p.epi == TPB_EPI_F32_ACC) {
             float* C = reinterpret_cast<float*>(p.C) + c_off + (long long)row * p.ldc + col;
             const bool accm = p.epi == TPB_EPI_F32_ACC;
             if (full_chunk) {
@@ -409,6 +552,10 @@ struct GemmCall {
   void* c2; long long ldc2;
   int max_ctas;
   int mode; const int* tile_expert; const int* k_offsets; long long c_stride;
+  // fusion with collectives (0 / null when unused)
+  int ag_world, ag_copiers; const void* const* ag_src; void* ag_dst; long long ag_shard_elems, ag_b_offset;
+  unsigned* ag_flags; unsigned ag_epoch;
+  int rs_world; void* const* rs_dst; long long rs_shard_elems, rs_c_offset;
 };
 
 static int run_gemm(const GemmCall& g, cudaStream_t stream) {
@@ -457,14 +604,30 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.status = status_block();
   p.mode = g.mode; p.num_experts = g.E; p.tile_expert = g.tile_expert; p.k_offsets = g.k_offsets;
   p.c_stride = g.c_stride;
+  p.ag_world = g.ag_world; p.ag_copiers = g.ag_world > 0 ? g.ag_copiers : 0;
+  p.ag_dst = g.ag_dst; p.ag_shard_elems = g.ag_shard_elems; p.ag_chunk_elems = 16384; p.ag_b_offset = g.ag_b_offset;
+  p.ag_flags = g.ag_flags; p.ag_epoch = g.ag_epoch;
+  p.rs_world = g.rs_world; p.rs_shard_elems = g.rs_shard_elems; p.rs_c_offset = g.rs_c_offset;
+  for (int i = 0; i < 8; ++i) {
+    p.ag_src[i] = (g.ag_world > 0 && i < g.ag_world) ? g.ag_src[i] : nullptr;
+    p.rs_dst[i] = (g.rs_world > 0 && i < g.rs_world) ? g.rs_dst[i] : nullptr;
+  }
+  if (g.ag_world > 0) {
+    if (g.ag_world > 8 || g.b_mn || g.mode != 0) return -2;
+    if (g.ldb != g.K || (g.ag_shard_elems % 8) || p.ag_copiers < 1 || p.ag_copiers >= sm_count()) return -2;
+  }
+  if (g.epi == TPB_EPI_RS_BF16) {
+    if (g.rs_world < 1 || g.rs_world > 8 || (g.N % 8) || (g.ldc % 8) || (g.rs_shard_elems % 8) || (g.rs_c_offset % 8))
+      return -2;
+  }
   const int n_logical = swiglu ? g.N / 2 : g.N;
   const int tile_n = swiglu ? BN / 2 : BN;
   const int m_tiles = (g.M + BM - 1) / BM, n_tiles = (n_logical + tile_n - 1) / tile_n;
   p.group_m = m_tiles < 16 ? m_tiles : 16;
   long long tiles = (long long)m_tiles * n_tiles * (g.mode == 2 ? g.E : 1);
-  int cap = sm_count();
+  int cap = sm_count() - p.ag_copiers;
   if (g.max_ctas > 0 && g.max_ctas < cap) cap = g.max_ctas;
-  const int grid = tiles > cap ? cap : (int)tiles;
+  const int grid = (tiles > cap ? cap : (int)tiles) + p.ag_copiers;
   cudaError_t e;
   if (!g.a_mn && !g.b_mn)      e = launch_gemm<false, false>(ta, tb, tb2, p, grid, stream);
   else if (!g.a_mn && g.b_mn)  e = launch_gemm<false, true>(ta, tb, tb2, p, grid, stream);
@@ -506,5 +669,43 @@ extern "C" int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B
   g.a_mn = a_mn; g.b_mn = b_mn; g.epi = epi; g.alpha = alpha;
   g.aux = nullptr; g.ldaux = 0; g.c2 = c2; g.ldc2 = ldc2; g.max_ctas = 0;
   g.mode = mode; g.tile_expert = tile_expert; g.k_offsets = k_offsets; g.c_stride = c_stride;
+  return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
+}
+
+
+// C = A * B^T where the flat bf16 buffer holding B is sharded over `world` GPUs: shard_ptrs[r] is
+// rank r's shard (peer-mapped symmetric memory), `gathered` the local buffer that receives all
+// shards (world * shard_elems elements), B starts b_offset elements into it and is a dense
+// row-major [N, K] matrix.  `flags` has world * ceil(shard_elems / 16384) entries (local memory,
+// zero-initialised once); pass a fresh non-zero `epoch` per call.  The whole buffer is gathered.
+extern "C" int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int epi,
+                                const void* aux, long long ldaux, void* c2, long long ldc2,
+                                const void* const* shard_ptrs, int world, long long shard_elems, void* gathered,
+                                long long b_offset, unsigned* flags, unsigned epoch, int copiers, void* stream_) {
+  GemmCall g{};
+  g.A = A; g.B = reinterpret_cast<const __nv_bfloat16*>(gathered) + b_offset; g.B2 = nullptr; g.C = C;
+  g.M = M; g.N = N; g.K = K; g.E = 1;
+  g.lda = lda; g.ldb = K; g.b_expert_stride = 0; g.ldc = ldc;
+  g.a_mn = 0; g.b_mn = 0; g.epi = epi; g.alpha = 1.f;
+  g.aux = aux; g.ldaux = ldaux; g.c2 = c2; g.ldc2 = ldc2; g.max_ctas = 0; g.mode = 0;
+  g.ag_world = world; g.ag_copiers = copiers; g.ag_src = shard_ptrs; g.ag_dst = gathered;
+  g.ag_shard_elems = shard_elems; g.ag_b_offset = b_offset; g.ag_flags = flags; g.ag_epoch = epoch;
+  return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
+}
+
+// C[M,N] = alpha * A * B^T reduced over ranks into the owners' bf16 shards: element (row, col) of C
+// has flat index c_offset + row * ldc + col in a buffer sharded `shard_elems` per rank;
+// shard_ptrs[r] is rank r's (peer-mapped) shard.  Shards must be zeroed (and all ranks past a
+// barrier) before the first contributing kernel, and a barrier must follow the last one.
+extern "C" int tpb_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                                long long ldc, int a_mn, int b_mn, float alpha, void* const* shard_ptrs, int world,
+                                long long shard_elems, long long c_offset, void* stream_) {
+  GemmCall g{};
+  g.A = A; g.B = B; g.B2 = nullptr; g.C = shard_ptrs[0];
+  g.M = M; g.N = N; g.K = K; g.E = 1;
+  g.lda = lda; g.ldb = ldb; g.b_expert_stride = 0; g.ldc = ldc;
+  g.a_mn = a_mn; g.b_mn = b_mn; g.epi = TPB_EPI_RS_BF16; g.alpha = alpha;
+  g.mode = 0;
+  g.rs_world = world; g.rs_dst = shard_ptrs; g.rs_shard_elems = shard_elems; g.rs_c_offset = c_offset;
   return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
 }

@@ -16,6 +16,7 @@ enum {
   TPB_EPI_BF16_ACC = 3,  // C(bf16) = C + alpha * acc
   TPB_EPI_BF16_RES = 4,  // C(bf16) = aux + alpha * acc   (residual add)
   TPB_EPI_SWIGLU = 5,    // B = [gate; up] rows, C[M, N/2] = silu(g) * u, optional c2[M, N] = [g | u]
+  TPB_EPI_RS_BF16 = 6,   // reduce-scatter: red.add alpha * acc into the owner's bf16 shard over P2P
 };
 
 // Status block: {code, site, block, thread}; code 0 = no kernel ever timed out.
@@ -89,6 +90,16 @@ int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B2, void* C,
                           long long lda, long long ldb, long long b_expert_stride, long long ldc, int a_mn, int b_mn,
                           int epi, float alpha, void* c2, long long ldc2, int mode, const int* tile_expert,
                           const int* k_offsets, long long c_stride, void* stream);
+
+// GEMM fused with the all-gather of the (flat, sharded) buffer that holds B, and GEMM fused with the
+// reduce-scatter of C into the owners' shards; see the comments at the definitions in gemm_sm100.cu.
+int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int epi,
+                     const void* aux, long long ldaux, void* c2, long long ldc2, const void* const* shard_ptrs,
+                     int world, long long shard_elems, void* gathered, long long b_offset, unsigned* flags,
+                     unsigned epoch, int copiers, void* stream);
+int tpb_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, long long ldc,
+                     int a_mn, int b_mn, float alpha, void* const* shard_ptrs, int world, long long shard_elems,
+                     long long c_offset, void* stream);
 
 // Router: one warp per token.  mode 0 softmax-top-k(-renormalise); mode 1 sigmoid + bias with
 // group-limited selection.  w_out [T,K] fp32, idx_out [T,K] int32, scores_out [T,E] fp32 (optional).

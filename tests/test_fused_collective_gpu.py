@@ -1,0 +1,86 @@
+"""GEMM fused with all-gather / reduce-scatter over NVLink peer memory (needs >= 2 GPUs)."""
+
+import os
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, results):
+  os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                     "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+  sys.path.insert(0, ROOT)
+  import torch.distributed as dist
+  from torchprime_b200.dist import runtime as rt
+  from torchprime_b200.dist.symm import SymmetricBuffer
+  from torchprime_b200.ops import _lib, fused_collective as fc, kernels as k
+  dev = rt.init()
+  try:
+    torch.manual_seed(0)
+    N, K, M = 1536, 512, 640
+    extra = 4096 + 8 * 13                       # other tensors of the "unit" after the weight
+    total = N * K + extra
+    shard = (total + world * 8 - 1) // (world * 8) * 8
+    full = torch.zeros(shard * world, dtype=torch.bfloat16, device=dev)
+    full[:total] = (torch.randn(total, device=dev) * 0.05).to(torch.bfloat16)   # same on every rank (seed)
+    sb = SymmetricBuffer(shard, torch.bfloat16, dev)
+    sb.local.copy_(full[rank * shard:(rank + 1) * shard])
+    torch.manual_seed(100 + rank)
+    x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+    gathered = torch.empty(shard * world, dtype=torch.bfloat16, device=dev)
+    ag = fc.AllGatherGemm(sb, shard, copiers=4)
+    for it in range(2):                          # twice: epochs, reuse of flags
+      gathered.zero_()
+      sb.barrier()
+      y = ag(x, gathered, 0, N, K)
+      torch.cuda.synchronize()
+      sb.barrier()
+      want = x.float() @ full[:N * K].view(N, K).float().t()
+      err = ((y.float() - want).norm() / want.norm()).item()
+      assert err < 1e-2, f"ag_gemm rel err {err}"
+      assert torch.equal(gathered, full), "gathered buffer differs from the concatenated shards"
+    # ---- reduce-scatter fused into a wgrad-layout GEMM
+    T, Nw, Kw = 768, 512, 256
+    c_off = 8 * 5
+    tot2 = c_off + Nw * Kw + 64
+    shard2 = (tot2 + world * 8 - 1) // (world * 8) * 8
+    gs = SymmetricBuffer(shard2, torch.bfloat16, dev)
+    dy = torch.randn(T, Nw, device=dev, dtype=torch.bfloat16)
+    xx = torch.randn(T, Kw, device=dev, dtype=torch.bfloat16)
+    part = (dy.float().t() @ xx.float()) / world
+    dist.all_reduce(part)
+    for it in range(2):
+      gs.local.zero_()
+      gs.barrier()
+      fc.gemm_rs(dy, xx, a_mn=True, b_mn=True, m=Nw, n=Kw, ldc=Kw, grad_shards=gs, shard_elems=shard2,
+                 c_offset=c_off, alpha=1.0 / world)
+      torch.cuda.synchronize()
+      gs.barrier()
+      torch.cuda.synchronize()
+      flat = torch.zeros(shard2 * world, dtype=torch.float32, device=dev)
+      flat[c_off:c_off + Nw * Kw] = part.reshape(-1)
+      mine = flat[rank * shard2:(rank + 1) * shard2]
+      err = ((gs.local.float() - mine).norm() / (mine.norm() + 1e-9)).item()
+      assert err < 2e-2, f"gemm_rs rel err {err}"
+    _lib.raise_on_device_timeout()
+    results[rank] = "ok"
+  except Exception as e:  # noqa: BLE001
+    import traceback
+    results[rank] = "".join(traceback.format_exception(e))
+  finally:
+    rt.shutdown()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_ag_gemm_and_gemm_rs_two_gpus(cuda_lib):
+  import torch.multiprocessing as mp
+  world = 2
+  mgr = mp.Manager()
+  results = mgr.dict()
+  mp.spawn(_worker, args=(world, 29641, results), nprocs=world, join=True)
+  assert all(results.get(r) == "ok" for r in range(world)), dict(results)

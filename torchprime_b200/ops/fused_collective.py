@@ -1,0 +1,73 @@
+"""GEMMs fused with their collective over NVLink peer memory.
+
+``ag_gemm``: ``y = x @ W^T`` where the flat buffer that contains ``W`` is sharded over the ranks of a
+group (FSDP parameter shards, or a row-sharded activation/weight for tensor parallelism).  A few
+copier CTAs of the same kernel pull every shard from its owner (plain bulk copies from peer memory,
+no multicast) into the local gathered buffer and publish per-chunk flags; the GEMM CTAs load their
+B tiles locally as soon as the chunks they need have landed.  After the call the whole buffer is
+gathered, so the other weights of the same FSDP unit are ready too.
+
+``gemm_rs``: ``dW = dY^T X`` (or any GEMM) whose epilogue adds ``alpha * tile`` directly into the
+owning rank's bf16 gradient shard with 16-byte ``red.add`` over P2P, replacing the separate
+reduce-scatter.  Shards must be zero and all ranks synchronised before the first contribution.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_uint, c_void_p
+
+import torch
+
+from . import _lib
+from ._lib import check, lib, ptr, stream_ptr
+
+P, I, LL, FL, U = c_void_p, c_int, c_longlong, c_float, c_uint
+_lib.register_signature("tpb_ag_gemm_bf16", [P, P, I, I, I, LL, LL, I, P, LL, P, LL, P, I, LL, P, LL, P, U, I, P])
+_lib.register_signature("tpb_gemm_rs_bf16", [P, P, I, I, I, LL, LL, LL, I, I, FL, P, I, LL, LL, P])
+
+CHUNK_ELEMS = 16384
+
+
+def num_flags(world: int, shard_elems: int) -> int:
+  return world * ((shard_elems + CHUNK_ELEMS - 1) // CHUNK_ELEMS)
+
+
+class AllGatherGemm:
+  """State for repeated fused all-gather + GEMM calls on one sharded flat buffer."""
+
+  def __init__(self, shard_buffer, shard_elems: int, copiers: int = 8):
+    self.sb = shard_buffer                     # dist.symm.SymmetricBuffer holding this rank's shard
+    self.world = shard_buffer.world
+    self.shard_elems = shard_elems
+    self.copiers = copiers
+    dev = shard_buffer.local.device
+    self.flags = torch.zeros(num_flags(self.world, shard_elems), dtype=torch.int32, device=dev)
+    self.epoch = 0
+
+  def __call__(self, x2d, gathered, b_offset: int, n: int, k: int, shard_offset: int = 0, out=None,
+               epi=_lib.EPI_BF16, aux=None, c2=None):
+    """out = x2d @ B^T with B = gathered[b_offset : b_offset + n*k].view(n, k); gathers every rank's
+    ``shard_elems`` elements (starting ``shard_offset`` elements into its symmetric buffer)."""
+    m = x2d.shape[0]
+    self.epoch += 1
+    if out is None:
+      out = torch.empty(m, n // 2 if epi == _lib.EPI_SWIGLU else n, dtype=torch.bfloat16, device=x2d.device)
+    table = self.sb.ptr_table(shard_offset)
+    rc = lib().tpb_ag_gemm_bf16(ptr(x2d), ptr(out), m, n, k, x2d.stride(0), out.stride(0), epi, ptr(aux),
+                                aux.stride(0) if aux is not None else 0, ptr(c2), c2.stride(0) if c2 is not None else 0,
+                                table, self.world, self.shard_elems, ptr(gathered), b_offset, ptr(self.flags),
+                                self.epoch, self.copiers, stream_ptr())
+    check(rc, f"ag_gemm M={m} N={n} K={k} world={self.world}")
+    return out
+
+
+def gemm_rs(a, b, *, a_mn, b_mn, m, n, ldc, grad_shards, shard_elems: int, c_offset: int, alpha: float,
+            shard_offset: int = 0):
+  """Adds ``alpha * (A @ B^T)`` ([m, n], row pitch ``ldc`` inside the flat sharded buffer at
+  ``c_offset``) into the owners' shards.  ``grad_shards`` is the SymmetricBuffer of gradient shards."""
+  k = a.shape[0] if a_mn else a.shape[1]
+  table = grad_shards.ptr_table(shard_offset)
+  rc = lib().tpb_gemm_rs_bf16(ptr(a), ptr(b), m, n, k, a.stride(0), b.stride(0), ldc, int(a_mn), int(b_mn),
+                              float(alpha), table, grad_shards.world, shard_elems, c_offset, stream_ptr())
+  check(rc, f"gemm_rs M={m} N={n} K={k} world={grad_shards.world}")
