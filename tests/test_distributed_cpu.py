@@ -1,0 +1,139 @@
+"""Multi-rank behaviour on CPU (gloo): FSDP, tensor-, context- and expert-parallel runs must
+reproduce the single-rank loss / gradient-norm trajectory; checkpoints round-trip; resume works."""
+
+import os
+import sys
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _train_worker(rank, world, port, overrides, steps, out, extra_action):
+  os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
+                     "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port)})
+  sys.path.insert(0, ROOT)
+  torch.set_num_threads(1)
+  import torch.distributed as dist
+  from torchprime_b200.config import compose
+  from torchprime_b200.data.synthetic import make_synthetic_dataset
+  from torchprime_b200.dist import runtime as rt
+  from torchprime_b200.models.model_utils import initialize_model_class
+  from torchprime_b200.trainer import Trainer
+  try:
+    rt.init(device="cpu")
+    cfg = compose("default", ["dataset=synthetic", "task.optimizer.type=adamw", "task.optimizer.learning_rate=1e-3",
+                              "profile_start_step=-1", "+engine.cpu_dtype=float32", f"task.max_steps={steps}"]
+                  + overrides)
+    torch.manual_seed(0)
+    model = initialize_model_class(cfg.model, device="meta")
+    data = make_synthetic_dataset(vocab_size=cfg.model.vocab_size, block_size=cfg.dataset.block_size, num_samples=64)
+    tr = Trainer(model=model, config=cfg, train_dataset=data)
+    loader = tr._get_train_dataloader()
+    if tr.start_step:
+      loader.load_state_dict({"cursor": tr.start_step})
+    traj = []
+    for step in range(tr.start_step, steps):
+      loss, gn = tr.train_step(tr._prepare_batch(loader.next_batch()))
+      l = loss.detach().clone().float()
+      if dist.is_initialized():
+        dist.all_reduce(l)
+        l /= world
+      traj.append((l.item(), gn.item()))
+      if extra_action and extra_action.startswith("save_at_2:") and step + 1 == 2:
+        from torchprime_b200.checkpoint import train_state
+        tr._loader = loader
+        train_state.save(extra_action[10:], tr, 2)
+    result = {"traj": traj}
+    if extra_action == "state_dict":
+      sd = tr.engine.full_state_dict()
+      result["norm"] = {k: v.float().norm().item() for k, v in sd.items()}
+    if rank == 0:
+      out.update(result)
+    rt.barrier()
+  except Exception as e:  # noqa: BLE001
+    import traceback
+    out["error"] = "".join(traceback.format_exception(e))
+  finally:
+    rt.shutdown()
+
+
+_PORT = [29700]
+
+
+def run(world, overrides, steps=3, extra_action=None):
+  _PORT[0] += 1
+  mgr = mp.Manager()
+  out = mgr.dict()
+  if world == 1:
+    _train_worker(0, 1, _PORT[0], overrides, steps, out, extra_action)
+  else:
+    mp.spawn(_train_worker, args=(world, _PORT[0], overrides, steps, out, extra_action), nprocs=world, join=True)
+  assert "error" not in out, out["error"]
+  return dict(out)
+
+
+def close(a, b, tol=2e-4):
+  for (la, ga), (lb, gb) in zip(a, b):
+    assert abs(la - lb) < tol * max(1, abs(lb)), (a, b)
+    assert abs(ga - gb) < 5 * tol * max(1, abs(gb)), (a, b)
+
+
+LLAMA = ["model=llama-tiny", "dataset.block_size=64", "task.global_batch_size=4"]
+
+
+@pytest.fixture(scope="module")
+def llama_single():
+  return run(1, LLAMA + ["ici_mesh.fsdp=1"])["traj"]
+
+
+def test_fsdp2_matches_single(llama_single):
+  close(run(2, LLAMA + ["ici_mesh.fsdp=2"])["traj"], llama_single)
+
+
+def test_data2_matches_single(llama_single):
+  close(run(2, LLAMA + ["ici_mesh.fsdp=1", "ici_mesh.data=2"])["traj"], llama_single)
+
+
+def test_tensor2_matches_single(llama_single):
+  close(run(2, LLAMA + ["ici_mesh.fsdp=1", "ici_mesh.tensor=2", "model/sharding=llama-fsdp-tp"])["traj"], llama_single)
+
+
+@pytest.mark.parametrize("lb", [False, True])
+def test_context2_matches_single(llama_single, lb):
+  ov = LLAMA + ["ici_mesh.fsdp=1", "ici_mesh.context=2", "+model.context=2", f"+model.load_balance_cp={str(lb).lower()}",
+                "model.attention_kernel=splash_attention", "model/sharding=llama-fsdp-tp-cp"]
+  close(run(2, ov)["traj"], llama_single)
+
+
+def test_adafactor_sharded_matches_single():
+  base = LLAMA + ["task.optimizer.type=adafactor"]
+  close(run(2, base + ["ici_mesh.fsdp=2"])["traj"], run(1, base + ["ici_mesh.fsdp=1"])["traj"], tol=5e-4)
+
+
+MIX = ["model=mixtral-tiny", "dataset.block_size=64", "task.global_batch_size=4", "model.moe_implementation=gmm"]
+
+
+def test_mixtral_expert_parallel_folded_matches_single():
+  single = run(1, MIX + ["ici_mesh.fsdp=1"])["traj"]
+  close(run(2, MIX + ["ici_mesh.fsdp=2"])["traj"], single)
+  ep = run(2, MIX + ["ici_mesh.fsdp=2", "ici_mesh.expert=2", "expert_axis_mode=folded",
+                     "model/sharding=mixtral-fsdp-ep"])["traj"]
+  close(ep, single)
+
+
+def test_resume_from_training_state(tmp_path):
+  ov = LLAMA + ["ici_mesh.fsdp=2"]
+  full = run(2, ov, steps=4, extra_action=f"save_at_2:{tmp_path}/ckpt")["traj"]
+  resumed = run(2, ov + [f"engine.resume_from={tmp_path}/ckpt"], steps=4)["traj"]
+  close(resumed, full[2:], tol=1e-5)
+
+
+def test_full_state_dict_gathers_all_parameters():
+  one = run(1, LLAMA + ["ici_mesh.fsdp=1"], steps=1, extra_action="state_dict")["norm"]
+  two = run(2, LLAMA + ["ici_mesh.fsdp=2"], steps=1, extra_action="state_dict")["norm"]
+  assert one.keys() == two.keys() and "model.layers.1.mlp.down_proj.weight" in one
+  for k in one:
+    assert abs(one[k] - two[k]) < 1e-4 * max(1.0, one[k]), k

@@ -95,6 +95,7 @@ class DeepseekV3MoE(nn.Module):
     self.grouped = GroupedMoEWeights(config.n_routed_experts, config.hidden_size, config.moe_intermediate_size)
     self.shared_experts = DeepseekV3MLP(config, intermediate_size=config.moe_intermediate_size * config.n_shared_experts)
     self.use_gmm = bool(config.get("use_gmm_kernel_for_moe", True))
+    self.num_experts = config.n_routed_experts
     self.ep = None
 
   def forward(self, hidden_states, residual=None):
@@ -247,6 +248,10 @@ class DeepseekV3ForCausalLM(BaseCausalLM):
     if isinstance(module, (GroupedMoEWeights, DeepseekV3TopkRouter)):
       return "normal"
     return None
+
+  def tp_sliceable(self, name: str) -> bool:
+    """The MLA projections and the MoE block are not tensor-parallel in this implementation."""
+    return False
 
   def convert_loaded_state_dict(self, state: dict) -> dict:
     """HF checkpoints store one Linear triple per expert; fold them into the grouped tensors."""

@@ -22,6 +22,7 @@ import torch.nn as nn
 
 from ..ops import functional as ops
 from ..ops import reference as ref
+from ..parallel.collectives import copy_to_tp, reduce_from_tp
 from ..utils.profiling import trace_scope
 from . import rope
 from .base import BaseCausalLM
@@ -46,9 +47,15 @@ class LlamaMLP(nn.Module):
     self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
     self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
     assert config.get("hidden_act", "silu") == "silu", "only SiLU-gated MLPs are implemented"
+    self.tp_group = None   # set by the engine when the tensor axis is > 1 (gate/up column-, down row-parallel)
 
   def forward(self, x, residual=None):
     with trace_scope("LlamaMLP"):
+      if self.tp_group is not None:
+        x = copy_to_tp(x, self.tp_group)
+        act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight)
+        y = reduce_from_tp(ops.linear(act, self.down_proj.weight), self.tp_group)
+        return y if residual is None else y + residual
       act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight)
       return ops.linear(act, self.down_proj.weight, residual=residual)
 
@@ -68,11 +75,16 @@ class LlamaAttention(nn.Module):
     self.v_proj = nn.Linear(self.hidden_size, self.num_key_value_heads * self.head_dim, bias=bias)
     self.o_proj = nn.Linear(self.num_heads * self.head_dim, self.hidden_size, bias=bias)
     self.attention_kernel = config.get("attention_kernel", None)
+    self.tp_group = None   # set by the engine: q/k/v column-parallel (heads split), o row-parallel
 
   def forward(self, x, rope_cos, rope_sin, residual=None, position_ids=None, segment_ids=None, cp=None):
     with trace_scope("LlamaAttention"):
       b, s, _ = x.shape
-      hq, hkv, d = self.num_heads, self.num_key_value_heads, self.head_dim
+      d = self.head_dim
+      # local head counts follow the (possibly tensor-parallel sliced) weights
+      hq, hkv = self.q_proj.weight.shape[0] // d, self.k_proj.weight.shape[0] // d
+      if self.tp_group is not None:
+        x = copy_to_tp(x, self.tp_group)
       bias = None
       if self.q_proj.bias is not None:
         bias = torch.cat([self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
@@ -88,6 +100,11 @@ class LlamaAttention(nn.Module):
       else:
         o = ops.attention(q, k, v, causal=True, q_segment_ids=segment_ids)
       o = o.reshape(b, s, hq * d)
+      if self.tp_group is not None:
+        out = reduce_from_tp(ops.linear(o, self.o_proj.weight), self.tp_group)
+        if self.o_proj.bias is not None:
+          out = out + self.o_proj.bias
+        return out if residual is None else out + residual
       if self.o_proj.bias is not None:
         out = ops.linear(o, self.o_proj.weight, bias=self.o_proj.bias)
         return out if residual is None else out + residual
@@ -124,18 +141,32 @@ class CausalLMHead(nn.Module):
     self.norm = norm
     self.lm_head = lm_head
     self.vocab_size = vocab_size
+    self.loss_group = None   # context-parallel group: the token count is taken over the whole sequence
+
+  def _valid_count(self, targets):
+    """Tokens that count towards the loss.  Under context parallelism the per-rank average of
+    this value over the group is used, so that the mean of the ranks' losses is the global mean."""
+    if self.loss_group is None:
+      return None
+    import torch.distributed as dist
+    n = (targets >= 0).sum().float()
+    dist.all_reduce(n, group=self.loss_group)
+    return (n / dist.get_world_size(self.loss_group)).clamp(min=1)
 
   def forward(self, hidden, targets=None, want_logits=True):
     """targets are already shifted (position t holds token t+1, -100 = ignore)."""
     with trace_scope("CausalLMHead"):
       h = self.norm(hidden)
+      n_valid = self._valid_count(targets) if targets is not None else None
       if targets is not None and not want_logits:
-        return None, ops.linear_cross_entropy(h, self.lm_head.weight, targets)
+        return None, ops.linear_cross_entropy(h, self.lm_head.weight, targets, n_valid=n_valid)
       logits = ops.linear(h, self.lm_head.weight).float()
       loss = None
       if targets is not None:
-        loss = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1),
-                                                 ignore_index=ref.IGNORE_INDEX)
+        flat = torch.nn.functional.cross_entropy(logits.view(-1, logits.shape[-1]), targets.reshape(-1),
+                                                 ignore_index=ref.IGNORE_INDEX,
+                                                 reduction="mean" if n_valid is None else "sum")
+        loss = flat if n_valid is None else flat / n_valid
       return logits, loss
 
 

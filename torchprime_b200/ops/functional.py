@@ -439,13 +439,14 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
   dgrad / wgrad GEMMs."""
 
   @staticmethod
-  def forward(ctx, h, w, targets, chunk_rows):
+  def forward(ctx, h, w, targets, chunk_rows, n_valid):
     from . import kernels as k
     h2 = h.reshape(-1, h.shape[-1])
     tg = targets.reshape(-1).contiguous()
     rows, vocab = h2.shape[0], w.shape[0]
-    n_valid = (tg >= 0).sum().clamp(min=1).float()
-    scale = (1.0 / n_valid).reshape(1)
+    if n_valid is None:
+      n_valid = (tg >= 0).sum().clamp(min=1).float()
+    scale = (1.0 / n_valid.float()).reshape(1)
     loss_sum = torch.zeros(1, dtype=torch.float32, device=h.device)
     need_dh = ctx.needs_input_grad[0]
     need_dw = ctx.needs_input_grad[1]
@@ -476,11 +477,16 @@ class _LinearCrossEntropyFn(torch.autograd.Function):
     dh, dw_local = ctx.saved_tensors
     gh = (dh * dloss.to(dh.dtype)).view(ctx.h_shape) if dh is not None else None
     gw = (dw_local * dloss).to(torch.bfloat16) if dw_local is not None else None
-    return gh, gw, None, None
+    return gh, gw, None, None, None
 
 
-def linear_cross_entropy(h, w, targets, chunk_rows: int = 2048):
-  """mean CE of ``h @ w^T`` against already shifted ``targets`` (-100 ignored)."""
-  if use_kernels(h, w) and w.shape[0] % 8 == 0:
-    return _LinearCrossEntropyFn.apply(h, w, targets, chunk_rows)
-  return ref.linear_cross_entropy(h, w, targets)
+def linear_cross_entropy(h, w, targets, chunk_rows: int = 2048, n_valid=None):
+  """CE of ``h @ w^T`` against already shifted ``targets`` (-100 ignored), summed and divided by
+  ``n_valid`` (default: the number of valid targets, i.e. the mean)."""
+  if use_kernels(h, w) and w.shape[0] % 8 == 0 and h.shape[-1] % 8 == 0:
+    return _LinearCrossEntropyFn.apply(h, w, targets, chunk_rows, n_valid)
+  if n_valid is None:
+    return ref.linear_cross_entropy(h, w, targets)
+  logits = F.linear(h, w).float()
+  return F.cross_entropy(logits.reshape(-1, logits.shape[-1]), targets.reshape(-1), ignore_index=ref.IGNORE_INDEX,
+                         reduction="sum") / n_valid

@@ -53,6 +53,9 @@ class _ParamSlot:
   full_shape: torch.Size | None = None
   owner: nn.Module | None = None
   attr: str = ""
+  ep_dim: int | None = None
+  local: bool = False        # expert-parallel slice owned by this rank only (not gathered)
+  local_offset: int = 0      # offset inside the engine-wide local region
 
 
 @dataclass
@@ -93,6 +96,13 @@ class FSDPEngine:
     self.tp = mesh.size("tensor") if mesh is not None else 1
     self.tp_rank = mesh.index("tensor") if mesh is not None else 0
     self.fsdp_group = mesh.group("fsdp") if mesh is not None else None
+    self.ep = mesh.size("expert") if mesh is not None else 1
+    self.ep_rank = mesh.index("expert") if mesh is not None else 0
+    self.ep_folded = mesh is not None and mesh.expert_mode == "folded"
+    if self.ep > 1 and self.ep_folded:
+      assert self.ep == mesh.size(("data", "fsdp")), (
+        "a folded expert axis must span all data x fsdp ranks (expert == data * fsdp)")
+    self.local_total = 0
     self.replica_axes = ("data", "context")
     self.replica_group = mesh.group(self.replica_axes) if mesh is not None else None
     self.replica_size = mesh.size(self.replica_axes) if mesh is not None else 1
@@ -114,6 +124,7 @@ class FSDPEngine:
       s.param.is_meta for u in self.units for s in u.slots)
     self._adopt_parameters(initialize=needs_init)
     self._wrap_forwards()
+    self.attach_parallel_adaptors()
 
   # ------------------------------------------------------------------ construction
   def _init_kind(self, module: nn.Module, pname: str, full_name: str) -> str:
@@ -127,6 +138,12 @@ class FSDPEngine:
     if "norm" in type(module).__name__.lower() or "norm" in full_name.split(".")[-2:][0].lower():
       return "ones"
     return "normal" if pname != "bias" else "zeros"
+
+  def _tp_sliceable(self, name: str) -> bool:
+    fn = getattr(self.model, "tp_sliceable", None)
+    if fn is not None:
+      return bool(fn(name))
+    return (".self_attn." in name or ".mlp." in name) and name.endswith("_proj.weight")
 
   def _build_units(self):
     model = self.model
@@ -145,17 +162,29 @@ class FSDPEngine:
             continue
           claimed.add(id(p))
           full_name = name_of.get(id(p), f"{uname}.{sub_name}.{pname}".strip("."))
-          tp_dim = self.plan.tp_dim(full_name) if (self.plan is not None and self.tp > 1) else None
+          tp_dim = None
+          if self.plan is not None and self.tp > 1 and self._tp_sliceable(full_name):
+            tp_dim = self.plan.tp_dim(full_name)
+          ep_dim = self.plan.ep_dim(full_name) if (self.plan is not None and self.ep > 1) else None
           full_shape = p.shape
           shape = list(p.shape)
           if tp_dim is not None:
             assert shape[tp_dim] % self.tp == 0, f"{full_name} dim {tp_dim} not divisible by tensor={self.tp}"
             shape[tp_dim] //= self.tp
+          if ep_dim is not None:
+            assert shape[ep_dim] % self.ep == 0, f"{full_name} dim {ep_dim} not divisible by expert={self.ep}"
+            shape[ep_dim] //= self.ep
           shape = torch.Size(shape)
           n = math.prod(shape)
-          u.slots.append(_ParamSlot(full_name, p, shape, n, off, self._init_kind(sub, pname, full_name),
-                                    tp_dim=tp_dim, full_shape=full_shape, owner=sub, attr=pname))
-          off += _round_up(n, _ALIGN)
+          slot = _ParamSlot(full_name, p, shape, n, off, self._init_kind(sub, pname, full_name),
+                            tp_dim=tp_dim, full_shape=full_shape, owner=sub, attr=pname, ep_dim=ep_dim,
+                            local=ep_dim is not None)
+          u.slots.append(slot)
+          if slot.local:
+            slot.local_offset = self.local_total
+            self.local_total += _round_up(n, _ALIGN)
+          else:
+            off += _round_up(n, _ALIGN)
       u.shard_size = _round_up(math.ceil(off / self.fsdp), _ALIGN) if off else 0
       u.total = u.shard_size * self.fsdp
       cls_name = type(mod).__name__
@@ -184,6 +213,8 @@ class FSDPEngine:
     for u in self.units:
       u.shard_offset = total_shard
       total_shard += u.shard_size
+    self.sharded_total = total_shard
+    total_shard += self.local_total
     self.total_shard = total_shard
     self.flat_param = torch.zeros(total_shard, dtype=self.param_dtype, device=dev)
     self.flat_grad = torch.zeros(total_shard, dtype=self.grad_dtype, device=dev)
@@ -229,6 +260,13 @@ class FSDPEngine:
           val = s.param.data.to(device=self.device, dtype=torch.float32)
         if s.tp_dim is not None:
           val = val.chunk(self.tp, dim=s.tp_dim)[self.tp_rank]
+        if s.local:
+          val = val.chunk(self.ep, dim=s.ep_dim)[self.ep_rank].reshape(-1)
+          lo_l = self.sharded_total + s.local_offset
+          if self.master_weights:
+            self.flat_master[lo_l:lo_l + s.numel].copy_(val)
+          self.flat_param[lo_l:lo_l + s.numel].copy_(val.to(self.param_dtype))
+          continue
         full[s.offset:s.offset + s.numel] = val.reshape(-1)
       lo = self.fsdp_rank * u.shard_size
       shard32 = full[lo:lo + u.shard_size]
@@ -243,15 +281,22 @@ class FSDPEngine:
                              requires_grad=s.param.requires_grad)
         s.owner._parameters[s.attr] = fresh
         s.param = fresh
+        if s.local:
+          lo_l = self.sharded_total + s.local_offset
+          fresh.data = self.flat_param[lo_l:lo_l + s.numel].view(s.shape)
+          fresh.main_grad = self.flat_grad[lo_l:lo_l + s.numel].view(s.shape)
       if self.fsdp == 1:
         self._point_params(u, self.unit_shard(u, self.flat_param), self.unit_shard(u, self.flat_grad))
       else:
         # Parameters hold no storage while their unit is not gathered.
         for s in u.slots:
-          s.param.main_grad = None
+          if not s.local:
+            s.param.main_grad = None
 
   def _point_params(self, u: Unit, flat_values: torch.Tensor, flat_grads: torch.Tensor | None):
     for s in u.slots:
+      if s.local:
+        continue
       s.param.data = flat_values[s.offset:s.offset + s.numel].view(s.shape)
       if flat_grads is not None:
         s.param.main_grad = flat_grads[s.offset:s.offset + s.numel].view(s.shape)
@@ -262,6 +307,21 @@ class FSDPEngine:
     for u in self.units:
       u.orig_forward = u.module.forward
       u.module.forward = _make_unit_forward(self, u)
+
+  def attach_parallel_adaptors(self):
+    """Give tensor-parallel and expert-parallel aware modules their process groups."""
+    if self.mesh is None:
+      return
+    if self.tp > 1:
+      grp = self.mesh.group("tensor")
+      for mod in self.model.modules():
+        if hasattr(mod, "tp_group"):
+          mod.tp_group = grp
+    if self.ep > 1:
+      from .ep import ExpertParallelMLP
+      for mod in self.model.modules():
+        if hasattr(mod, "ep") and hasattr(mod, "num_experts"):
+          mod.ep = ExpertParallelMLP(self.mesh, mod.num_experts)
 
   def unwrap(self):
     for u in self.units:
@@ -326,7 +386,8 @@ class FSDPEngine:
     u.gathered = None
     empty = torch.empty(0, dtype=self.param_dtype, device=self.device)
     for s in u.slots:
-      s.param.data = empty
+      if not s.local:
+        s.param.data = empty
 
   def _neighbor(self, u: Unit, step: int):
     j = u.index + step
@@ -360,7 +421,8 @@ class FSDPEngine:
       self._reduce_scatter(u)
       self._release(u)
       for s in u.slots:
-        s.param.main_grad = None
+        if not s.local:
+          s.param.main_grad = None
 
   def _reduce_scatter(self, u: Unit):
     if u.shard_size == 0:
@@ -417,12 +479,23 @@ class FSDPEngine:
           u.rs_work = None
       torch.cuda.current_stream().wait_stream(self.comm_stream)
     self._pending_rs.clear()
-    if self.replica_group is not None and self.replica_size > 1:
+    dense = self.flat_grad[:self.sharded_total]
+    if self.replica_group is not None and self.replica_size > 1 and dense.numel():
       if dist.get_backend(self.replica_group) == "nccl":
-        dist.all_reduce(self.flat_grad, op=dist.ReduceOp.AVG, group=self.replica_group)
+        dist.all_reduce(dense, op=dist.ReduceOp.AVG, group=self.replica_group)
       else:
-        dist.all_reduce(self.flat_grad, group=self.replica_group)
-        self.flat_grad.div_(self.replica_size)
+        dist.all_reduce(dense, group=self.replica_group)
+        dense.div_(self.replica_size)
+    if self.local_total:
+      # Expert-parallel parameters: tokens of every batch shard reached these experts, so the
+      # local gradient is already a sum over ranks of d(loss_r); average it like the dense ones.
+      local = self.flat_grad[self.sharded_total:]
+      axes = ("context",) if self.ep_folded else ("data", "fsdp", "context")
+      grp = self.mesh.group(axes)
+      if grp is not None:
+        dist.all_reduce(local, group=grp)
+      batch_shards = self.mesh.size(("data", "fsdp")) * (1 if self.ep_folded else self.ep)
+      local.mul_(1.0 / (batch_shards * self.mesh.size("context")))
 
   def sync_params_from_master(self):
     if self.master_weights:
@@ -450,7 +523,14 @@ class FSDPEngine:
     for u in self.units:
       full = self._gather_unit_full(u, flat)
       for s in u.slots:
-        t = full[s.offset:s.offset + s.numel].view(s.shape)
+        if s.local:
+          lo_l = self.sharded_total + s.local_offset
+          t = flat[lo_l:lo_l + s.numel].view(s.shape)
+          parts = [torch.empty_like(t) for _ in range(self.ep)]
+          dist.all_gather(parts, t.contiguous(), group=self.mesh.group("expert"))
+          t = torch.cat(parts, dim=s.ep_dim)
+        else:
+          t = full[s.offset:s.offset + s.numel].view(s.shape)
         if s.tp_dim is not None and tp_group is not None:
           parts = [torch.empty_like(t) for _ in range(self.tp)]
           dist.all_gather(parts, t.contiguous(), group=tp_group)
@@ -463,9 +543,11 @@ class FSDPEngine:
     """This rank's flat shards plus the layout needed to reassemble them."""
     layout = [{"unit": u.name, "shard_offset": u.shard_offset, "shard_size": u.shard_size, "total": u.total,
                "slots": [{"name": s.name, "shape": list(s.shape), "offset": s.offset, "tp_dim": s.tp_dim,
-                          "full_shape": list(s.full_shape)} for s in u.slots]} for u in self.units]
+                          "full_shape": list(s.full_shape), "local": s.local, "ep_dim": s.ep_dim,
+                          "local_offset": self.sharded_total + s.local_offset} for s in u.slots]}
+              for u in self.units]
     return {"flat_param": self.flat_param, "layout": layout, "fsdp": self.fsdp, "fsdp_rank": self.fsdp_rank,
-            "tp": self.tp, "tp_rank": self.tp_rank}
+            "tp": self.tp, "tp_rank": self.tp_rank, "ep": self.ep, "ep_rank": self.ep_rank}
 
   def load_full_state_dict(self, state: dict, strict: bool = True):
     """Scatter an un-sharded state dict (present on every rank) into the flat shards."""
@@ -486,6 +568,13 @@ class FSDPEngine:
         val = val.to(device=self.device, dtype=torch.float32)
         if s.tp_dim is not None:
           val = val.chunk(self.tp, dim=s.tp_dim)[self.tp_rank]
+        if s.local:
+          val = val.chunk(self.ep, dim=s.ep_dim)[self.ep_rank].reshape(-1)
+          lo_l = self.sharded_total + s.local_offset
+          if self.master_weights:
+            self.flat_master[lo_l:lo_l + s.numel].copy_(val)
+          self.flat_param[lo_l:lo_l + s.numel].copy_(val.to(self.param_dtype))
+          continue
         full[s.offset:s.offset + s.numel] = val.reshape(-1)
       lo = self.fsdp_rank * u.shard_size
       if self.master_weights:

@@ -77,19 +77,32 @@ class ShardedOptimizerBase:
     use_k = e.is_cuda and ops.get_backend() != "torch"
     if max_value is not None and max_value > 0:
       g.clamp_(-max_value, max_value)
+    def sumsq_into(acc, t):
+      if t.numel() == 0:
+        return
+      if use_k:
+        from ..ops import kernels as k
+        k.sumsq_(t, acc)
+      else:
+        for lo in range(0, t.numel(), _CHUNK):   # bounded temporaries
+          acc.add_(torch.linalg.vector_norm(t[lo:lo + _CHUNK], dtype=torch.float32).pow(2))
+
     self._sumsq.zero_()
-    if use_k:
-      from ..ops import kernels as k
-      k.sumsq_(g, self._sumsq)
-    else:
-      for lo in range(0, g.numel(), _CHUNK):   # bounded temporaries
-        self._sumsq.add_(torch.linalg.vector_norm(g[lo:lo + _CHUNK], dtype=torch.float32).pow(2))
-    # shards are disjoint over fsdp (and tensor); replicas hold identical values
-    if dist.is_initialized():
-      for axes in (("fsdp",), ("tensor",)):
-        grp = e.mesh.group(axes) if e.mesh is not None else None
-        if grp is not None:
-          dist.all_reduce(self._sumsq, group=grp)
+    sumsq_into(self._sumsq, g)
+    if dist.is_initialized() and e.mesh is not None:
+      tp_grp = e.mesh.group("tensor")
+      if tp_grp is not None:
+        # tensor-parallel slices are disjoint over the tensor group, everything else is replicated
+        # there: all-reduce only the sliced part so replicated gradients are counted once
+        sliced = torch.zeros_like(self._sumsq)
+        for start, n in self._tp_pieces():
+          sumsq_into(sliced, g[start:start + n])
+        self._sumsq.sub_(sliced)
+        dist.all_reduce(sliced, group=tp_grp)
+        self._sumsq.add_(sliced)
+      fsdp_grp = e.mesh.group("fsdp")
+      if fsdp_grp is not None:
+        dist.all_reduce(self._sumsq, group=fsdp_grp)
     if use_k:
       from ..ops import kernels as k
       k.clip_coef_(self._sumsq, max_norm or 0.0, self._coef, self._norm)
@@ -100,6 +113,22 @@ class ShardedOptimizerBase:
       else:
         self._coef.fill_(1.0)
     return self._norm
+
+  def _tp_pieces(self):
+    """(start, length) ranges of this rank's flat shard that belong to tensor-parallel sliced parameters."""
+    if getattr(self, "_tp_piece_cache", None) is None:
+      e = self.engine
+      pieces = []
+      for u in e.units:
+        lo, hi = e.fsdp_rank * u.shard_size, (e.fsdp_rank + 1) * u.shard_size
+        for s in u.slots:
+          if s.tp_dim is None or s.local:
+            continue
+          a, b = max(lo, s.offset), min(hi, s.offset + s.numel)
+          if a < b:
+            pieces.append((u.shard_offset + a - lo, b - a))
+      self._tp_piece_cache = pieces
+    return self._tp_piece_cache
 
   def zero_grad(self):
     self.engine.zero_grad()
@@ -164,31 +193,42 @@ class ShardedAdafactor(ShardedOptimizerBase):
     self.pieces = self._plan_pieces()
 
   def _plan_pieces(self):
+    """Flat (un-factored) pieces plus, for every >=2-D parameter, one entry per rank describing the
+    whole rows of it (possibly none) that live in this rank's shard.  Every rank lists every
+    factored parameter in the same order so the statistics exchange is one uniform all-reduce."""
     e = self.engine
     pieces = []
     for u in e.units:
       lo, hi = e.fsdp_rank * u.shard_size, (e.fsdp_rank + 1) * u.shard_size
       for s in u.slots:
-        a, b = max(lo, s.offset), min(hi, s.offset + s.numel)
-        if a >= b:
-          continue
         cols = s.shape[-1] if len(s.shape) >= 2 else None
+        if s.local:
+          start = e.sharded_total + s.local_offset
+          if cols is None:
+            pieces.append({"kind": "flat", "start": start, "n": s.numel, "v": None})
+          else:
+            pieces.append({"kind": "rows", "start": start, "rows": s.numel // cols, "cols": cols,
+                           "total_rows": s.numel // cols, "vr": None, "vc": None, "shared": False})
+          continue
+        a, b = max(lo, s.offset), min(hi, s.offset + s.numel)
+        has = a < b
         start = u.shard_offset + (a - lo)
         rel0, rel1 = a - s.offset, b - s.offset
         if cols is None:
-          pieces.append({"kind": "flat", "start": start, "n": b - a, "v": None, "slot": s})
+          if has:
+            pieces.append({"kind": "flat", "start": start, "n": b - a, "v": None})
           continue
-        first_row = -(-rel0 // cols)
-        last_row = rel1 // cols
-        head_n = min(first_row * cols, rel1) - rel0
+        first_row = -(-rel0 // cols) if has else 0
+        last_row = rel1 // cols if has else 0
+        head_n = (min(first_row * cols, rel1) - rel0) if has else 0
         if head_n > 0:
-          pieces.append({"kind": "flat", "start": start, "n": head_n, "v": None, "slot": s})
-        if last_row > first_row:
-          pieces.append({"kind": "rows", "start": start + head_n, "rows": last_row - first_row, "cols": cols,
-                         "row0": first_row, "total_rows": s.numel // cols, "vr": None, "vc": None, "slot": s})
-        tail0 = max(last_row, first_row) * cols
-        if rel1 > tail0 and tail0 >= rel0 + head_n:
-          pieces.append({"kind": "flat", "start": start + (tail0 - rel0), "n": rel1 - tail0, "v": None, "slot": s})
+          pieces.append({"kind": "flat", "start": start, "n": head_n, "v": None})
+        pieces.append({"kind": "rows", "start": start + head_n, "rows": max(0, last_row - first_row), "cols": cols,
+                       "total_rows": s.numel // cols, "vr": None, "vc": None, "shared": e.fsdp > 1})
+        if has:
+          tail0 = max(last_row, first_row) * cols
+          if rel1 > tail0 and tail0 >= rel0 + head_n:
+            pieces.append({"kind": "flat", "start": start + (tail0 - rel0), "n": rel1 - tail0, "v": None})
     return pieces
 
   def step(self, lr: float | None = None):
@@ -198,7 +238,16 @@ class ShardedAdafactor(ShardedOptimizerBase):
     beta2t = 1.0 - math.pow(self.step_count, self.decay_rate)
     master = e.flat_master if e.flat_master is not None else e.flat_param
     coef = self._coef
+    dev = e.flat_grad.device
     grp = e.fsdp_group if e.fsdp > 1 else None
+
+    def apply(sl, upd, n):
+      rms = upd.norm(2) / math.sqrt(n)
+      upd = upd / torch.clamp(rms / self.clip_threshold, min=1.0)
+      master[sl].add_(upd.to(master.dtype), alpha=-lr)
+
+    # phase 1: local statistics; factored pieces queue their column sums and row-moment sums
+    shared_stats, work = [], []
     for pc in self.pieces:
       if pc["kind"] == "flat":
         sl = slice(pc["start"], pc["start"] + pc["n"])
@@ -207,32 +256,44 @@ class ShardedAdafactor(ShardedOptimizerBase):
         if pc["v"] is None:
           pc["v"] = torch.zeros_like(upd)
         pc["v"].mul_(beta2t).add_(upd, alpha=1.0 - beta2t)
-        upd = g * pc["v"].rsqrt()
-        denom_n = pc["n"]
-      else:
-        r, c = pc["rows"], pc["cols"]
+        apply(sl, g * pc["v"].rsqrt(), pc["n"])
+        continue
+      r, c = pc["rows"], pc["cols"]
+      if pc["vr"] is None:
+        pc["vr"] = torch.zeros(r, dtype=torch.float32, device=dev)
+        pc["vc"] = torch.zeros(c, dtype=torch.float32, device=dev)
+      g = None
+      col_sum = torch.zeros(c, dtype=torch.float32, device=dev)
+      if r > 0:
         sl = slice(pc["start"], pc["start"] + r * c)
         g = (e.flat_grad[sl].float() * coef).view(r, c)
         sq = g * g + self.eps[0]
-        if pc["vr"] is None:
-          pc["vr"] = torch.zeros(r, dtype=torch.float32, device=g.device)
-          pc["vc"] = torch.zeros(c, dtype=torch.float32, device=g.device)
         col_sum = sq.sum(0)
-        if grp is not None:
-          dist.all_reduce(col_sum, group=grp)
         pc["vr"].mul_(beta2t).add_(sq.mean(-1), alpha=1.0 - beta2t)
-        pc["vc"].mul_(beta2t).add_(col_sum / pc["total_rows"], alpha=1.0 - beta2t)
-        row_mean = pc["vr"].sum()
-        if grp is not None:
-          dist.all_reduce(row_mean, group=grp)
-        row_mean = row_mean / pc["total_rows"]
-        r_factor = (pc["vr"] / row_mean).rsqrt().unsqueeze(-1)
-        c_factor = pc["vc"].rsqrt().unsqueeze(0)
-        upd = (g * r_factor * c_factor).reshape(-1)
-        denom_n = r * c
-      rms = upd.norm(2) / math.sqrt(denom_n)
-      upd = upd / torch.clamp(rms / self.clip_threshold, min=1.0)
-      master[sl].add_(upd.to(master.dtype), alpha=-lr)
+      stat = torch.cat([col_sum, pc["vr"].sum().reshape(1)])
+      if pc["shared"]:
+        shared_stats.append(stat)
+      work.append((pc, g, stat))
+    if shared_stats and grp is not None:
+      flat = torch.cat(shared_stats)
+      dist.all_reduce(flat, group=grp)
+      off = 0
+      for i, (pc, g, stat) in enumerate(work):
+        if pc["shared"]:
+          n = stat.numel()
+          work[i] = (pc, g, flat[off:off + n])
+          off += n
+    # phase 2: factored update
+    for pc, g, stat in work:
+      c = pc["cols"]
+      pc["vc"].mul_(beta2t).add_(stat[:c] / pc["total_rows"], alpha=1.0 - beta2t)
+      if g is None:
+        continue
+      row_mean = stat[c] / pc["total_rows"]
+      r_factor = (pc["vr"] / row_mean).rsqrt().unsqueeze(-1)
+      c_factor = pc["vc"].rsqrt().unsqueeze(0)
+      upd = (g * r_factor * c_factor).reshape(-1)
+      apply(slice(pc["start"], pc["start"] + upd.numel()), upd, upd.numel())
     if e.master_weights:
       e.flat_param.copy_(master)
 

@@ -87,6 +87,10 @@ class Trainer:
     if cp_enabled(config) and hasattr(model, "cp"):
       from ..parallel.cp import ContextParallelAttention
       model.cp = ContextParallelAttention(self.mesh, load_balanced=lb_cp_enabled(config))
+      if getattr(model, "_head", None) is not None:
+        model._head.loss_group = self.mesh.group("context")
+      if hasattr(model, "model"):
+        model.model.max_rope_positions = int(config.dataset.block_size)
 
     self.optimizer = type(self)._create_optimizer(config, self.engine)
     self.lr_scheduler = LRScheduler(
