@@ -1,0 +1,78 @@
+"""Launcher plumbing, e2e checkers, system check, benchmark row — all on CPU."""
+
+import datetime
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, os.path.join(ROOT, "e2e_testing"))
+
+from torchprime_b200.dist import launcher as L
+from torchprime_b200.launcher import benchmark_db_util, cli
+
+
+def test_jobset_name_and_workload_args():
+  name = cli.generate_jobset_name("My Run!", datetime.datetime(2025, 1, 2, 3, 4, 5))
+  assert name.endswith("-20250102-030405") and name == name.lower() and len(name) <= 40
+  args = cli.workload_args(["model=llama-3-8b"], {"artifact_dir": "/art"}, "js")
+  assert "profile_dir=/art/js/profile/0-0" in args and "output_dir=/art/js/outputs/0-0" in args
+  assert cli.workload_args(["output_dir=x"], {}, "js").count("output_dir=x") == 1
+  env = cli.workload_env({"gpus": 8, "artifact_dir": "/art"}, "js", "note")
+  assert env["TORCHPRIME_ACCELERATOR_TYPE"] == "b200-8" and env["TORCHPRIME_JOBSET_NAME"] == "js"
+
+
+def test_tp_run_dry_run(tmp_path, monkeypatch):
+  monkeypatch.chdir(tmp_path)
+  assert cli.main(["run", "--gpus", "2", "--dry-run", "-m", "torchprime_b200.train", "model=llama-tiny"]) == 0
+
+
+def test_launcher_propagates_failure_and_stops_peers(tmp_path):
+  script = tmp_path / "w.py"
+  script.write_text("import os, sys, time\nr = int(os.environ['RANK'])\nassert os.environ['MASTER_ADDR'] == '127.0.0.1'\n"
+                    "if r == 1:\n  sys.exit(7)\ntime.sleep(60)\n")
+  import time
+  t0 = time.time()
+  rc = L.launch([sys.executable, str(script)], nproc=3, grace_s=2.0)
+  assert rc == 7 and time.time() - t0 < 30
+  ok = tmp_path / "ok.py"
+  ok.write_text("import os\nassert int(os.environ['WORLD_SIZE']) == 2\n")
+  assert L.launch([sys.executable, str(ok)], nproc=2) == 0
+
+
+def test_e2e_checkers(tmp_path):
+  import checks
+  log = tmp_path / "log.txt"
+  log.write_text("Epoch: 0.0, step: 0, loss: 1.2352, grad_norm: 1.0\nEpoch: 0.1, step: 9, loss: 0.4826, grad_norm: 0.5\n"
+                 "Finished training run\n")
+  assert checks.check_logs(str(log)) == 0
+  assert checks.check_loss(str(log), 0.4826, 0.001) == 0 and checks.check_loss(str(log), 0.6, 0.001) == 1
+  (tmp_path / "p" / "a").mkdir(parents=True)
+  assert checks.check_profile(str(tmp_path / "p")) == 1
+  (tmp_path / "p" / "a" / "trace_rank0.json").write_text("{}")
+  assert checks.check_profile(str(tmp_path / "p")) == 0
+  out = tmp_path / "out"
+  out.mkdir()
+  (out / "train_metrics.json").write_text(json.dumps({"step_execution_time": 1.0}))
+  bounds = tmp_path / "b.yaml"
+  assert checks.update_bounds(str(bounds), "k", [0.95, 1.0, 1.05, 1.02]) == 0
+  assert checks.check_step_time(str(out), "k", str(bounds)) == 0
+  (out / "train_metrics.json").write_text(json.dumps({"step_execution_time": 9.0}))
+  assert checks.check_step_time(str(out), "k", str(bounds)) == 1
+  b = checks.compute_bounds([1.0, 1.0, 1.0])
+  assert b["confidence_interval"] == pytest.approx(0.03)
+
+
+def test_system_check_and_benchmark_row(tmp_path):
+  from torchprime_b200.tools import system_check
+  assert system_check.main([f"output_dir={tmp_path}", "--foo"]) == 0
+  assert any(f.startswith("log-") for f in os.listdir(tmp_path))
+  (tmp_path / "train_metrics.json").write_text(json.dumps({"step_execution_time": 0.5, "mfu": 0.3, "tokens_per_second": 10.0,
+                                                           "num_steps": 3, "train_runtime": 9.0}))
+  (tmp_path / "train_config.json").write_text(json.dumps({"model": {"model_id": "m"}, "ici_mesh": {"fsdp": 8, "data": 1},
+                                                          "task": {"global_batch_size": 8}, "dataset": {"block_size": 128}}))
+  row = benchmark_db_util.append_row(str(tmp_path), str(tmp_path / "db.jsonl"))
+  assert row["hardware_num_chips"] == 8 and row["metrics_mfu"] == 0.3 and os.path.exists(tmp_path / "db.jsonl")
