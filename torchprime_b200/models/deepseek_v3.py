@@ -63,6 +63,8 @@ class DeepseekV3TopkRouter(nn.Module):
     self.topk_group = int(config.topk_group)
     self.norm_topk_prob = bool(config.norm_topk_prob)
     self.weight = nn.Parameter(torch.empty(self.n_routed_experts, config.hidden_size))
+    if not self.weight.is_meta:
+      nn.init.normal_(self.weight, std=float(config.get("initializer_range", 0.02)))
     self.register_buffer("e_score_correction_bias", torch.zeros(self.n_routed_experts, device="cpu"))
 
   def forward(self, x):
