@@ -49,3 +49,33 @@ extern "C" void tpb_status_clear(void) {
     for (int i = 0; i < 4; ++i) tpb::g_status_host[i] = 0;
 }
 extern "C" int tpb_sm_count(void) { return tpb::sm_count(); }
+
+// A wait that is meant to run out: spins (bounded by `budget_cycles`) until *flag == expected and
+// reports kTimeoutPeerFlag into the status block when the budget is exhausted.  Used by the
+// failure-detection tests to show that a stuck wait ends with a status code, not with a hung GPU.
+__global__ void bounded_wait_kernel(const unsigned* flag, unsigned expected, long long budget_cycles, int* status,
+                                    int* result) {
+  const long long t0 = clock64();
+  while (true) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+    if (v == expected) {
+      *result = 1;
+      return;
+    }
+    if (clock64() - t0 > budget_cycles) {
+      tpb::report(status, tpb::kTimeoutPeerFlag, 99);
+      *result = -1;
+      return;
+    }
+    __nanosleep(200);
+  }
+}
+
+extern "C" int tpb_bounded_wait(const unsigned* flag, unsigned expected, long long budget_cycles, int* result,
+                                void* stream) {
+  bounded_wait_kernel<<<1, 1, 0, reinterpret_cast<cudaStream_t>(stream)>>>(flag, expected, budget_cycles,
+                                                                           tpb::status_block(), result);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}

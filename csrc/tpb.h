@@ -23,6 +23,9 @@ enum {
 int tpb_status(int* out4);
 void tpb_status_clear(void);
 int tpb_sm_count(void);
+// Bounded device-side wait on a flag (failure-detection building block): *result = 1 when the flag
+// reached `expected`, -1 (and status code 5) when `budget_cycles` ran out first.
+int tpb_bounded_wait(const unsigned* flag, unsigned expected, long long budget_cycles, int* result, void* stream);
 
 // C[M,N] = alpha * A[M,K] * B[N,K]^T.  a_mn / b_mn = 1 when that operand is stored
 // with its M/N index contiguous ([K][M] resp. [K][N]) instead of K contiguous.
