@@ -123,8 +123,11 @@ int tpb_moe_combine_dw(const void* rows, const int* dest, const void* dout, floa
 int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int Hq,
                  int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv, long long ldo, float scale,
                  int causal, int window, const int* q_pos, const int* q_seg, const int* kv_seg, void* stream);
+// `scratch` holds tpb_attn_bwd_scratch_floats(B, Sq, Hq) floats; dq/dk/dv are fully overwritten.
+long long tpb_attn_bwd_scratch_floats(int B, int Sq, int Hq);
+void tpb_attn_bwd_set_prof(long long* counters);
 int tpb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,
-                 float* delta, float* dq_acc, void* dq, void* dk, void* dv, int B, int Sq, int Sk, int Hq, int Hkv,
+                 float* scratch, void* dq, void* dk, void* dv, int B, int Sq, int Sk, int Hq, int Hkv,
                  int dqk, int dvd, long long ldq, long long ldk, long long ldv, long long lddo, long long lddq,
                  long long lddk, long long lddv, float scale, int causal, int window, const int* q_pos,
                  const int* q_seg, const int* kv_seg, void* stream);

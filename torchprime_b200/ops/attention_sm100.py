@@ -20,7 +20,7 @@ from ._lib import check, lib, ptr, stream_ptr
 
 P, I, LL, F = c_void_p, c_int, c_longlong, c_float
 _lib.register_signature("tpb_attn_fwd", [P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, F, I, I, P, P, P, P])
-_lib.register_signature("tpb_attn_bwd", [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, LL,
+_lib.register_signature("tpb_attn_bwd", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, LL,
                                          LL, LL, F, I, I, P, P, P, P])
 
 
@@ -75,10 +75,8 @@ def attn_bwd(do, q, k, v, o, lse, causal=True, scale=None, window=None, q_pos=No
   o = o.contiguous()
   if dqk != 128:
     return _eager_bwd(do, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk, dv)
-  sq_pad = (sq + 63) // 64 * 64
-  dq_acc = torch.zeros(b, hq, sq_pad, dqk, dtype=torch.float32, device=q.device)
-  delta = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
-  rc = lib().tpb_attn_bwd(ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(delta), ptr(dq_acc), ptr(dq),
+  scratch = torch.empty(2 * b * hq * ((sq + 127) // 128 * 128), dtype=torch.float32, device=q.device)
+  rc = lib().tpb_attn_bwd(ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(scratch), ptr(dq),
                           ptr(dk), ptr(dv), b, sq, sk, hq, hkv, dqk, dvd, q.stride(1), k.stride(1), v.stride(1),
                           do.stride(1), dq.stride(1), dk.stride(1), dv.stride(1), float(scale), int(bool(causal)),
                           int(window or 0), ptr(q_pos), ptr(q_seg), ptr(kv_seg), stream_ptr())
