@@ -125,7 +125,6 @@ int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
                  int causal, int window, const int* q_pos, const int* q_seg, const int* kv_seg, void* stream);
 // `scratch` holds tpb_attn_bwd_scratch_floats(B, Sq, Hq) floats; dq/dk/dv are fully overwritten.
 long long tpb_attn_bwd_scratch_floats(int B, int Sq, int Hq);
-void tpb_attn_bwd_set_prof(long long* counters);
 int tpb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,
                  float* scratch, void* dq, void* dk, void* dv, int B, int Sq, int Sk, int Hq, int Hkv,
                  int dqk, int dvd, long long ldq, long long ldk, long long ldv, long long lddo, long long lddq,
