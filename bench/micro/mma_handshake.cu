@@ -21,7 +21,7 @@ using namespace tpb;
 // WAIT_MMA: MMA thread waits for ds_full.  WAIT_CMP: compute waits for sdp_full.  TMEM: compute touches TMEM.
 // MATH: compute does the exp math.  ARRIVE: 0 none, 1 all threads, 2 one lane per warp.
 template <int WAIT_MMA, bool WAIT_CMP, bool TMEM, bool MATH, int ARRIVE>
-__global__ void __launch_bounds__(320, 1) skel(long long* out, int iters, int* status, float* sink, long long* ts) {
+__global__ void __launch_bounds__(352, 1) skel(long long* out, int iters, int* status, float* sink, long long* ts) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   __shared__ uint64_t sdp_full[2], ds_full[2], done_bar, dummy[2];
@@ -63,6 +63,15 @@ __global__ void __launch_bounds__(320, 1) skel(long long* out, int iters, int* s
     long long t0 = clock64();
     scores(0);
     bool ok = true;
+    if (WAIT_MMA == 5) {
+      // two issuing threads: this one only issues the score MMAs; it may run one step ahead of
+      // the compute warps (buffer (j+1)&1 is free once they arrived for step j-1)
+      for (int j = 0; j < iters && ok; ++j) {
+        if (j >= 1) { ok = mbar_wait(&ds_full[(j - 1) & 1], ((j - 1) >> 1) & 1, status, 2, 95); tc_fence_after(); }
+        if (j + 1 < iters) scores(j + 1);
+      }
+      iters = 0;
+    }
     for (int j = 0; j < iters && ok; ++j) {
       const bool rec = ts && blockIdx.x == 0 && j >= 100 && j < 104;
       if (rec) ts[(j - 100) * 8 + 0] = clock64() - t0;
@@ -82,9 +91,32 @@ __global__ void __launch_bounds__(320, 1) skel(long long* out, int iters, int* s
       if (rec) ts[(j - 100) * 8 + 3] = clock64() - t0;
     }
     if (ts && blockIdx.x == 0) ts[63] = t0;
-    tc_commit(&done_bar);
-    mbar_wait(&done_bar, 0, status, 1, 99);
-    out[blockIdx.x] = clock64() - t0;
+    if (WAIT_MMA != 5) {
+      tc_commit(&done_bar);
+      mbar_wait(&done_bar, 0, status, 1, 99);
+      out[blockIdx.x] = clock64() - t0;
+    }
+  } else if (warp == 10) {
+    if (WAIT_MMA == 5 && lane == 0) {
+      constexpr uint32_t id_dq = make_idesc_bf16(128, 128, false, true);
+      const uint32_t aB = smem_u32(smem + 64 * 1024);
+      long long t0 = clock64();
+      bool ok = true;
+      for (int j = 0; j < iters && ok; ++j) {
+        ok = mbar_wait(&ds_full[j & 1], (j >> 1) & 1, status, 2, 97);
+        tc_fence_after();
+        const uint32_t tDS = tm + 128 + (j & 1) * 128 + 64;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          uint64_t bd = make_smem_desc(aB + k * 2048, 64 * 128, 1024);
+          mma_ts(tm, tDS + (k >> 1) * 32 + (k & 1) * 8, bd, id_dq, (j | k) != 0);
+        }
+        tc_commit(&dummy[1]);
+      }
+      tc_commit(&done_bar);
+      mbar_wait(&done_bar, 0, status, 1, 99);
+      out[blockIdx.x] = clock64() - t0;
+    }
   } else if (warp >= 2) {
     const int half = (warp - 2) >> 2;
     const uint32_t tb = tm + ((uint32_t)((warp & 3) * 32) << 16);
@@ -134,8 +166,9 @@ __global__ void __launch_bounds__(320, 1) skel(long long* out, int iters, int* s
 template <int A, bool B, bool C, bool D, int E>
 void run(const char* name, long long* d_out, int* d_status, float* sink, long long* ts = nullptr) {
   cudaFuncSetAttribute(skel<A, B, C, D, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  int iters_unused = 0; (void)iters_unused;
   const int iters = 512;
-  for (int rep = 0; rep < 2; ++rep) skel<A, B, C, D, E><<<148, 320, 200 * 1024>>>(d_out, iters, d_status, sink, ts);
+  for (int rep = 0; rep < 2; ++rep) skel<A, B, C, D, E><<<148, 352, 200 * 1024>>>(d_out, iters, d_status, sink, ts);
   cudaError_t e = cudaDeviceSynchronize();
   long long h[1];
   cudaMemcpy(h, d_out, sizeof(h), cudaMemcpyDeviceToHost);
@@ -164,6 +197,7 @@ int main() {
   run<1, true, true, true, 1>("+ mma thread waits for them (full handshake)", d_out, d_status, sink);
   run<1, true, true, true, 2>("full handshake, one arrival per warp", d_out, d_status, sink);
   run<1, true, false, false, 1>("full handshake, no math, no TMEM traffic", d_out, d_status, sink, ts);
+  run<5, true, true, true, 1>("full handshake, two issuing threads (scores / dQ)", d_out, d_status, sink);
   int hs[4]; cudaMemcpy(hs, d_status, 16, cudaMemcpyDeviceToHost);
   printf("status %d %d %d %d\n", hs[0], hs[1], hs[2], hs[3]);
   return 0;

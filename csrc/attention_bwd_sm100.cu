@@ -154,14 +154,20 @@ __device__ __forceinline__ void store_acc_row(uint32_t tsrc, int col0, __nv_bflo
   }
 }
 
-// K-major operand tile [128 rows][128 d] in two 64-wide d blocks: descriptor of k-step k (16 d).
-__device__ __forceinline__ uint64_t kmajor_desc(uint32_t tile, int k) {
-  return make_smem_desc(tile + (k >> 2) * (BWD_T * 128) + (k & 3) * 32, 16, 1024);
+// Elementwise product of two packed bf16 pairs (one HMUL2.BF16).
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&a), *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&r);
 }
-// The same tile read as an MN-major B operand (N = d contiguous, K = rows): k-step k (16 rows).
-__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t tile, int k) {
-  return make_smem_desc(tile + k * 2048, BWD_T * 128, 1024);
-}
+
+// Operand tiles are [128 rows][128 d] in two 64-wide d blocks.  Descriptor low words (the high
+// word kDescHi is common): K-major use, k-step k covers 16 d; MN-major use (N = d contiguous,
+// K = rows), k-step k covers 16 rows.  The k-dependent part is a compile-time constant.
+constexpr uint32_t kDescHi = smem_desc_hi(1024);
+__device__ __forceinline__ uint32_t kmajor_lo(uint32_t tile) { return smem_desc_lo(tile, 16); }
+__device__ __forceinline__ uint32_t mnmajor_lo(uint32_t tile) { return smem_desc_lo(tile, BWD_T * 128); }
+__device__ __forceinline__ constexpr uint32_t kmajor_k(int k) { return (uint32_t)(((k >> 2) * (BWD_T * 128) + (k & 3) * 32) >> 4); }
+__device__ __forceinline__ constexpr uint32_t mnmajor_k(int k) { return (uint32_t)((k * 2048) >> 4); }
 // TMEM column (relative to the tile) where the bf16 A operand of k-step k lives: compute half
 // k >> 2 packed its 64 results into the first 32 columns of its own 64-column range.
 __device__ __forceinline__ uint32_t a_col(int k) { return (uint32_t)((k >> 2) * 64 + (k & 3) * 8); }
@@ -313,48 +319,65 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (lane == 0 && n_steps > 0) {
       constexpr uint32_t id_s = make_idesc_bf16(BWD_T, BWD_T, false, false);    // S^T, dP^T
       constexpr uint32_t id_acc = make_idesc_bf16(BWD_T, BWD_D, false, true);   // dV, dK (A in TMEM, B MN-major)
-      const uint32_t aK = smem_u32(smem + OFF_K), aV = smem_u32(smem + OFF_V);
+      const uint32_t dK = kmajor_lo(smem_u32(smem + OFF_K)), dVd = kmajor_lo(smem_u32(smem + OFF_V));
       const uint32_t aQ0 = smem_u32(smem + OFF_Q), aDO0 = smem_u32(smem + OFF_DO);
       const uint32_t tS = tmem_base + T_S, tDP = tmem_base + T_DP;
-      bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutTmaFull, 22);
-      auto issue_s = [&](int i) -> bool {
-        const int sq = i % KV_QSTAGES;
-        if (!mbar_wait(&q_full[sq], (i / KV_QSTAGES) & 1, p.status, kTimeoutTmaFull, 23)) return false;
-        tc_fence_after();
-        const uint32_t aQ = aQ0 + sq * TILE_BYTES;
+      // The MMA queue is shallow, so whatever this thread does between two MMAs is tensor idle
+      // time: every wait is therefore placed before the LAST MMA of the preceding group, where
+      // its latency hides behind the seven MMAs still in flight.
+      auto wait_q = [&](int i) { return mbar_wait(&q_full[i % KV_QSTAGES], (i / KV_QSTAGES) & 1, p.status, kTimeoutTmaFull, 23); };
+      auto wait_do = [&](int i) { return mbar_wait(&do_full[i % KV_DOSTAGES], (i / KV_DOSTAGES) & 1, p.status, kTimeoutTmaFull, 24); };
+      auto wait_p = [&](int i) { return mbar_wait(p_full, i & 1, p.status, kTimeoutSoftmax, 25); };
+      auto wait_ds = [&](int i) { return mbar_wait(ds_full, i & 1, p.status, kTimeoutSoftmax, 26); };
+      auto group = [&](auto&& mma, auto&& hook) -> bool {
 #pragma unroll
-        for (int k = 0; k < BWD_D / 16; ++k) mma_ss(tS, kmajor_desc(aK, k), kmajor_desc(aQ, k), id_s, k != 0);
+        for (int k = 0; k < 7; ++k) mma(k);
+        if (!hook()) return false;
+        tc_fence_after();
+        mma(7);
+        return true;
+      };
+      bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutTmaFull, 22) && wait_q(0);
+      tc_fence_after();
+      auto issue_s = [&](int i, auto&& hook) -> bool {      // S^T(i) = K Q(i)^T
+        const uint32_t dQ = kmajor_lo(aQ0 + (i % KV_QSTAGES) * TILE_BYTES);
+        if (!group([&](int k) { mma_ss_w(tS, dK + kmajor_k(k), kDescHi, dQ + kmajor_k(k), kDescHi, id_s, k != 0); }, hook))
+          return false;
         tc_commit(s_full);
         return true;
       };
-      auto issue_dp = [&](int i) -> bool {
-        const int sd = i % KV_DOSTAGES;
-        if (!mbar_wait(&do_full[sd], (i / KV_DOSTAGES) & 1, p.status, kTimeoutTmaFull, 24)) return false;
-        tc_fence_after();
-        const uint32_t aDO = aDO0 + sd * TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < BWD_D / 16; ++k) mma_ss(tDP, kmajor_desc(aV, k), kmajor_desc(aDO, k), id_s, k != 0);
+      auto issue_dp = [&](int i, auto&& hook) -> bool {     // dP^T(i) = V dO(i)^T
+        const uint32_t dDO = kmajor_lo(aDO0 + (i % KV_DOSTAGES) * TILE_BYTES);
+        if (!group([&](int k) { mma_ss_w(tDP, dVd + kmajor_k(k), kDescHi, dDO + kmajor_k(k), kDescHi, id_s, k != 0); }, hook))
+          return false;
         tc_commit(dp_full);
         return true;
       };
-      if (ok) ok = issue_s(0);
-      if (ok) ok = issue_dp(0);
+      auto none = [] { return true; };
+      if (ok) ok = issue_s(0, [&] { return wait_do(0); });
+      if (ok) ok = issue_dp(0, none);
       for (int i = 0; i < n_steps && ok; ++i) {
-        const uint32_t aQ = aQ0 + (i % KV_QSTAGES) * TILE_BYTES, aDO = aDO0 + (i % KV_DOSTAGES) * TILE_BYTES;
-        if (!mbar_wait(p_full, i & 1, p.status, kTimeoutSoftmax, 25)) break;
+        const uint32_t mQ = mnmajor_lo(aQ0 + (i % KV_QSTAGES) * TILE_BYTES);
+        const uint32_t mDO = mnmajor_lo(aDO0 + (i % KV_DOSTAGES) * TILE_BYTES);
+        const bool more = i + 1 < n_steps;
+        // Waits on the compute warps stay where the data is needed: hooking them into the previous
+        // group would hold back that group's commit, which the compute warps are waiting for.
+        if (!wait_p(i)) break;
         tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < BWD_T / 16; ++k)   // dV += P^T dO
-          mma_ts(tmem_base + T_DV, tS + a_col(k), mnmajor_desc(aDO, k), id_acc, (i | k) != 0);
+        // dV += P^T dO
+        ok = group([&](int k) { mma_ts_w(tmem_base + T_DV, tS + a_col(k), mDO + mnmajor_k(k), kDescHi, id_acc, (i | k) != 0); },
+                   [&] { return more ? wait_q(i + 1) : true; });
+        if (!ok) break;
         tc_commit(&do_empty[i % KV_DOSTAGES]);
-        if (i + 1 < n_steps && !issue_s(i + 1)) break;
-        if (!mbar_wait(ds_full, i & 1, p.status, kTimeoutSoftmax, 26)) break;
+        if (more && !issue_s(i + 1, none)) break;
+        if (!wait_ds(i)) break;
         tc_fence_after();
-#pragma unroll
-        for (int k = 0; k < BWD_T / 16; ++k)   // dK += dS^T Q
-          mma_ts(tmem_base + T_DK, tDP + a_col(k), mnmajor_desc(aQ, k), id_acc, (i | k) != 0);
+        // dK += dS^T Q
+        ok = group([&](int k) { mma_ts_w(tmem_base + T_DK, tDP + a_col(k), mQ + mnmajor_k(k), kDescHi, id_acc, (i | k) != 0); },
+                   [&] { return more ? wait_do(i + 1) : true; });
+        if (!ok) break;
         tc_commit(&q_empty[i % KV_QSTAGES]);
-        if (i + 1 < n_steps && !issue_dp(i + 1)) break;
+        if (more && !issue_dp(i + 1, none)) break;
       }
       tc_commit(acc_done);
     }
@@ -387,11 +410,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!mbar_wait(s_full, step & 1, p.status, kTimeoutAccFull, 27)) { ok = false; break; }
         tc_fence_after();
         uint32_t pk_p[32];
+        uint32_t sreg[64];
+        tmem_ld32(tS, sreg);
+        tmem_ld32(tS + 32, sreg + 32);
+        tmem_wait_ld();
 #pragma unroll
         for (int ch = 0; ch < 2; ++ch) {
-          uint32_t s[32];
-          tmem_ld32(tS + ch * 32, s);
-          tmem_wait_ld();
+          const uint32_t* s = sreg + ch * 32;
           const float4* lse4 = reinterpret_cast<const float4*>(aux + half * 64 + ch * 32);
           if (!need_mask) {
 #pragma unroll
@@ -434,24 +459,22 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         // ---- phase 2: dS^T = P^T o (dP^T - delta), written over dP^T
         if (!mbar_wait(dp_full, step & 1, p.status, kTimeoutAccFull, 28)) { ok = false; break; }
         tc_fence_after();
-#pragma unroll
-        for (int ch = 0; ch < 2; ++ch) {
-          uint32_t dp[32], pk_ds[16];
-          tmem_ld32(tDP + ch * 32, dp);
+        {
+          uint32_t dreg[64], pk_ds[32];
+          tmem_ld32(tDP, dreg);
+          tmem_ld32(tDP + 32, dreg + 32);
           tmem_wait_ld();
-          const float4* dlt4 = reinterpret_cast<const float4*>(aux + BWD_T + half * 64 + ch * 32);
+          const float4* dlt4 = reinterpret_cast<const float4*>(aux + BWD_T + half * 64);
 #pragma unroll
-          for (int c4 = 0; c4 < 8; ++c4) {
+          for (int c4 = 0; c4 < 16; ++c4) {
             const float4 Dl = dlt4[c4];
-            const float2 pa = unpack_bf16(pk_p[ch * 16 + 2 * c4]), pb = unpack_bf16(pk_p[ch * 16 + 2 * c4 + 1]);
-            pk_ds[2 * c4] = pack_bf16(pa.x * (__uint_as_float(dp[4 * c4]) - Dl.x),
-                                      pa.y * (__uint_as_float(dp[4 * c4 + 1]) - Dl.y));
-            pk_ds[2 * c4 + 1] = pack_bf16(pb.x * (__uint_as_float(dp[4 * c4 + 2]) - Dl.z),
-                                          pb.y * (__uint_as_float(dp[4 * c4 + 3]) - Dl.w));
+            pk_ds[2 * c4] = mul_bf16x2(pk_p[2 * c4], pack_bf16(__uint_as_float(dreg[4 * c4]) - Dl.x,
+                                                               __uint_as_float(dreg[4 * c4 + 1]) - Dl.y));
+            pk_ds[2 * c4 + 1] = mul_bf16x2(pk_p[2 * c4 + 1], pack_bf16(__uint_as_float(dreg[4 * c4 + 2]) - Dl.z,
+                                                                       __uint_as_float(dreg[4 * c4 + 3]) - Dl.w));
           }
-          // chunk 1 is read (above) before chunk 0's result could overwrite it: results go to
-          // columns [0,32) of this warp's range, chunk 1's inputs are columns [32,64)
-          tmem_st16(tDP + ch * 16, pk_ds);
+          // all 64 inputs of this warp are in registers, so its first 32 columns can be overwritten
+          tmem_st32(tDP, pk_ds);
         }
         tmem_wait_st();
         tc_fence_before();
@@ -575,45 +598,54 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t id_s = make_idesc_bf16(BWD_T, BWD_T, false, false);    // S, dP
       constexpr uint32_t id_dq = make_idesc_bf16(BWD_T, BWD_D, false, true);    // dQ (A in TMEM, B MN-major)
-      const uint32_t aQ = smem_u32(smem + OFF_Q), aDO = smem_u32(smem + OFF_DO);
+      const uint32_t dQ = kmajor_lo(smem_u32(smem + OFF_Q)), dDO = kmajor_lo(smem_u32(smem + OFF_DO));
       const uint32_t aK0 = smem_u32(smem + OFF_K), aV0 = smem_u32(smem + OFF_V);
       const uint32_t tDP = tmem_base + T_DP;
-      bool ok = mbar_wait(qdo_full, 0, p.status, kTimeoutTmaFull, 32);
-      auto issue_s = [&](int j) -> bool {
-        const int sk = j % DQ_KSTAGES;
-        if (!mbar_wait(&k_full[sk], (j / DQ_KSTAGES) & 1, p.status, kTimeoutTmaFull, 33)) return false;
-        tc_fence_after();
-        const uint32_t aK = aK0 + sk * TILE_BYTES;
-        const uint32_t tS = tmem_base + T_S + (j & 1) * BWD_T;
+      // Waits sit before the last MMA of the preceding group (see the dK/dV kernel).
+      auto wait_k = [&](int j) { return mbar_wait(&k_full[j % DQ_KSTAGES], (j / DQ_KSTAGES) & 1, p.status, kTimeoutTmaFull, 33); };
+      auto wait_v = [&](int j) { return mbar_wait(&v_full[j % DQ_VSTAGES], (j / DQ_VSTAGES) & 1, p.status, kTimeoutTmaFull, 37); };
+      auto wait_ds = [&](int j) { return mbar_wait(ds_full, j & 1, p.status, kTimeoutSoftmax, 34); };
+      auto group = [&](auto&& mma, auto&& hook) -> bool {
 #pragma unroll
-        for (int k = 0; k < BWD_D / 16; ++k) mma_ss(tS, kmajor_desc(aQ, k), kmajor_desc(aK, k), id_s, k != 0);
+        for (int k = 0; k < 7; ++k) mma(k);
+        if (!hook()) return false;
+        tc_fence_after();
+        mma(7);
+        return true;
+      };
+      bool ok = mbar_wait(qdo_full, 0, p.status, kTimeoutTmaFull, 32) && wait_k(0);
+      tc_fence_after();
+      auto issue_s = [&](int j, auto&& hook) -> bool {      // S(j) = Q K_j^T
+        const uint32_t dK = kmajor_lo(aK0 + (j % DQ_KSTAGES) * TILE_BYTES);
+        const uint32_t tS = tmem_base + T_S + (j & 1) * BWD_T;
+        if (!group([&](int k) { mma_ss_w(tS, dQ + kmajor_k(k), kDescHi, dK + kmajor_k(k), kDescHi, id_s, k != 0); }, hook))
+          return false;
         tc_commit(&s_full[j & 1]);
         return true;
       };
-      auto issue_dp = [&](int j) -> bool {
-        const int sv = j % DQ_VSTAGES;
-        if (!mbar_wait(&v_full[sv], (j / DQ_VSTAGES) & 1, p.status, kTimeoutTmaFull, 37)) return false;
-        tc_fence_after();
-        const uint32_t aV = aV0 + sv * TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < BWD_D / 16; ++k) mma_ss(tDP, kmajor_desc(aDO, k), kmajor_desc(aV, k), id_s, k != 0);
-        tc_commit(&v_empty[sv]);
+      auto issue_dp = [&](int j, auto&& hook) -> bool {     // dP(j) = dO V_j^T
+        const uint32_t dV = kmajor_lo(aV0 + (j % DQ_VSTAGES) * TILE_BYTES);
+        if (!group([&](int k) { mma_ss_w(tDP, dDO + kmajor_k(k), kDescHi, dV + kmajor_k(k), kDescHi, id_s, k != 0); }, hook))
+          return false;
+        tc_commit(&v_empty[j % DQ_VSTAGES]);
         tc_commit(dp_full);
         return true;
       };
-      if (ok) ok = issue_s(0);
-      if (ok) ok = issue_dp(0);
+      auto none = [] { return true; };
+      if (ok) ok = issue_s(0, [&] { return wait_v(0); });
+      if (ok) ok = issue_dp(0, [&] { return nblk > 1 ? wait_k(1) : true; });
       for (int j = 0; j < nblk && ok; ++j) {
-        const int sk = j % DQ_KSTAGES;
-        if (j + 1 < nblk && !issue_s(j + 1)) break;
-        if (!mbar_wait(ds_full, j & 1, p.status, kTimeoutSoftmax, 34)) break;
+        const bool more = j + 1 < nblk;
+        if (more && !issue_s(j + 1, none)) break;
+        if (!wait_ds(j)) break;   // not hooked into S(j+1): that would hold back its commit
         tc_fence_after();
-        const uint32_t aK = aK0 + sk * TILE_BYTES;
-#pragma unroll
-        for (int k = 0; k < BWD_T / 16; ++k)   // dQ += dS K   (K tile [128 keys][128 d]: N = d contiguous)
-          mma_ts(tmem_base + T_DQ, tDP + a_col(k), mnmajor_desc(aK, k), id_dq, (j | k) != 0);
-        tc_commit(&k_empty[sk]);
-        if (j + 1 < nblk && !issue_dp(j + 1)) break;
+        const uint32_t mK = mnmajor_lo(aK0 + (j % DQ_KSTAGES) * TILE_BYTES);
+        // dQ += dS K   (K tile [128 keys][128 d]: N = d contiguous)
+        ok = group([&](int k) { mma_ts_w(tmem_base + T_DQ, tDP + a_col(k), mK + mnmajor_k(k), kDescHi, id_dq, (j | k) != 0); },
+                   [&] { return more ? wait_v(j + 1) : true; });
+        if (!ok) break;
+        tc_commit(&k_empty[j % DQ_KSTAGES]);
+        if (more && !issue_dp(j + 1, [&] { return j + 2 < nblk ? wait_k(j + 2) : true; })) break;
       }
       tc_commit(acc_done);
     }
@@ -646,11 +678,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, p.status, kTimeoutAccFull, 36)) { ok = false; break; }
       tc_fence_after();
       uint32_t pk_p[32];
+      uint32_t sreg[64];
+      tmem_ld32(tS, sreg);
+      tmem_ld32(tS + 32, sreg + 32);
+      tmem_wait_ld();
 #pragma unroll
       for (int ch = 0; ch < 2; ++ch) {
-        uint32_t s[32];
-        tmem_ld32(tS + ch * 32, s);
-        tmem_wait_ld();
+        const uint32_t* s = sreg + ch * 32;
         if (!need_mask) {
 #pragma unroll
           for (int c = 0; c < 32; c += 2)
@@ -676,17 +710,16 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // ---- phase 2: dS = P o (dP - delta), written over dP
       if (!mbar_wait(dp_full, j & 1, p.status, kTimeoutAccFull, 39)) { ok = false; break; }
       tc_fence_after();
-#pragma unroll
-      for (int ch = 0; ch < 2; ++ch) {
-        uint32_t dp[32], pk[16];
-        tmem_ld32(tDP + ch * 32, dp);
+      {
+        uint32_t dreg[64], pk[32];
+        tmem_ld32(tDP, dreg);
+        tmem_ld32(tDP + 32, dreg + 32);
         tmem_wait_ld();
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float2 pp = unpack_bf16(pk_p[ch * 16 + c / 2]);
-          pk[c / 2] = pack_bf16(pp.x * (__uint_as_float(dp[c]) - delta), pp.y * (__uint_as_float(dp[c + 1]) - delta));
-        }
-        tmem_st16(tDP + ch * 16, pk);
+        for (int c = 0; c < 32; ++c)
+          pk[c] = mul_bf16x2(pk_p[c], pack_bf16(__uint_as_float(dreg[2 * c]) - delta,
+                                                __uint_as_float(dreg[2 * c + 1]) - delta));
+        tmem_st32(tDP, pk);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -709,6 +742,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 }  // namespace tpb
 
 using namespace tpb;
+
 
 // Floats of scratch `tpb_attn_bwd` needs (scaled log-sum-exp and delta rows, padded to 128).
 extern "C" long long tpb_attn_bwd_scratch_floats(int B, int Sq, int Hq) {

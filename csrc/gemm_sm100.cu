@@ -333,11 +333,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, p.status, kTimeoutAccFree, 2)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
+        // The MMA queue is shallow: whatever this thread does between two MMAs is tensor idle
+        // time.  So the wait for the next k-block's operands is placed before the last MMA of the
+        // current one, where its latency hides behind the MMAs still in flight.
+        bool prewaited = false;
         for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
-          if (!mbar_wait(&full[stage], phase, p.status, kTimeoutTmaFull, 3)) {
+          if (!prewaited && !mbar_wait(&full[stage], phase, p.status, kTimeoutTmaFull, 3)) {
             ok = false;
             break;
           }
+          prewaited = false;
           tc_fence_after();
           const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sB = sA + A_BYTES;
@@ -347,8 +352,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                         : make_smem_desc(sA + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(sB + k * 2048, 8192, 1024)
                                         : make_smem_desc(sB + k * 32, 16, 1024);
+            if (k == BK / 16 - 1 && kb + 1 < ti.kb1) {
+              const int ns = (stage + 1 == STAGES) ? 0 : stage + 1;
+              const uint32_t np = (stage + 1 == STAGES) ? (phase ^ 1) : phase;
+              if (!mbar_wait(&full[ns], np, p.status, kTimeoutTmaFull, 3)) {
+                ok = false;
+                break;
+              }
+              prewaited = true;
+            }
             mma_ss(d_tmem, adesc, bdesc, idesc, ((kb - ti.kb0) | k) != 0);
           }
+          if (!ok) break;
           tc_commit(&empty[stage]);
           if (++stage == STAGES) {
             stage = 0;
