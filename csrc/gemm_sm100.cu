@@ -320,6 +320,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      constexpr uint32_t desc_hi = smem_desc_hi(1024);
+      const uint32_t smem_base = smem_u32(smem);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -344,14 +346,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           prewaited = false;
           tc_fence_after();
-          const uint32_t sA = smem_u32(smem + stage * STAGE_BYTES);
-          const uint32_t sB = sA + A_BYTES;
+          // Descriptors of one stage differ from the stage's first one only in the low word, by a
+          // compile-time constant per k-step: one integer add per operand and MMA.
+          const uint32_t sA = smem_base + stage * STAGE_BYTES;
+          const uint32_t a_lo = smem_desc_lo(sA, A_MN ? 8192 : 16);
+          const uint32_t b_lo = smem_desc_lo(sA + A_BYTES, B_MN ? 8192 : 16);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t adesc = A_MN ? make_smem_desc(sA + k * 2048, 8192, 1024)
-                                        : make_smem_desc(sA + k * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc(sB + k * 2048, 8192, 1024)
-                                        : make_smem_desc(sB + k * 32, 16, 1024);
             if (k == BK / 16 - 1 && kb + 1 < ti.kb1) {
               const int ns = (stage + 1 == STAGES) ? 0 : stage + 1;
               const uint32_t np = (stage + 1 == STAGES) ? (phase ^ 1) : phase;
@@ -361,7 +362,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               }
               prewaited = true;
             }
-            mma_ss(d_tmem, adesc, bdesc, idesc, ((kb - ti.kb0) | k) != 0);
+            mma_ss_w(d_tmem, a_lo + (A_MN ? k * 128 : k * 2), desc_hi, b_lo + (B_MN ? k * 128 : k * 2), desc_hi, idesc,
+                     ((kb - ti.kb0) | k) != 0);
           }
           if (!ok) break;
           tc_commit(&empty[stage]);
