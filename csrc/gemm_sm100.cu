@@ -72,6 +72,7 @@ struct GemmParams {
   long long ag_b_offset;        // element offset of B inside the gathered buffer
   unsigned* ag_flags;           // [ag_world * chunks_per_shard], value = epoch when ready
   unsigned ag_epoch;
+  int ag_local;                 // rank whose shard already sits in ag_dst (not copied, not waited for); -1: none
   // Reduce-scatter fusion (TPB_EPI_RS_BF16): the epilogue adds alpha * acc straight into the
   // owner's bf16 gradient shard over P2P with vector red.add.
   int rs_world;
@@ -129,6 +130,10 @@ __device__ __forceinline__ bool ag_wait_range(const GemmParams& p, long long lo,
   long long e = lo;
   while (e <= hi) {
     const long long owner = e / p.ag_shard_elems;
+    if (owner == p.ag_local) {
+      e = (owner + 1) * p.ag_shard_elems;
+      continue;
+    }
     const long long j = (e - owner * p.ag_shard_elems) / p.ag_chunk_elems;
     const unsigned* f = p.ag_flags + owner * cps + j;
     unsigned v;
@@ -161,12 +166,16 @@ __device__ void ag_copier(const GemmParams& p, uint8_t* smem) {
   for (int i = 0; i < SLOTS; ++i) mbar_init(&bars[i], 1);
   fence_barrier_init();
   const long long cps = ag_chunks_per_shard(p);
-  const long long n_chunks = cps * p.ag_world;
+  const int n_owners = p.ag_local >= 0 ? p.ag_world - 1 : p.ag_world;   // the local shard is in place
+  const long long n_chunks = cps * n_owners;
   const int G = p.ag_copiers, c = blockIdx.x;
-  const long long mine = (n_chunks - c + G - 1) / G;   // chunks c, c+G, ...
+  const long long mine = (n_chunks - c + G - 1) / G;   // chunks c, c+G, ... of the shards to copy
   auto chunk_geom = [&](long long k, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, long long& id) {
-    id = c + k * G;
-    const long long owner = id / cps, j = id % cps;
+    const long long r = c + k * G;
+    long long owner = r / cps;
+    const long long j = r % cps;
+    if (p.ag_local >= 0 && owner >= p.ag_local) ++owner;
+    id = owner * cps + j;
     const long long off = j * p.ag_chunk_elems;
     const long long n = min(p.ag_chunk_elems, p.ag_shard_elems - off);
     src = reinterpret_cast<const uint8_t*>(p.ag_src[owner]) + off * 2;
@@ -570,7 +579,7 @@ struct GemmCall {
   int max_ctas;
   int mode; const int* tile_expert; const int* k_offsets; long long c_stride;
   // fusion with collectives (0 / null when unused)
-  int ag_world, ag_copiers; const void* const* ag_src; void* ag_dst; long long ag_shard_elems, ag_b_offset;
+  int ag_world, ag_copiers, ag_local; const void* const* ag_src; void* ag_dst; long long ag_shard_elems, ag_b_offset;
   unsigned* ag_flags; unsigned ag_epoch;
   int rs_world; void* const* rs_dst; long long rs_shard_elems, rs_c_offset;
 };
@@ -623,7 +632,7 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.c_stride = g.c_stride;
   p.ag_world = g.ag_world; p.ag_copiers = g.ag_world > 0 ? g.ag_copiers : 0;
   p.ag_dst = g.ag_dst; p.ag_shard_elems = g.ag_shard_elems; p.ag_chunk_elems = 16384; p.ag_b_offset = g.ag_b_offset;
-  p.ag_flags = g.ag_flags; p.ag_epoch = g.ag_epoch;
+  p.ag_flags = g.ag_flags; p.ag_epoch = g.ag_epoch; p.ag_local = g.ag_world > 0 ? g.ag_local : -1;
   p.rs_world = g.rs_world; p.rs_shard_elems = g.rs_shard_elems; p.rs_c_offset = g.rs_c_offset;
   for (int i = 0; i < 8; ++i) {
     p.ag_src[i] = (g.ag_world > 0 && i < g.ag_world) ? g.ag_src[i] : nullptr;
@@ -695,10 +704,12 @@ extern "C" int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B
 // shards (world * shard_elems elements), B starts b_offset elements into it and is a dense
 // row-major [N, K] matrix.  `flags` has world * ceil(shard_elems / 16384) entries (local memory,
 // zero-initialised once); pass a fresh non-zero `epoch` per call.  The whole buffer is gathered.
+// local_rank >= 0: that rank's shard is already in `gathered` (it is neither copied nor waited for).
 extern "C" int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int epi,
                                 const void* aux, long long ldaux, void* c2, long long ldc2,
                                 const void* const* shard_ptrs, int world, long long shard_elems, void* gathered,
-                                long long b_offset, unsigned* flags, unsigned epoch, int copiers, void* stream_) {
+                                long long b_offset, unsigned* flags, unsigned epoch, int copiers, int local_rank,
+                                void* stream_) {
   GemmCall g{};
   g.A = A; g.B = reinterpret_cast<const __nv_bfloat16*>(gathered) + b_offset; g.B2 = nullptr; g.C = C;
   g.M = M; g.N = N; g.K = K; g.E = 1;
@@ -707,6 +718,7 @@ extern "C" int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, lon
   g.aux = aux; g.ldaux = ldaux; g.c2 = c2; g.ldc2 = ldc2; g.max_ctas = 0; g.mode = 0;
   g.ag_world = world; g.ag_copiers = copiers; g.ag_src = shard_ptrs; g.ag_dst = gathered;
   g.ag_shard_elems = shard_elems; g.ag_b_offset = b_offset; g.ag_flags = flags; g.ag_epoch = epoch;
+  g.ag_local = local_rank;
   return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
 }
 

@@ -2,9 +2,10 @@
 
 ``ag_gemm``: ``y = x @ W^T`` where the flat buffer that contains ``W`` is sharded over the ranks of a
 group (FSDP parameter shards, or a row-sharded activation/weight for tensor parallelism).  A few
-copier CTAs of the same kernel pull every shard from its owner (plain bulk copies from peer memory,
-no multicast) into the local gathered buffer and publish per-chunk flags; the GEMM CTAs load their
-B tiles locally as soon as the chunks they need have landed.  After the call the whole buffer is
+copier CTAs of the same kernel pull every remote shard from its owner (plain bulk copies from peer
+memory, no multicast) into the local gathered buffer and publish per-chunk flags; the GEMM CTAs
+load their B tiles locally as soon as the chunks they need have landed.  The rank's own shard is
+put in place by a device-to-device copy on the same stream before the kernel starts.  After the call the whole buffer is
 gathered, so the other weights of the same FSDP unit are ready too.
 
 ``gemm_rs``: ``dW = dY^T X`` (or any GEMM) whose epilogue adds ``alpha * tile`` directly into the
@@ -23,7 +24,7 @@ from . import _lib
 from ._lib import check, lib, ptr, stream_ptr
 
 P, I, LL, FL, U = c_void_p, c_int, c_longlong, c_float, c_uint
-_lib.register_signature("tpb_ag_gemm_bf16", [P, P, I, I, I, LL, LL, I, P, LL, P, LL, P, I, LL, P, LL, P, U, I, P])
+_lib.register_signature("tpb_ag_gemm_bf16", [P, P, I, I, I, LL, LL, I, P, LL, P, LL, P, I, LL, P, LL, P, U, I, I, P])
 _lib.register_signature("tpb_gemm_rs_bf16", [P, P, I, I, I, LL, LL, LL, I, I, FL, P, I, LL, LL, P])
 
 CHUNK_ELEMS = 16384
@@ -36,7 +37,7 @@ def num_flags(world: int, shard_elems: int) -> int:
 class AllGatherGemm:
   """State for repeated fused all-gather + GEMM calls on one sharded flat buffer."""
 
-  def __init__(self, shard_buffer, shard_elems: int, copiers: int = 8):
+  def __init__(self, shard_buffer, shard_elems: int, copiers: int = 16):
     self.sb = shard_buffer                     # dist.symm.SymmetricBuffer holding this rank's shard
     self.world = shard_buffer.world
     self.shard_elems = shard_elems
@@ -54,10 +55,13 @@ class AllGatherGemm:
     if out is None:
       out = torch.empty(m, n // 2 if epi == _lib.EPI_SWIGLU else n, dtype=torch.bfloat16, device=x2d.device)
     table = self.sb.ptr_table(shard_offset)
+    rank = self.sb.rank
+    gathered[rank * self.shard_elems:(rank + 1) * self.shard_elems].copy_(
+        self.sb.local[shard_offset:shard_offset + self.shard_elems])
     rc = lib().tpb_ag_gemm_bf16(ptr(x2d), ptr(out), m, n, k, x2d.stride(0), out.stride(0), epi, ptr(aux),
                                 aux.stride(0) if aux is not None else 0, ptr(c2), c2.stride(0) if c2 is not None else 0,
                                 table, self.world, self.shard_elems, ptr(gathered), b_offset, ptr(self.flags),
-                                self.epoch, self.copiers, stream_ptr())
+                                self.epoch, self.copiers, rank, stream_ptr())
     check(rc, f"ag_gemm M={m} N={n} K={k} world={self.world}")
     return out
 
