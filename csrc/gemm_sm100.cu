@@ -18,6 +18,7 @@
 // Every wait is bounded (common.cuh); on timeout the roles fall through to the
 // common exit, TMEM is released and the status block tells the host what happened.
 
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -220,51 +221,67 @@ __device__ void ag_copier(const GemmParams& p, uint8_t* smem) {
   if (mine > 0) publish(mine - 1);
 }
 
-template <bool A_MN, bool B_MN>
+// PAIR: the kernel runs as clusters of two CTAs on 256 x 256 output tiles.  Each CTA stages its
+// 128 rows of A and ONE 128-row half of B per k-block (32 KB instead of 48 KB, in a 6-deep ring),
+// the even CTA issues tcgen05.mma.cta_group::2 (M = 256) for both, and each CTA drains its own
+// 128 accumulator rows.  Shared-memory traffic per FLOP drops by a third, which is what bounds
+// the single-CTA kernel (TMA writes plus operand reads exceed 128 B/clk).  Dense mode only.
+template <bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
+  constexpr int NST = PAIR ? 6 : STAGES;                 // ring depth
+  constexpr int SBYTES = PAIR ? 32768 : STAGE_BYTES;     // bytes per stage in this CTA
+  constexpr int TM = PAIR ? 2 * BM : BM;                 // output rows per tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
-  uint64_t* empty = full + STAGES;
-  uint64_t* acc_full = empty + STAGES;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);   // == 6 * 32768
+  uint64_t* empty = full + NST;
+  uint64_t* acc_full = empty + NST;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if ((int)blockIdx.x < p.ag_copiers) {
+  if (!PAIR && (int)blockIdx.x < p.ag_copiers) {
     ag_copier(p, smem);
     return;
   }
-  const int cta = (int)blockIdx.x - p.ag_copiers;
-  const int n_ctas = (int)gridDim.x - p.ag_copiers;
+  const int rank = PAIR ? (int)cluster_ctarank() : 0;    // 0: issues the MMAs of the pair
+  // tiles are dealt to CTAs (or to CTA pairs)
+  const int cta = PAIR ? (int)blockIdx.x / 2 : (int)blockIdx.x - p.ag_copiers;
+  const int n_ctas = PAIR ? (int)gridDim.x / 2 : (int)gridDim.x - p.ag_copiers;
   const bool swiglu = p.epi == TPB_EPI_SWIGLU;
   const int tile_n_out = swiglu ? BN / 2 : BN;  // output columns covered by one tile
   const int n_logical = swiglu ? p.N / 2 : p.N;
-  const int m_tiles = (p.M + BM - 1) / BM;
+  const int m_tiles = (p.M + TM - 1) / TM;
   const int n_tiles = (n_logical + tile_n_out - 1) / tile_n_out;
   const int num_tiles = m_tiles * n_tiles * (p.mode == 2 ? p.num_experts : 1);
   const int num_kb = (p.K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < NST; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&acc_full[a], 1);
-      mbar_init(&acc_empty[a], 4);
+      mbar_init(&acc_empty[a], PAIR ? 8 : 4);   // one arrival per epilogue warp (of both CTAs)
     }
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, 512);
-    tmem_relinquish();
+    if (PAIR) {
+      tmem_alloc_pair(tmem_slot, 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(tmem_slot, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -280,7 +297,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int t = cta; t < num_tiles && ok; t += n_ctas) {
         const TileInfo ti = tile_info(p, t, m_tiles, n_tiles, num_kb);
         if (ti.skip) continue;
-        const int m0 = ti.tm * BM, n0 = ti.tn * tile_n_out;
+        const int m0 = ti.tm * TM + rank * BM, n0 = ti.tn * tile_n_out;
         const int ez = p.mode == 1 ? ti.e : 0;
         if (p.ag_world > 0) {
           // B rows [n0, n0 + BN) of a dense [N, ldb = K] matrix occupy one flat range
@@ -293,10 +310,31 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             ok = false;
             break;
           }
-          uint8_t* sA = smem + stage * STAGE_BYTES;
+          uint8_t* sA = smem + stage * SBYTES;
           uint8_t* sB = sA + A_BYTES;
-          mbar_expect_tx(&full[stage], STAGE_BYTES);
           const int k0 = kb * BK;
+          if (PAIR) {
+            // Both CTAs' bytes are counted on the even CTA's barrier, which alone expects them.
+            const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+            if (rank == 0) mbar_expect_tx(&full[stage], 2 * SBYTES);
+            if (!A_MN) {
+              tma_load_2d_pair(sA, &tmA, bar, k0, m0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < BM / 64; ++c) tma_load_2d_pair(sA + c * 8192, &tmA, bar, m0 + c * 64, k0);
+            }
+            // this CTA's half of B: rows/columns [n0 + rank * 128, +128) (for SwiGLU the odd CTA
+            // takes the "up" half)
+            const CUtensorMap* mb = (swiglu && rank == 1) ? &tmB2 : &tmB;
+            const int nb = (swiglu && rank == 1) ? p.b2_off + n0 : n0 + rank * 128;
+            if (!B_MN) {
+              tma_load_3d_pair(sB, mb, bar, k0, nb, 0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < 2; ++c) tma_load_3d_pair(sB + c * 8192, mb, bar, nb + c * 64, k0, 0);
+            }
+          } else {
+          mbar_expect_tx(&full[stage], STAGE_BYTES);
           if (!A_MN) {
             tma_load_2d(sA, &tmA, &full[stage], k0, m0);  // box {64 k, 128 rows}
           } else {
@@ -318,7 +356,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 tma_load_3d(sB + c * 8192, &tmB, &full[stage], n0 + c * 64, k0, ez);
             }
           }
-          if (++stage == STAGES) {
+          }
+          if (++stage == NST) {
             stage = 0;
             phase ^= 1;
           }
@@ -327,8 +366,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TM, BN, A_MN, B_MN);
       constexpr uint32_t desc_hi = smem_desc_hi(1024);
       const uint32_t smem_base = smem_u32(smem);
       int stage = 0;
@@ -357,31 +396,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           tc_fence_after();
           // Descriptors of one stage differ from the stage's first one only in the low word, by a
           // compile-time constant per k-step: one integer add per operand and MMA.
-          const uint32_t sA = smem_base + stage * STAGE_BYTES;
+          const uint32_t sA = smem_base + stage * SBYTES;
           const uint32_t a_lo = smem_desc_lo(sA, A_MN ? 8192 : 16);
           const uint32_t b_lo = smem_desc_lo(sA + A_BYTES, B_MN ? 8192 : 16);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             if (k == BK / 16 - 1 && kb + 1 < ti.kb1) {
-              const int ns = (stage + 1 == STAGES) ? 0 : stage + 1;
-              const uint32_t np = (stage + 1 == STAGES) ? (phase ^ 1) : phase;
+              const int ns = (stage + 1 == NST) ? 0 : stage + 1;
+              const uint32_t np = (stage + 1 == NST) ? (phase ^ 1) : phase;
               if (!mbar_wait(&full[ns], np, p.status, kTimeoutTmaFull, 3)) {
                 ok = false;
                 break;
               }
               prewaited = true;
             }
-            mma_ss_w(d_tmem, a_lo + (A_MN ? k * 128 : k * 2), desc_hi, b_lo + (B_MN ? k * 128 : k * 2), desc_hi, idesc,
-                     ((kb - ti.kb0) | k) != 0);
+            if (PAIR)
+              mma_ss_pair_w(d_tmem, a_lo + (A_MN ? k * 128 : k * 2), desc_hi, b_lo + (B_MN ? k * 128 : k * 2), desc_hi,
+                            idesc, ((kb - ti.kb0) | k) != 0);
+            else
+              mma_ss_w(d_tmem, a_lo + (A_MN ? k * 128 : k * 2), desc_hi, b_lo + (B_MN ? k * 128 : k * 2), desc_hi, idesc,
+                       ((kb - ti.kb0) | k) != 0);
           }
           if (!ok) break;
-          tc_commit(&empty[stage]);
-          if (++stage == STAGES) {
+          if (PAIR) tc_commit_pair(&empty[stage]); else tc_commit(&empty[stage]);
+          if (++stage == NST) {
             stage = 0;
             phase ^= 1;
           }
         }
-        if (ok) tc_commit(&acc_full[acc]);
+        if (ok) { if (PAIR) tc_commit_pair(&acc_full[acc]); else tc_commit(&acc_full[acc]); }
       }
     }
   } else {
@@ -399,7 +442,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int tm = ti.tm, tn = ti.tn;
       const bool empty_k = ti.kb1 <= ti.kb0;   // nothing was accumulated: the tile is all zeros
       const long long c_off = p.mode == 2 ? (long long)ti.e * p.c_stride : 0;
-      const int row = tm * BM + q * 32 + lane;
+      const int row = tm * TM + rank * BM + q * 32 + lane;
       const int n0 = tn * tile_n_out;
       const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(q * 32) << 16);
       const bool row_ok = row < p.M;
@@ -532,15 +575,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) {
+        if (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+        else mbar_arrive(&acc_empty[acc]);
+      }
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();   // neither CTA's shared memory or TMEM goes away under the other
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if (PAIR) tmem_dealloc_pair(tmem_base, 512); else tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -558,12 +605,39 @@ cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUte
                         int grid, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<A_MN, B_MN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GEMM_SMEM);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  gemm_kernel<A_MN, B_MN><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, tb2, p);
+  gemm_kernel<A_MN, B_MN, false><<<grid, GEMM_THREADS, GEMM_SMEM, stream>>>(ta, tb, tb2, p);
   return cudaGetLastError();
+}
+
+// Launch as clusters of two CTAs (`grid` is even).
+template <bool A_MN, bool B_MN>
+cudaError_t launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
+                             int grid, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_kernel<A_MN, B_MN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GEMM_SMEM);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = GEMM_SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gemm_kernel<A_MN, B_MN, true>, ta, tb, tb2, p);
 }
 
 
@@ -655,6 +729,38 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   if (g.max_ctas > 0 && g.max_ctas < cap) cap = g.max_ctas;
   const int grid = (tiles > cap ? cap : (int)tiles) + p.ag_copiers;
   cudaError_t e;
+  // CTA pairs for dense GEMMs with enough 256 x 256 tiles to fill the machine (TPB_GEMM_PAIR=0
+  // keeps the single-CTA kernel)
+  // TPB_GEMM_PAIR: 0 = never, 2 = for every dense shape (tests), default = when the tiles fill the machine
+  static const int pair_mode = []() { const char* v = getenv("TPB_GEMM_PAIR"); return v ? atoi(v) : 1; }();
+  static const int max_pairs = []() {
+    // clusters of two that can be resident at once (an SM without a free partner stays idle)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 74, 1, 1);
+    cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = GEMM_SMEM;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    int n = 0;
+    cudaFuncSetAttribute(gemm_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM);
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_kernel<false, false, true>, &cfg) != cudaSuccess || n < 1) n = 0;
+    (void)cudaGetLastError();
+    return n < sm_count() / 2 ? n : sm_count() / 2;
+  }();
+  const long long pair_tiles = (long long)((g.M + 2 * BM - 1) / (2 * BM)) * n_tiles;
+  if (pair_mode != 0 && max_pairs > 0 && g.mode == 0 && g.ag_world == 0 && g.epi != TPB_EPI_RS_BF16 &&
+      g.max_ctas == 0 && (pair_mode == 2 || pair_tiles >= max_pairs)) {
+    const int pairs = pair_tiles > max_pairs ? max_pairs : (int)pair_tiles;
+    const int m_tiles2 = (g.M + 2 * BM - 1) / (2 * BM);
+    p.group_m = m_tiles2 < 8 ? m_tiles2 : 8;
+    if (!g.a_mn && !g.b_mn)      e = launch_gemm_pair<false, false>(ta, tb, tb2, p, 2 * pairs, stream);
+    else if (!g.a_mn && g.b_mn)  e = launch_gemm_pair<false, true>(ta, tb, tb2, p, 2 * pairs, stream);
+    else if (g.a_mn && !g.b_mn)  e = launch_gemm_pair<true, false>(ta, tb, tb2, p, 2 * pairs, stream);
+    else                         e = launch_gemm_pair<true, true>(ta, tb, tb2, p, 2 * pairs, stream);
+    return e == cudaSuccess ? 0 : 1000 + (int)e;
+  }
   if (!g.a_mn && !g.b_mn)      e = launch_gemm<false, false>(ta, tb, tb2, p, grid, stream);
   else if (!g.a_mn && g.b_mn)  e = launch_gemm<false, true>(ta, tb, tb2, p, grid, stream);
   else if (g.a_mn && !g.b_mn)  e = launch_gemm<true, false>(ta, tb, tb2, p, grid, stream);
