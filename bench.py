@@ -6,7 +6,8 @@
 
 Config: Llama-3-8B (32 layers, hidden 4096, 32/8 heads, FFN 14336, vocab 128256), sequence
 8192, one sequence per GPU (global batch = N, weak scaling), bf16 compute, fused AdamW with
-fp32 master weights and moments, per-layer rematerialisation, random-init weights and
+fp32 master weights and moments, rematerialisation of as many layers as memory requires
+(`engine.remat_layers=auto`; the JSON line says how many), random-init weights and
 uniform-random token ids.  Two timed regions of exactly K steps each, both bracketed by a
 barrier + device synchronisation and timed with CUDA events (max over ranks):
 
@@ -231,7 +232,8 @@ def main():
       "gpu_launches": int(launches),
       "clocks": clocks,
       "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq_len,
-                 "parallelism": f"fsdp{n}", "remat": "per-layer", "optimizer": "adamw fp32 master+moments",
+                 "parallelism": f"fsdp{n}", "remat": trainer.engine.remat_summary(),
+                 "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1), "optimizer": "adamw fp32 master+moments",
                  "l2": "no flush needed: each step streams >16 GB of weights/optimizer state, far above the 126 MB L2",
                  "baseline": "vs_baseline = value / (6.91k tok/s/chip x n_gpus), Llama-3-8B seq 8192 on TPU v6e-256",
                  "attention": trainer_attention_impl()},

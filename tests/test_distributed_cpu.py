@@ -93,6 +93,13 @@ def test_fsdp2_matches_single(llama_single):
   close(run(2, LLAMA + ["ici_mesh.fsdp=2"])["traj"], llama_single)
 
 
+@pytest.mark.parametrize("policy", ["none", "1"])
+def test_fsdp2_saved_activations_match_single(llama_single, policy):
+  """Units that keep their activations (parameters re-gathered before their backward) and a mix of
+  kept and recomputed units both reproduce the single-rank run."""
+  close(run(2, LLAMA + ["ici_mesh.fsdp=2", f"engine.remat_layers={policy}"])["traj"], llama_single)
+
+
 def test_data2_matches_single(llama_single):
   close(run(2, LLAMA + ["ici_mesh.fsdp=1", "ici_mesh.data=2"])["traj"], llama_single)
 

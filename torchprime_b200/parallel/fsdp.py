@@ -68,6 +68,8 @@ class Unit:
   shard_size: int = 0
   shard_offset: int = 0     # offset of this unit's shard inside the engine-wide flat shards
   remat: bool = True
+  remat_class: bool = False  # named by the remat config (activation_checkpoint_layers)
+  keep: bool | None = None   # "auto" policy: decided on the first step
   terminal: bool = False
   offload: bool = False
   big: bool = False         # has dedicated gather / grad buffers
@@ -83,7 +85,7 @@ class FSDPEngine:
   def __init__(self, model: nn.Module, mesh, plan=None, *, device=None, param_dtype=torch.bfloat16,
                grad_dtype=None, master_weights: bool = True, remat_classes=(), offload_tensors=(),
                init_std: float | None = None, seed: int = 42, materialize: bool | None = None,
-               fused_collectives: bool = False):
+               fused_collectives: bool = False, remat_policy: str | int = "all"):
     self.model = model
     self.mesh = mesh
     self.plan = plan
@@ -112,6 +114,12 @@ class FSDPEngine:
     self.fused_collectives = fused_collectives
     self.remat_classes = set(remat_classes or ())
     self.offload_tensors = set(offload_tensors or ())
+    # Which of the units named by ``remat_classes`` really recompute their forward in backward:
+    # "all" (every one), "none", an integer (that many, counted from the first), or "auto": keep
+    # the activations of as many units as fit in free device memory (measured on the first step).
+    self.remat_policy = remat_policy
+    self._remat_budget = None        # bytes still available for saved activations ("auto", first step)
+    self._remat_unit_bytes = None    # measured activation bytes of one saved unit
     self.units: list[Unit] = []
     self._dummy = None
     self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
@@ -188,7 +196,8 @@ class FSDPEngine:
       u.shard_size = _round_up(math.ceil(off / self.fsdp), _ALIGN) if off else 0
       u.total = u.shard_size * self.fsdp
       cls_name = type(mod).__name__
-      u.remat = True if self.fsdp > 1 else (cls_name in self.remat_classes)
+      u.remat_class = cls_name in self.remat_classes
+      u.remat = u.remat_class or self.fsdp > 1
       u.offload = bool(self.offload_tensors) and cls_name in self.remat_classes
       self.units.append(u)
     if hasattr(model, "fsdp_units") and self.units:
@@ -392,6 +401,52 @@ class FSDPEngine:
   def _neighbor(self, u: Unit, step: int):
     j = u.index + step
     return self.units[j] if 0 <= j < len(self.units) else None
+
+  # ------------------------------------------------------------------ rematerialisation policy
+  def keep_activations(self, u: Unit) -> bool:
+    """True when unit ``u`` keeps its activations for backward instead of recomputing them."""
+    if not u.remat_class:
+      return self.fsdp > 1          # not asked to recompute; under fsdp the saved path re-gathers
+    pol = self.remat_policy
+    if pol == "all":
+      return False
+    if pol == "none":
+      return True
+    if isinstance(pol, int):
+      firsts = [x.index for x in self.units if x.remat_class][:pol]
+      return u.index not in firsts
+    # auto
+    if u.keep is not None:
+      return u.keep
+    if not self.is_cuda:
+      u.keep = False
+      return False
+    if self._remat_budget is None:
+      free, _total = torch.cuda.mem_get_info(self.device)
+      cached = torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+      self._remat_budget = free + cached
+    if self._remat_unit_bytes is None:
+      u.keep = self._remat_budget > (8 << 30)       # measure on the first candidate if there is room at all
+      return u.keep
+    # reserve: two more units' worth of transients in backward, the head's logits chunks, fragmentation
+    reserve = int(2.5 * self._remat_unit_bytes) + (8 << 30)
+    usable = int(0.85 * (self._remat_budget - reserve))
+    kept = sum(1 for x in self.units if x.keep)
+    u.keep = (kept + 1) * self._remat_unit_bytes <= usable
+    return u.keep
+
+  def note_saved_unit_bytes(self, nbytes: int):
+    self._remat_unit_bytes = max(int(nbytes), 1)
+
+  def remat_summary(self) -> str:
+    cands = [x for x in self.units if x.remat_class]
+    kept = sum(1 for x in cands if self.keep_activations_static(x))
+    return f"{len(cands) - kept} of {len(cands)} layers recomputed (policy {self.remat_policy})"
+
+  def keep_activations_static(self, u: Unit) -> bool:
+    if self.remat_policy == "auto":
+      return bool(u.keep)
+    return self.keep_activations(u)
 
   # ------------------------------------------------------------------ hooks used by the unit function
   def pre_forward(self, u: Unit):
@@ -612,7 +667,66 @@ def _run_unit(engine: FSDPEngine, u: Unit, args, kwargs):
     for s in u.slots:
       s.param.grad_overwrite = engine._overwrite_next
     return u.orig_forward(*args, **kwargs)
+  if engine.keep_activations(u) and any(isinstance(a, torch.Tensor) and a.requires_grad for a in args):
+    return _run_unit_saved(engine, u, args, kwargs)
   return _RematFn.apply(engine, u, kwargs, engine._dummy, *args)
+
+
+def _run_unit_saved(engine: FSDPEngine, u: Unit, args, kwargs):
+  """Forward with the autograd graph kept (no recomputation).  The unit's parameters are gathered
+  for the forward, released, and gathered again when the first gradient reaches the unit's outputs;
+  the autograd nodes inside hold the Parameter objects, whose storage the engine re-points, so
+  they read the re-gathered values.  Gradients are reduced when the gradient of the unit's inputs
+  is complete."""
+  idx = [i for i, a in enumerate(args) if isinstance(a, torch.Tensor) and a.requires_grad]
+  call = list(args)
+  wrapped = _PostBackwardFn.apply(engine, u, *[args[i] for i in idx])
+  for i, t in zip(idx, wrapped):
+    call[i] = t
+  measure = engine.is_cuda and engine.remat_policy == "auto" and engine._remat_unit_bytes is None
+  before = torch.cuda.memory_allocated(engine.device) if measure else 0
+  engine.pre_forward(u)
+  out = u.orig_forward(*call, **kwargs)
+  engine.post_forward(u)
+  if measure:
+    engine.note_saved_unit_bytes(torch.cuda.memory_allocated(engine.device) - before)
+  outs = out if isinstance(out, tuple) else (out,)
+  t_idx = [i for i, o in enumerate(outs) if isinstance(o, torch.Tensor) and o.requires_grad]
+  hooked = _PreBackwardFn.apply(engine, u, *[outs[i] for i in t_idx])
+  outs = list(outs)
+  for i, t in zip(t_idx, hooked):
+    outs[i] = t
+  return tuple(outs) if isinstance(out, tuple) else outs[0]
+
+
+class _PreBackwardFn(torch.autograd.Function):
+  """Identity on a unit's outputs; its backward runs before any node inside the unit."""
+
+  @staticmethod
+  def forward(ctx, engine, u, *outs):
+    ctx.engine, ctx.unit = engine, u
+    return tuple(o.view_as(o) for o in outs)
+
+  @staticmethod
+  def backward(ctx, *grads):
+    ctx.engine.pre_backward(ctx.unit)
+    return (None, None, *grads)
+
+
+class _PostBackwardFn(torch.autograd.Function):
+  """Identity on a unit's differentiable inputs; its backward runs after every node inside the
+  unit that lies on a path to those inputs, i.e. after all of the unit's parameter gradients."""
+
+  @staticmethod
+  def forward(ctx, engine, u, *ins):
+    ctx.engine, ctx.unit = engine, u
+    return tuple(t.view_as(t) for t in ins)
+
+  @staticmethod
+  def backward(ctx, *grads):
+    _collect_leaf_grads(ctx.unit)
+    ctx.engine.post_backward(ctx.unit)
+    return (None, None, *grads)
 
 
 def _split_tensors(args):

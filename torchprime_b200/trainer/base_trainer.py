@@ -46,6 +46,18 @@ logger = logging.getLogger(__name__)
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}
 
 
+def _remat_policy(v):
+  """``engine.remat_layers``: all | none | auto | <number of layers that recompute>."""
+  if isinstance(v, bool):
+    return "all" if v else "none"
+  if isinstance(v, int):
+    return v
+  v = str(v).lower()
+  if v in ("all", "none", "auto"):
+    return v
+  return int(v)
+
+
 class Trainer:
   minibatch: bool
 
@@ -80,7 +92,8 @@ class Trainer:
       grad_dtype=_DTYPES[eng.grad_dtype] if eng.get("grad_dtype", None) else None,
       master_weights=bool(eng.get("master_weights", True)),
       remat_classes=self.remat_plan.remat_classes, offload_tensors=self.remat_plan.offload_tensors,
-      seed=int(self.config.get("seed", 42)), fused_collectives=bool(eng.get("fused_collectives", False)))
+      seed=int(self.config.get("seed", 42)), fused_collectives=bool(eng.get("fused_collectives", False)),
+      remat_policy=_remat_policy(eng.get("remat_layers", "auto")))
     _move_buffers(model, self.device)
     if hasattr(model, "return_logits"):
       model.return_logits = not bool(eng.get("chunked_ce", True))
