@@ -55,8 +55,11 @@ __device__ __forceinline__ float rbf(float x) { return __bfloat162float(__float2
 // RMSNorm
 // ----------------------------------------------------------------------------
 constexpr int NORM_THREADS = 256;
-constexpr int NORM_VPT = 4;  // 16-byte vectors kept in registers per thread (dim <= 8192)
-
+constexpr int NORM_VPT = 4;  // most 16-byte vectors kept in registers per thread (dim <= 8192)
+// The kernels are instantiated for 1, 2 and 4 vectors per thread: a 4096-wide row needs two, and
+// the instantiation that holds exactly that many leaves registers for more resident CTAs, which
+// is what a latency-bound row-per-CTA kernel needs to fill the memory pipe.
+template <int VPT>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_fwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res, const uint4* __restrict__ w,
                    uint4* __restrict__ y, uint4* __restrict__ h_out, float* __restrict__ rstd_out, int rows,
@@ -64,10 +67,10 @@ rmsnorm_fwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res, c
   __shared__ float red[32];
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const uint4* xr = x + (size_t)row * nvec;
-    float vals[NORM_VPT][8];
+    float vals[VPT][8];
     float ss = 0.f;
 #pragma unroll
-    for (int j = 0; j < NORM_VPT; ++j) {
+    for (int j = 0; j < VPT; ++j) {
       int i = threadIdx.x + j * NORM_THREADS;
       if (i < nvec) {
         unpack8(xr[i], vals[j]);
@@ -86,7 +89,7 @@ rmsnorm_fwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res, c
     const float rstd = rsqrtf(ss / (float)(nvec * 8) + eps);
     if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
 #pragma unroll
-    for (int j = 0; j < NORM_VPT; ++j) {
+    for (int j = 0; j < VPT; ++j) {
       int i = threadIdx.x + j * NORM_THREADS;
       if (i < nvec) {
         float wv[8], o[8];
@@ -99,15 +102,16 @@ rmsnorm_fwd_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res, c
   }
 }
 
+template <int VPT>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, const uint4* __restrict__ w,
                    const float* __restrict__ rstd, const uint4* __restrict__ dres, uint4* __restrict__ dx,
                    float* __restrict__ dw, int rows, int nvec) {
   __shared__ float red[32];
-  float dw_acc[NORM_VPT][8];
-  float wv[NORM_VPT][8];
+  float dw_acc[VPT][8];
+  float wv[VPT][8];
 #pragma unroll
-  for (int j = 0; j < NORM_VPT; ++j) {
+  for (int j = 0; j < VPT; ++j) {
     int i = threadIdx.x + j * NORM_THREADS;
 #pragma unroll
     for (int e = 0; e < 8; ++e) dw_acc[j][e] = 0.f;
@@ -116,10 +120,10 @@ rmsnorm_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, co
   const float inv_d = 1.0f / (float)(nvec * 8);
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
     const float rs = rstd[row];
-    float g[NORM_VPT][8], xh[NORM_VPT][8];
+    float g[VPT][8], xh[VPT][8];
     float dot = 0.f;
 #pragma unroll
-    for (int j = 0; j < NORM_VPT; ++j) {
+    for (int j = 0; j < VPT; ++j) {
       int i = threadIdx.x + j * NORM_THREADS;
       if (i < nvec) {
         float dyv[8], xv[8];
@@ -136,7 +140,7 @@ rmsnorm_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, co
     }
     dot = block_sum(dot, red) * inv_d;
 #pragma unroll
-    for (int j = 0; j < NORM_VPT; ++j) {
+    for (int j = 0; j < VPT; ++j) {
       int i = threadIdx.x + j * NORM_THREADS;
       if (i < nvec) {
         float o[8];
@@ -154,11 +158,17 @@ rmsnorm_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, co
   }
   if (dw) {
 #pragma unroll
-    for (int j = 0; j < NORM_VPT; ++j) {
+    for (int j = 0; j < VPT; ++j) {
       int i = threadIdx.x + j * NORM_THREADS;
       if (i < nvec) {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) atomicAdd(&dw[i * 8 + e], dw_acc[j][e]);
+        // two 16-byte vector reductions instead of eight scalar atomics
+        float* dst = dw + i * 8;
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(dw_acc[j][0]), "f"(dw_acc[j][1]),
+                     "f"(dw_acc[j][2]), "f"(dw_acc[j][3])
+                     : "memory");
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4), "f"(dw_acc[j][4]),
+                     "f"(dw_acc[j][5]), "f"(dw_acc[j][6]), "f"(dw_acc[j][7])
+                     : "memory");
       }
     }
   }
@@ -462,6 +472,18 @@ inline int grid_for(long long work_items, int threads, int waves = 8) {
 }
 inline int rc(cudaError_t e) { return e == cudaSuccess ? 0 : 1000 + (int)e; }
 
+static void launch_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                               void* dx, float* dw_f32, int rows, int dim, cudaStream_t stream) {
+  const int nvec = dim / 8;
+  const int vpt = (nvec + NORM_THREADS - 1) / NORM_THREADS;
+  const int per_sm = vpt <= 2 ? 4 : 2;
+  const int grid = rows < sm_count() * per_sm ? rows : sm_count() * per_sm;
+#define TPB_LAUNCH_NORM_BWD(V) rmsnorm_bwd_kernel<V><<<grid, NORM_THREADS, 0, stream>>>( \
+      (const uint4*)dy, (const uint4*)x, (const uint4*)w, rstd, (const uint4*)dres, (uint4*)dx, dw_f32, rows, nvec)
+  if (vpt <= 1) TPB_LAUNCH_NORM_BWD(1); else if (vpt == 2) TPB_LAUNCH_NORM_BWD(2); else TPB_LAUNCH_NORM_BWD(4);
+#undef TPB_LAUNCH_NORM_BWD
+}
+
 }  // namespace tpb
 
 using namespace tpb;
@@ -471,9 +493,14 @@ extern "C" int tpb_rmsnorm_fwd(const void* x, const void* res, const void* w, vo
                                int rows, int dim, float eps, void* stream) {
   if (dim % 8 || dim > 8 * NORM_THREADS * NORM_VPT) return -2;
   if (rows <= 0) return 0;
-  int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
-  rmsnorm_fwd_kernel<<<grid, NORM_THREADS, 0, STREAM(stream)>>>(
-      (const uint4*)x, (const uint4*)res, (const uint4*)w, (uint4*)y, (uint4*)h_out, rstd, rows, dim / 8, eps);
+  const int nvec = dim / 8;
+  const int vpt = (nvec + NORM_THREADS - 1) / NORM_THREADS;
+  const int per_sm = vpt <= 2 ? 8 : 4;
+  const int grid = rows < sm_count() * per_sm ? rows : sm_count() * per_sm;
+#define TPB_LAUNCH_NORM_FWD(V) rmsnorm_fwd_kernel<V><<<grid, NORM_THREADS, 0, STREAM(stream)>>>( \
+      (const uint4*)x, (const uint4*)res, (const uint4*)w, (uint4*)y, (uint4*)h_out, rstd, rows, nvec, eps)
+  if (vpt <= 1) TPB_LAUNCH_NORM_FWD(1); else if (vpt == 2) TPB_LAUNCH_NORM_FWD(2); else TPB_LAUNCH_NORM_FWD(4);
+#undef TPB_LAUNCH_NORM_FWD
   return rc(cudaGetLastError());
 }
 
@@ -481,10 +508,7 @@ extern "C" int tpb_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
                                void* dx, float* dw_f32, int rows, int dim, void* stream) {
   if (dim % 8 || dim > 8 * NORM_THREADS * NORM_VPT) return -2;
   if (rows <= 0) return 0;
-  int grid = rows < sm_count() * 4 ? rows : sm_count() * 4;
-  rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, STREAM(stream)>>>((const uint4*)dy, (const uint4*)x, (const uint4*)w,
-                                                                rstd, (const uint4*)dres, (uint4*)dx, dw_f32, rows,
-                                                                dim / 8);
+  launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw_f32, rows, dim, STREAM(stream));
   return rc(cudaGetLastError());
 }
 
@@ -634,9 +658,7 @@ extern "C" int tpb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
   cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(float) * dim, s);
   if (e != cudaSuccess) return 1000 + (int)e;
   if (rows > 0) {
-    int grid = rows < sm_count() * 4 ? rows : sm_count() * 4;
-    rmsnorm_bwd_kernel<<<grid, NORM_THREADS, 0, s>>>((const uint4*)dy, (const uint4*)x, (const uint4*)w, rstd,
-                                                     (const uint4*)dres, (uint4*)dx, scratch, rows, dim / 8);
+    launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, scratch, rows, dim, s);
     e = cudaGetLastError();
     if (e != cudaSuccess) return 1000 + (int)e;
   }
