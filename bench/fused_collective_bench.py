@@ -55,8 +55,10 @@ def main():
   out = {}
 
   # ---- F1: all-gather fused into the QKV GEMM
-  ag = fc.AllGatherGemm(sb, shard, copiers=int(os.environ.get("TPB_AG_COPIERS", "16")))
+  ag = fc.AllGatherGemm(sb, shard, copiers=int(os.environ.get("TPB_AG_COPIERS", "32")))
   t_fused = timed(lambda: ag(x, gathered, 0, HQKV, D), pre=sb.barrier)
+  agp = fc.AllGatherGemm(sb, shard, copiers=int(os.environ.get("TPB_AG_COPIERS", "32")), push=True)
+  t_push = timed(lambda: agp(x, None, 0, HQKV, D), pre=sb.barrier)
   def nccl_then_gemm():
     dist.all_gather_into_tensor(gathered, sb.local)
     k.gemm(x, gathered[:HQKV * D].view(HQKV, D))
@@ -65,7 +67,8 @@ def main():
   flops = 2.0 * T * HQKV * D
   link_bytes = (world - 1) * shard * 2
   roof = max(flops / (peak * 1e12), link_bytes / (NVLINK_GBS * 1e9)) * 1e3
-  out["ag_gemm"] = {"fused_ms": t_fused, "nccl_allgather_plus_gemm_ms": t_nccl, "gemm_only_ms": t_gemm,
+  out["ag_gemm"] = {"fused_push_ms": t_push, "fraction_of_roofline_push": roof / t_push,
+                    "fused_pull_ms": t_fused, "nccl_allgather_plus_gemm_ms": t_nccl, "gemm_only_ms": t_gemm,
                     "roofline_ms": roof, "fraction_of_roofline": roof / t_fused, "nvlink_bytes_in": link_bytes,
                     "copier_ctas": ag.copiers}
 

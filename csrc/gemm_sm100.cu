@@ -74,6 +74,12 @@ struct GemmParams {
   unsigned* ag_flags;           // [ag_world * chunks_per_shard], value = epoch when ready
   unsigned ag_epoch;
   int ag_local;                 // rank whose shard already sits in ag_dst (not copied, not waited for); -1: none
+  // Push mode (ag_push != 0): the copier CTAs of rank ag_local read ITS OWN shard and store it into
+  // every peer's gathered buffer (posted writes, no round trip per chunk), then raise the flag in
+  // the peer's flag array; each rank waits on flags in its own memory.
+  int ag_push;
+  void* ag_push_dst[8];         // gathered buffer of every rank (symmetric memory)
+  unsigned* ag_push_flags[8];   // flag array of every rank (symmetric memory)
   // Reduce-scatter fusion (TPB_EPI_RS_BF16): the epilogue adds alpha * acc straight into the
   // owner's bf16 gradient shard over P2P with vector red.add.
   int rs_world;
@@ -141,7 +147,7 @@ __device__ __forceinline__ bool ag_wait_range(const GemmParams& p, long long lo,
     long long t0 = 0;
     int spins = 0;
     while (true) {
-      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
       if (v == p.ag_epoch) break;
       if (++spins == 64) {
         spins = 0;
@@ -226,6 +232,72 @@ __device__ void ag_copier(const GemmParams& p, uint8_t* smem) {
 // the even CTA issues tcgen05.mma.cta_group::2 (M = 256) for both, and each CTA drains its own
 // 128 accumulator rows.  Shared-memory traffic per FLOP drops by a third, which is what bounds
 // the single-CTA kernel (TMA writes plus operand reads exceed 128 B/clk).  Dense mode only.
+// Push-mode copier CTA: chunks c, c+G, ... of the local shard go  local memory -> shared memory ->
+// every peer's gathered buffer (plain bulk stores to peer memory), then the chunk's flag is raised
+// in every peer's flag array.
+__device__ void ag_pusher(const GemmParams& p, uint8_t* smem) {
+  constexpr int SLOTS = 6;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SLOTS * 32768);
+  if (threadIdx.x != 0) return;
+  for (int i = 0; i < SLOTS; ++i) mbar_init(&bars[i], 1);
+  fence_barrier_init();
+  const long long cps = ag_chunks_per_shard(p);
+  const int G = p.ag_copiers, c = blockIdx.x;
+  const long long mine = (cps - c + G - 1) / G;
+  const int me = p.ag_local;
+  auto geom = [&](long long k, long long& j, long long& off, uint32_t& bytes) {
+    j = c + k * G;
+    off = j * p.ag_chunk_elems;
+    bytes = (uint32_t)(min(p.ag_chunk_elems, p.ag_shard_elems - off) * 2);
+  };
+  auto issue_load = [&](long long k) {
+    long long j, off; uint32_t bytes;
+    geom(k, j, off, bytes);
+    const int slot = (int)(k % SLOTS);
+    mbar_expect_tx(&bars[slot], bytes);
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(smem + slot * 32768)),
+                 "l"(reinterpret_cast<const uint8_t*>(p.ag_src[me]) + off * 2), "r"(bytes), "r"(smem_u32(&bars[slot]))
+                 : "memory");
+  };
+  auto publish = [&](long long k) {
+    long long j, off; uint32_t bytes;
+    geom(k, j, off, bytes);
+    asm volatile("fence.proxy.async;" ::: "memory");
+    __threadfence_system();
+    for (int r = 0; r < p.ag_world; ++r) {
+      if (r == me) continue;
+      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ag_push_flags[r] + me * cps + j), "r"(p.ag_epoch)
+                   : "memory");
+    }
+  };
+  // Up to DEPTH chunks of stores are in flight (a remote store group takes a round trip to
+  // complete); the remaining slots of the ring prefetch the next local chunks.
+  constexpr int DEPTH = 4;
+  for (long long k = 0; k < mine && k < SLOTS; ++k) issue_load(k);
+  for (long long k = 0; k < mine; ++k) {
+    const int slot = (int)(k % SLOTS);
+    if (!mbar_wait(&bars[slot], (uint32_t)((k / SLOTS) & 1), p.status, kTimeoutTmaFull, 7)) return;
+    long long j, off; uint32_t bytes;
+    geom(k, j, off, bytes);
+    for (int r = 0; r < p.ag_world; ++r) {
+      if (r == me) continue;
+      uint8_t* dst = reinterpret_cast<uint8_t*>(p.ag_push_dst[r]) + ((long long)me * p.ag_shard_elems + off) * 2;
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+                   "r"(smem_u32(smem + slot * 32768)), "r"(bytes)
+                   : "memory");
+    }
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    if (k >= DEPTH) {
+      asm volatile("cp.async.bulk.wait_group 4;" ::: "memory");   // the stores of chunk k-DEPTH are complete
+      publish(k - DEPTH);
+      if (k - DEPTH + SLOTS < mine) issue_load(k - DEPTH + SLOTS);
+    }
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  for (long long k = (mine > DEPTH ? mine - DEPTH : 0); k < mine; ++k) publish(k);
+}
+
 template <bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -244,7 +316,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (!PAIR && (int)blockIdx.x < p.ag_copiers) {
-    ag_copier(p, smem);
+    if (p.ag_push) ag_pusher(p, smem); else ag_copier(p, smem);
     return;
   }
   const int rank = PAIR ? (int)cluster_ctarank() : 0;    // 0: issues the MMAs of the pair
@@ -655,6 +727,7 @@ struct GemmCall {
   // fusion with collectives (0 / null when unused)
   int ag_world, ag_copiers, ag_local; const void* const* ag_src; void* ag_dst; long long ag_shard_elems, ag_b_offset;
   unsigned* ag_flags; unsigned ag_epoch;
+  void* const* ag_push_dst; unsigned* const* ag_push_flags;
   int rs_world; void* const* rs_dst; long long rs_shard_elems, rs_c_offset;
 };
 
@@ -708,13 +781,17 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.ag_dst = g.ag_dst; p.ag_shard_elems = g.ag_shard_elems; p.ag_chunk_elems = 16384; p.ag_b_offset = g.ag_b_offset;
   p.ag_flags = g.ag_flags; p.ag_epoch = g.ag_epoch; p.ag_local = g.ag_world > 0 ? g.ag_local : -1;
   p.rs_world = g.rs_world; p.rs_shard_elems = g.rs_shard_elems; p.rs_c_offset = g.rs_c_offset;
+  p.ag_push = (g.ag_world > 0 && g.ag_push_dst != nullptr && g.ag_push_flags != nullptr) ? 1 : 0;
   for (int i = 0; i < 8; ++i) {
+    p.ag_push_dst[i] = (p.ag_push && i < g.ag_world) ? g.ag_push_dst[i] : nullptr;
+    p.ag_push_flags[i] = (p.ag_push && i < g.ag_world) ? g.ag_push_flags[i] : nullptr;
     p.ag_src[i] = (g.ag_world > 0 && i < g.ag_world) ? g.ag_src[i] : nullptr;
     p.rs_dst[i] = (g.rs_world > 0 && i < g.rs_world) ? g.rs_dst[i] : nullptr;
   }
   if (g.ag_world > 0) {
     if (g.ag_world > 8 || g.b_mn || g.mode != 0) return -2;
     if (g.ldb != g.K || (g.ag_shard_elems % 8) || p.ag_copiers < 1 || p.ag_copiers >= sm_count()) return -2;
+    if (p.ag_push && (g.ag_local < 0 || g.ag_local >= g.ag_world)) return -2;
   }
   if (g.epi == TPB_EPI_RS_BF16) {
     if (g.rs_world < 1 || g.rs_world > 8 || (g.N % 8) || (g.ldc % 8) || (g.rs_shard_elems % 8) || (g.rs_c_offset % 8))
@@ -811,11 +888,14 @@ extern "C" int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B
 // row-major [N, K] matrix.  `flags` has world * ceil(shard_elems / 16384) entries (local memory,
 // zero-initialised once); pass a fresh non-zero `epoch` per call.  The whole buffer is gathered.
 // local_rank >= 0: that rank's shard is already in `gathered` (it is neither copied nor waited for).
+// push_gathered / push_flags (both non-null): push mode, tables of every rank's gathered buffer and
+// flag array in symmetric memory (`gathered` and `flags` are this rank's entries); the copier CTAs
+// then send the local shard to the peers instead of fetching theirs.
 extern "C" int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int epi,
                                 const void* aux, long long ldaux, void* c2, long long ldc2,
                                 const void* const* shard_ptrs, int world, long long shard_elems, void* gathered,
                                 long long b_offset, unsigned* flags, unsigned epoch, int copiers, int local_rank,
-                                void* stream_) {
+                                void* const* push_gathered, unsigned* const* push_flags, void* stream_) {
   GemmCall g{};
   g.A = A; g.B = reinterpret_cast<const __nv_bfloat16*>(gathered) + b_offset; g.B2 = nullptr; g.C = C;
   g.M = M; g.N = N; g.K = K; g.E = 1;
@@ -825,6 +905,7 @@ extern "C" int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, lon
   g.ag_world = world; g.ag_copiers = copiers; g.ag_src = shard_ptrs; g.ag_dst = gathered;
   g.ag_shard_elems = shard_elems; g.ag_b_offset = b_offset; g.ag_flags = flags; g.ag_epoch = epoch;
   g.ag_local = local_rank;
+  g.ag_push_dst = push_gathered; g.ag_push_flags = push_flags;
   return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
 }
 

@@ -99,7 +99,8 @@ int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B2, void* C,
 int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int epi,
                      const void* aux, long long ldaux, void* c2, long long ldc2, const void* const* shard_ptrs,
                      int world, long long shard_elems, void* gathered, long long b_offset, unsigned* flags,
-                     unsigned epoch, int copiers, int local_rank, void* stream);
+                     unsigned epoch, int copiers, int local_rank, void* const* push_gathered,
+                     unsigned* const* push_flags, void* stream);
 int tpb_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, long long ldc,
                      int a_mn, int b_mn, float alpha, void* const* shard_ptrs, int world, long long shard_elems,
                      long long c_offset, void* stream);

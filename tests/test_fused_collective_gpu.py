@@ -44,6 +44,19 @@ def _worker(rank, world, port, results):
       err = ((y.float() - want).norm() / want.norm()).item()
       assert err < 1e-2, f"ag_gemm rel err {err}"
       assert torch.equal(gathered, full), "gathered buffer differs from the concatenated shards"
+    # ---- push mode: every rank sends its shard, flags are raised in the peers' memory
+    agp = fc.AllGatherGemm(sb, shard, copiers=4, push=True)
+    for it in range(2):
+      agp.gathered.zero_()
+      torch.cuda.synchronize()
+      sb.barrier()
+      y = agp(x, None, 0, N, K)
+      torch.cuda.synchronize()
+      sb.barrier()
+      torch.cuda.synchronize()
+      err = ((y.float() - want).norm() / want.norm()).item()
+      assert err < 1e-2, f"ag_gemm (push) rel err {err}"
+      assert torch.equal(agp.gathered, full), "pushed gathered buffer differs from the concatenated shards"
     # ---- reduce-scatter fused into a wgrad-layout GEMM
     T, Nw, Kw = 768, 512, 256
     c_off = 8 * 5

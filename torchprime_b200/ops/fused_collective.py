@@ -24,7 +24,7 @@ from . import _lib
 from ._lib import check, lib, ptr, stream_ptr
 
 P, I, LL, FL, U = c_void_p, c_int, c_longlong, c_float, c_uint
-_lib.register_signature("tpb_ag_gemm_bf16", [P, P, I, I, I, LL, LL, I, P, LL, P, LL, P, I, LL, P, LL, P, U, I, I, P])
+_lib.register_signature("tpb_ag_gemm_bf16", [P, P, I, I, I, LL, LL, I, P, LL, P, LL, P, I, LL, P, LL, P, U, I, I, P, P, P])
 _lib.register_signature("tpb_gemm_rs_bf16", [P, P, I, I, I, LL, LL, LL, I, I, FL, P, I, LL, LL, P])
 
 CHUNK_ELEMS = 16384
@@ -37,14 +37,29 @@ def num_flags(world: int, shard_elems: int) -> int:
 class AllGatherGemm:
   """State for repeated fused all-gather + GEMM calls on one sharded flat buffer."""
 
-  def __init__(self, shard_buffer, shard_elems: int, copiers: int = 16):
+  def __init__(self, shard_buffer, shard_elems: int, copiers: int = 32, push: bool = False):
+    """``push``: every rank sends its shard to the peers (posted stores over NVLink) instead of
+    fetching theirs.  The gathered buffer and the flags then live in symmetric memory owned by this
+    object (``self.gathered``), and the ranks must be synchronised between two calls (nobody may
+    still be reading the previous gather when the next one starts to arrive)."""
     self.sb = shard_buffer                     # dist.symm.SymmetricBuffer holding this rank's shard
     self.world = shard_buffer.world
     self.shard_elems = shard_elems
     self.copiers = copiers
+    self.push = push
     dev = shard_buffer.local.device
-    self.flags = torch.zeros(num_flags(self.world, shard_elems), dtype=torch.int32, device=dev)
     self.epoch = 0
+    if push:
+      from ..dist.symm import SymmetricBuffer
+      self.gathered_sb = SymmetricBuffer(shard_elems * self.world, torch.bfloat16, dev, group=shard_buffer.group)
+      self.flags_sb = SymmetricBuffer(num_flags(self.world, shard_elems), torch.int32, dev, group=shard_buffer.group)
+      self.flags_sb.local.zero_()
+      self.gathered = self.gathered_sb.local
+      self.flags = self.flags_sb.local
+      self.flags_sb.barrier()
+    else:
+      self.gathered = None
+      self.flags = torch.zeros(num_flags(self.world, shard_elems), dtype=torch.int32, device=dev)
 
   def __call__(self, x2d, gathered, b_offset: int, n: int, k: int, shard_offset: int = 0, out=None,
                epi=_lib.EPI_BF16, aux=None, c2=None):
@@ -52,6 +67,8 @@ class AllGatherGemm:
     ``shard_elems`` elements (starting ``shard_offset`` elements into its symmetric buffer)."""
     m = x2d.shape[0]
     self.epoch += 1
+    if self.push:
+      gathered = self.gathered
     if out is None:
       out = torch.empty(m, n // 2 if epi == _lib.EPI_SWIGLU else n, dtype=torch.bfloat16, device=x2d.device)
     table = self.sb.ptr_table(shard_offset)
@@ -61,7 +78,9 @@ class AllGatherGemm:
     rc = lib().tpb_ag_gemm_bf16(ptr(x2d), ptr(out), m, n, k, x2d.stride(0), out.stride(0), epi, ptr(aux),
                                 aux.stride(0) if aux is not None else 0, ptr(c2), c2.stride(0) if c2 is not None else 0,
                                 table, self.world, self.shard_elems, ptr(gathered), b_offset, ptr(self.flags),
-                                self.epoch, self.copiers, rank, stream_ptr())
+                                self.epoch, self.copiers, rank,
+                                self.gathered_sb.ptr_table() if self.push else None,
+                                self.flags_sb.ptr_table() if self.push else None, stream_ptr())
     check(rc, f"ag_gemm M={m} N={n} K={k} world={self.world}")
     return out
 
