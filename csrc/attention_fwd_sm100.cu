@@ -20,6 +20,8 @@
 // query of the tile can see are skipped; only blocks that straddle a mask edge pay for
 // per-element masking.
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tpb.h"
 
@@ -323,6 +325,359 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Head dim 128: two 128-row query tiles per CTA, 128-key steps.
+//
+// Every MMA is 128 x 128 x 16 (full tensor rate with operands in shared memory; the 64-key steps
+// of the kernel above are bound by operand fetch), each K/V tile is loaded once for 256 query
+// rows, and the two tiles alternate on the tensor core: while the softmax warps of tile a work on
+// step j, the tensor core runs P V and the next Q K^T of tile b.
+//
+//   warp 0      TMA producer: both Q tiles once, then 2-stage rings of 128-key K and V tiles.
+//   warp 1      MMA issuer.  Per step j and tile x: O_x += P_x(j) V_j, then S_x(j+1) = Q_x K_{j+1}^T
+//               into the columns P_x(j) has just been read from (S and P share TMEM columns).
+//   warps 2-5   softmax of tile a (thread = query row), warps 6-9 softmax of tile b.
+//   TMEM        S_a [0,128)  S_b [128,256)  O_a [256,384)  O_b [384,512)
+// ------------------------------------------------------------------------------------------
+// 2^x for x <= 0 on the FMA pipe (no MUFU): round-to-nearest split x = n + f with the 1.5 * 2^23
+// trick, a degree-3 polynomial for 2^f on [-0.5, 0.5] (relative error 8e-5, far below the bf16
+// rounding of the result) and an integer add of n into the exponent.  -inf gives 0.
+__device__ __forceinline__ float exp2_fma(float x) {
+  x = fmaxf(x, -125.f);
+  const float fl = x + 12582912.f;
+  const float f = x - (fl - 12582912.f);
+  float pl = fmaf(0.05508868f, f, 0.24260405f);
+  pl = fmaf(pl, f, 0.69327623f);
+  pl = fmaf(pl, f, 0.99992895f);
+  return __int_as_float(__float_as_int(pl) + (__float_as_int(fl) << 23));
+}
+
+constexpr int F2_T = 128;                 // tile edge: rows per query tile, keys per step
+constexpr int F2_THREADS = 320;
+constexpr int F2_TILE_BYTES = F2_T * 128 * 2;   // 32 KB
+namespace f2 {
+constexpr int OFF_Q = 0;                          // two tiles
+constexpr int OFF_K = 2 * F2_TILE_BYTES;          // two stages
+constexpr int OFF_V = OFF_K + 2 * F2_TILE_BYTES;
+constexpr int OFF_BAR = OFF_V + 2 * F2_TILE_BYTES;
+constexpr int TOTAL = OFF_BAR + 256 + 1024;
+}  // namespace f2
+
+__global__ void __launch_bounds__(F2_THREADS, 1)
+attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const AttnFwdParams p) {
+  using namespace f2;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint64_t* q_full = bars;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* k_empty = bars + 3;   // [2]
+  uint64_t* v_full = bars + 5;    // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2 tiles]
+  uint64_t* p_full = bars + 11;   // [2 tiles], count 128
+  uint64_t* o_done = bars + 13;   // [2 tiles]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  int* tile_minmax = reinterpret_cast<int*>(bars + 16);  // [2 tiles][2]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_ctiles = (p.Sq + 2 * F2_T - 1) / (2 * F2_T);
+  const int ct = n_ctiles - 1 - (int)(blockIdx.x / (p.Hq * p.B));   // heaviest (latest) rows first
+  const int hq = (blockIdx.x / p.B) % p.Hq, b = blockIdx.x % p.B;
+  const int hkv = hq / (p.Hq / p.Hkv);
+  const int q0 = ct * 2 * F2_T;
+  const int pos_off = p.Sk - p.Sq;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 128); mbar_init(&o_done[i], 1);
+      tile_minmax[2 * i] = 0x7fffffff;
+      tile_minmax[2 * i + 1] = -0x7fffffff;
+    }
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // position range of each query tile
+  if (threadIdx.x < 2 * F2_T) {
+    const int r = q0 + threadIdx.x;
+    if (r < p.Sq) {
+      const int qp = p.q_pos ? p.q_pos[(long long)b * p.Sq + r] : r + pos_off;
+      atomicMin(&tile_minmax[2 * (threadIdx.x / F2_T)], qp);
+      atomicMax(&tile_minmax[2 * (threadIdx.x / F2_T) + 1], qp);
+    }
+  }
+  __syncthreads();
+  const int nblk_total = (p.Sk + F2_T - 1) / F2_T;
+  int lo[2], hi[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int mn = tile_minmax[2 * x], mx = tile_minmax[2 * x + 1];
+    hi[x] = p.causal ? min(nblk_total, mx / F2_T + 1) : nblk_total;
+    lo[x] = (p.window > 0) ? max(0, (mn - p.window + 1) / F2_T) : 0;
+    if (mx < 0) hi[x] = 0;
+    if (hi[x] <= lo[x]) { lo[x] = 0; hi[x] = 0; }
+  }
+  const int any = (hi[0] > lo[0]) || (hi[1] > lo[1]);
+  const int blk_lo = !any ? 0 : ((hi[0] > lo[0] && hi[1] > lo[1]) ? min(lo[0], lo[1]) : (hi[0] > lo[0] ? lo[0] : lo[1]));
+  const int blk_hi = max(hi[0], hi[1]);
+  const int nblk = any ? blk_hi - blk_lo : 0;
+  auto active = [&](int x, int j) { const int blk = blk_lo + j; return blk >= lo[x] && blk < hi[x]; };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0 && nblk > 0) {
+      tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, 2 * F2_TILE_BYTES);
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          tma_load_3d(smem + OFF_Q + x * F2_TILE_BYTES + c * (F2_T * 128), &tmQ, q_full, c * 64,
+                      b * p.Sq + q0 + x * F2_T, hq);
+      for (int j = 0; j < nblk; ++j) {
+        const int s = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int row = b * p.Sk + (blk_lo + j) * F2_T;
+        if (!mbar_wait(&k_empty[s], ph ^ 1, p.status, kTimeoutStageFree, 41)) break;
+        mbar_expect_tx(&k_full[s], F2_TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          tma_load_3d(smem + OFF_K + s * F2_TILE_BYTES + c * (F2_T * 128), &tmK, &k_full[s], c * 64, row, hkv);
+        if (!mbar_wait(&v_empty[s], ph ^ 1, p.status, kTimeoutStageFree, 42)) break;
+        mbar_expect_tx(&v_full[s], F2_TILE_BYTES);
+#pragma unroll
+        for (int c = 0; c < 2; ++c)
+          tma_load_3d(smem + OFF_V + s * F2_TILE_BYTES + c * (F2_T * 128), &tmV, &v_full[s], c * 64, row, hkv);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0 && nblk > 0) {
+      constexpr uint32_t id_qk = make_idesc_bf16(F2_T, F2_T, false, false);
+      constexpr uint32_t id_pv = make_idesc_bf16(F2_T, FWD_DV, false, true);
+      constexpr uint32_t hi_w = smem_desc_hi(1024);
+      const uint32_t qlo[2] = {smem_desc_lo(smem_u32(smem + OFF_Q), 16),
+                               smem_desc_lo(smem_u32(smem + OFF_Q + F2_TILE_BYTES), 16)};
+      const uint32_t k0 = smem_u32(smem + OFF_K), v0 = smem_u32(smem + OFF_V);
+      bool ok = mbar_wait(q_full, 0, p.status, kTimeoutTmaFull, 43);
+      tc_fence_after();
+      int steps[2] = {0, 0};   // steps issued per tile (barrier phases)
+      auto issue_s = [&](int x, int j) {   // S_x = Q_x K_j^T
+        const uint32_t klo = smem_desc_lo(k0 + (j & 1) * F2_TILE_BYTES, 16);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t kk = (uint32_t)(((k >> 2) * (F2_T * 128) + (k & 3) * 32) >> 4);
+          mma_ss_w(tmem_base + x * F2_T, qlo[x] + kk, hi_w, klo + kk, hi_w, id_qk, k != 0);
+        }
+        tc_commit(&s_full[x]);
+      };
+      auto issue_pv = [&](int x, int j, bool first) {   // O_x += P_x V_j
+        const uint32_t vlo = smem_desc_lo(v0 + (j & 1) * F2_TILE_BYTES, F2_T * 128);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          mma_ts_w(tmem_base + 256 + x * F2_T, tmem_base + x * F2_T + k * 8, vlo + (uint32_t)((k * 2048) >> 4), hi_w,
+                   id_pv, (!first) | (k != 0));
+        tc_commit(&o_done[x]);
+      };
+      if (ok) ok = mbar_wait(&k_full[0], 0, p.status, kTimeoutTmaFull, 44);
+      tc_fence_after();
+      if (ok) {
+        if (active(0, 0)) issue_s(0, 0);
+        if (active(1, 0)) issue_s(1, 0);
+        tc_commit(&k_empty[0]);
+      }
+      for (int j = 0; j < nblk && ok; ++j) {
+        const int jn = j + 1;
+        bool v_ready = false, k_ready = false;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (active(x, j)) {
+            if (!mbar_wait(&p_full[x], steps[x] & 1, p.status, kTimeoutSoftmax, 45)) { ok = false; break; }
+            if (!v_ready) {
+              if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, p.status, kTimeoutTmaFull, 46)) { ok = false; break; }
+              v_ready = true;
+            }
+            tc_fence_after();
+            issue_pv(x, j, steps[x] == 0);
+            ++steps[x];
+          }
+          if (jn < nblk && active(x, jn)) {
+            if (!k_ready) {
+              if (!mbar_wait(&k_full[jn & 1], (jn >> 1) & 1, p.status, kTimeoutTmaFull, 47)) { ok = false; break; }
+              k_ready = true;
+              tc_fence_after();
+            }
+            issue_s(x, jn);
+          }
+        }
+        if (!ok) break;
+        tc_commit(&v_empty[j & 1]);
+        if (jn < nblk) tc_commit(&k_empty[jn & 1]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue
+    const int x = (warp - 2) >> 2;                // query tile of this warp
+    const int q = warp & 3;                       // TMEM lane quarter
+    const int r_local = q * 32 + lane;
+    const int row = q0 + x * F2_T + r_local;
+    const bool row_ok = row < p.Sq;
+    const long long grow = (long long)b * p.Sq + row;
+    const int qpos = row_ok ? (p.q_pos ? p.q_pos[grow] : row + pos_off) : -1;
+    const int qseg = (p.q_seg && row_ok) ? p.q_seg[grow] : 0;
+    const int qpos_min = tile_minmax[2 * x], qpos_max = tile_minmax[2 * x + 1];
+    const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t tS = tmem_base + x * F2_T + lane_addr, tO = tmem_base + 256 + x * F2_T + lane_addr;
+    const int* ks = p.kv_seg ? p.kv_seg + (long long)b * p.Sk : nullptr;
+    const int win = p.window > 0 ? p.window : 0x7fffffff;
+    const int kmax = p.causal ? min(qpos, p.Sk - 1) : p.Sk - 1;   // keep needs kp <= kmax
+
+    float m_used = -INFINITY;   // maximum the exponentials are currently taken against (log2 units)
+    float l = 0.f;
+    bool ok = true;
+    int step = 0;
+    for (int j = 0; j < nblk && ok; ++j) {
+      if (!active(x, j)) continue;
+      if (!mbar_wait(&s_full[x], step & 1, p.status, kTimeoutAccFull, 48)) { ok = false; break; }
+      tc_fence_after();
+      const int kv0 = (blk_lo + j) * F2_T;
+      const bool need_mask = (p.causal && kv0 + F2_T - 1 > qpos_min) || (kv0 + F2_T > p.Sk) ||
+                             (p.window > 0 && qpos_max - kv0 >= p.window) || p.q_seg != nullptr;
+      // all 128 scores of the row into registers with one wait
+      uint32_t r[128];
+      tmem_ld32(tS, r);
+      tmem_ld32(tS + 32, r + 32);
+      tmem_ld32(tS + 64, r + 64);
+      tmem_ld32(tS + 96, r + 96);
+      tmem_wait_ld();
+      float m_blk = -INFINITY;
+      if (need_mask) {
+#pragma unroll
+        for (int c = 0; c < 128; ++c) {
+          const int kp = kv0 + c;
+          bool keep = (kp <= kmax) & (qpos - kp < win) & row_ok;
+          if (ks) keep = keep & (__ldg(ks + min(kp, p.Sk - 1)) == qseg);
+          r[c] = keep ? r[c] : 0xff800000u;   // -inf
+          m_blk = fmaxf(m_blk, __uint_as_float(r[c]));
+        }
+      } else {
+        // eight independent chains instead of one 128-long dependent one
+        float mx[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mx[e] = __uint_as_float(r[e]);
+#pragma unroll
+        for (int c = 8; c < 128; c += 8)
+#pragma unroll
+          for (int e = 0; e < 8; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(r[c + e]));
+        m_blk = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+      }
+      m_blk *= p.scale_log2;     // scale > 0: max(s) * c == max(s * c)
+      // lazy running maximum
+      float alpha = 1.f;
+      bool rescale = false;
+      if (m_blk > m_used + kRescaleThreshold || (m_used == -INFINITY && m_blk > -INFINITY)) {
+        alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_blk);
+        rescale = (m_used != -INFINITY);
+        m_used = m_blk;
+      }
+      const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+      // the previous P V of this tile must be complete before O is rescaled; the score columns are
+      // free anyway (this S was computed after that P V was issued)
+      if (step > 0) {
+        if (!mbar_wait(&o_done[x], (step - 1) & 1, p.status, kTimeoutAccFull, 49)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+          for (int c = 0; c < FWD_DV / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tO + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st32(tO + c * 32, o);
+          }
+        }
+      }
+      // P = exp2(s * c - m), packed bf16 over the first 64 of the 128 score columns (masked scores
+      // are -inf and give exactly 0)
+      // The exponentials of one step cost 2048 MUFU cycles per scheduler for the two tiles, as much
+      // as the step's MMAs; every fourth one is evaluated on the FMA pipe instead (exp2_fma).
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const float p0 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c]), p.scale_log2, -m_safe));
+          const float p1 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 1]), p.scale_log2, -m_safe));
+          const float p2 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 2]), p.scale_log2, -m_safe));
+          const float p3 = exp2_fma(fmaf(__uint_as_float(r[ch * 32 + c + 3]), p.scale_log2, -m_safe));
+          sums[0] += p0; sums[1] += p1; sums[2] += p2; sums[3] += p3;
+          pk[c / 2] = pack_bf16(p0, p1);
+          pk[c / 2 + 1] = pack_bf16(p2, p3);
+        }
+        tmem_st16(tS + ch * 16, pk);
+      }
+      const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+      l = l * alpha + sum;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_full[x]);
+      ++step;
+    }
+
+    // ---- epilogue: O / l, log-sum-exp
+    if (ok && step > 0) ok = mbar_wait(&o_done[x], (step - 1) & 1, p.status, kTimeoutAccFull, 50);
+    tc_fence_after();
+    const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+    if (row_ok && p.lse) {
+      const float lse = (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : INFINITY;
+      p.lse[((long long)b * p.Hq + hq) * p.Sq + row] = lse;
+    }
+    __nv_bfloat16* orow = p.O + grow * p.ldo + (long long)hq * FWD_DV;
+#pragma unroll 1
+    for (int c = 0; c < FWD_DV / 32; ++c) {
+      uint32_t o[32];
+      if (step > 0 && ok) {
+        tmem_ld32(tO + c * 32, o);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = 0;
+      }
+      if (row_ok) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          float f[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[8 * v + e]) * inv_l;
+          *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) =
+              make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 template <int DQK>
 cudaError_t launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const AttnFwdParams& p,
                        cudaStream_t stream) {
@@ -342,6 +697,7 @@ cudaError_t launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUten
 
 using namespace tpb;
 
+
 // q: [B*Sq, ...] with row pitch ldq and head h at column h*dqk; k, v likewise (v heads are 128 wide).
 extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
                             int Hq, int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv,
@@ -350,6 +706,35 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
   if (dv != 128 || (dqk != 128 && dqk != 192) || Hq % Hkv) return -2;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -2;
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
+  // TPB_ATTN_FWD_V2=1 selects the two-tile, 128-key-step kernel.  It is correct but not yet faster
+  // than the 64-key kernel (0.63 ms against 0.59 ms at B=1, S=8192, 32/8 heads): with ten warps per
+  // CTA a thread gets 168 registers, the 128 scores of a row spill, and the softmax of one step
+  // takes about 2500 clocks against 1024 clocks of MMAs per tile.
+  static const bool use_v2 = []() { const char* v = getenv("TPB_ATTN_FWD_V2"); return v && v[0] == '1'; }();
+  if (dqk == 128 && use_v2) {
+    // two query tiles per CTA, 128-key steps
+    CUtensorMap tq, tk, tv;
+    if (make_tmap_3d(&tq, q, dqk, (uint64_t)B * Sq, Hq, ldq, dqk, 64, F2_T)) return -3;
+    if (make_tmap_3d(&tk, k, dqk, (uint64_t)B * Sk, Hkv, ldk, dqk, 64, F2_T)) return -4;
+    if (make_tmap_3d(&tv, v, dv, (uint64_t)B * Sk, Hkv, ldv, dv, 64, F2_T)) return -5;
+    AttnFwdParams p;
+    p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.causal = causal; p.window = window;
+    p.q_pos = q_pos; p.q_seg = q_seg; p.kv_seg = kv_seg;
+    p.O = reinterpret_cast<__nv_bfloat16*>(o); p.ldo = ldo; p.lse = lse;
+    p.status = status_block();
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, f2::TOTAL);
+      if (e != cudaSuccess) return 1000 + (int)e;
+      configured = true;
+    }
+    const int n_ctiles = (Sq + 2 * F2_T - 1) / (2 * F2_T);
+    attn_fwd2_kernel<<<n_ctiles * Hq * B, F2_THREADS, f2::TOTAL, reinterpret_cast<cudaStream_t>(stream_)>>>(tq, tk, tv, p);
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? 0 : 1000 + (int)e;
+  }
   CUtensorMap tq, tk, tv;
   if (make_tmap_3d(&tq, q, dqk, (uint64_t)B * Sq, Hq, ldq, dqk, 64, FWD_BM)) return -3;
   if (make_tmap_3d(&tk, k, dqk, (uint64_t)B * Sk, Hkv, ldk, dqk, 64, FWD_BN)) return -4;
