@@ -55,7 +55,7 @@ def main():
   out = {}
 
   # ---- F1: all-gather fused into the QKV GEMM
-  ag = fc.AllGatherGemm(sb, shard, copiers=int(os.environ.get("TPB_AG_COPIERS", "32")))
+  ag = fc.AllGatherGemm(sb, shard, copiers=int(os.environ.get("TPB_AG_COPIERS", "32")), push=False)
   t_fused = timed(lambda: ag(x, gathered, 0, HQKV, D), pre=sb.barrier)
   agp = fc.AllGatherGemm(sb, shard, copiers=int(os.environ.get("TPB_AG_COPIERS", "32")), push=True)
   t_push = timed(lambda: agp(x, None, 0, HQKV, D), pre=sb.barrier)

@@ -48,7 +48,95 @@ struct AttnFwdParams {
   long long ldo;       // elements between consecutive tokens of O
   float* lse;          // [B, Hq, Sq]
   int* status;
+  // Context-parallel K/V exchange fused into the kernel (cp_world > 1): the first cp_copiers CTAs
+  // push this rank's K/V rows into every rank's gathered buffers (plain 16-byte stores over NVLink,
+  // natural key order, so the zig-zag permutation costs nothing) and raise one flag per 128 keys in
+  // every rank's flag array; the TMA producer of an attention CTA waits (bounded) for the flag of a
+  // key block before loading it from the local gathered buffer.
+  int cp_world, cp_rank, cp_copiers, cp_zigzag;
+  int cp_s_local;                      // keys per rank and batch row (multiple of 128; of 256 if zig-zag)
+  const __nv_bfloat16* cp_k_src;       // this rank's keys  [B * cp_s_local rows], row pitch cp_ld_k
+  const __nv_bfloat16* cp_v_src;
+  long long cp_ld_k, cp_ld_v;
+  int cp_row_elems;                    // Hkv * 128: elements per key row in the gathered buffers
+  __nv_bfloat16* cp_k_dst[8];          // gathered K [B * Sk, Hkv * 128] of every rank
+  __nv_bfloat16* cp_v_dst[8];
+  unsigned* cp_flags[8];               // [B * Sk / 128] of every rank
+  unsigned cp_epoch;
 };
+
+constexpr int CP_CHUNK = 128;          // keys per flag
+
+// Natural position of local key row t (0 <= t < s_local) of rank r.
+__device__ __forceinline__ int cp_natural_pos(int t, int r, int world, int s_local, int zigzag) {
+  if (!zigzag) return r * s_local + t;
+  const int half = s_local / 2;
+  return t < half ? r * half + t : (2 * world - 1 - r) * half + (t - half);
+}
+
+// Copier CTA: chunks c, c + G, ... (128 key rows of one batch row each) of the local K and V.
+__device__ void cp_pusher(const AttnFwdParams& p) {
+  const int chunks_per_row = p.cp_s_local / CP_CHUNK;
+  const int n_chunks = p.B * chunks_per_row;
+  const int vec_per_row = p.cp_row_elems / 8;            // 16-byte vectors per key row
+  const int nvec = CP_CHUNK * vec_per_row;
+  for (int ch = blockIdx.x; ch < n_chunks; ch += p.cp_copiers) {
+    const int b = ch / chunks_per_row, t0 = (ch % chunks_per_row) * CP_CHUNK;
+    const int pos0 = cp_natural_pos(t0, p.cp_rank, p.cp_world, p.cp_s_local, p.cp_zigzag);
+    const long long dst_row0 = (long long)b * p.Sk + pos0;
+    for (int which = 0; which < 2; ++which) {
+      const __nv_bfloat16* src = which == 0 ? p.cp_k_src : p.cp_v_src;
+      const long long ld = which == 0 ? p.cp_ld_k : p.cp_ld_v;
+      const long long src_row0 = (long long)b * p.cp_s_local + t0;
+      for (int i = threadIdx.x; i < nvec; i += 8 * blockDim.x) {
+        uint4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int k = i + u * blockDim.x;
+          if (k < nvec)
+            v[u] = *reinterpret_cast<const uint4*>(src + (src_row0 + k / vec_per_row) * ld + (k % vec_per_row) * 8);
+        }
+        for (int r = 0; r < p.cp_world; ++r) {
+          uint4* dst = reinterpret_cast<uint4*>((which == 0 ? p.cp_k_dst[r] : p.cp_v_dst[r]) +
+                                                dst_row0 * p.cp_row_elems);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int k = i + u * blockDim.x;
+            if (k < nvec) dst[k] = v[u];
+          }
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const long long f = (long long)b * (p.Sk / CP_CHUNK) + pos0 / CP_CHUNK;
+      for (int r = 0; r < p.cp_world; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.cp_flags[r] + f), "r"(p.cp_epoch) : "memory");
+    }
+  }
+}
+
+// Bounded wait for the flag of the 128-key chunk that holds key `kv0` of batch row `b`.
+__device__ __forceinline__ bool cp_wait_keys(const AttnFwdParams& p, int b, int kv0) {
+  const unsigned* f = p.cp_flags[p.cp_rank] + (long long)b * (p.Sk / CP_CHUNK) + kv0 / CP_CHUNK;
+  long long t0 = 0;
+  int spins = 0;
+  while (true) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+    if (v == p.cp_epoch) break;
+    if (++spins == 64) {
+      spins = 0;
+      if (t0 == 0) t0 = clock64();
+      else if (clock64() - t0 > kSpinBudgetCycles) { report(p.status, kTimeoutPeerFlag, 51); return false; }
+      __nanosleep(100);
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");   // the rows were written with generic stores
+  return true;
+}
+
 
 template <int DQK>
 struct FwdSmem {
@@ -82,8 +170,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qtiles = (p.Sq + FWD_BM - 1) / FWD_BM;
-  const int qt = n_qtiles - 1 - (int)blockIdx.x;   // heaviest (latest) tiles first under a causal mask
-  const int hq = blockIdx.y, b = blockIdx.z;
+  int bx = blockIdx.x, by = blockIdx.y, bz = blockIdx.z;
+  if (p.cp_world > 1) {
+    // one-dimensional grid: the copier CTAs come first so that they are scheduled first
+    if ((int)blockIdx.x < p.cp_copiers) {
+      cp_pusher(p);
+      return;
+    }
+    const int id = (int)blockIdx.x - p.cp_copiers;
+    bx = id % n_qtiles; by = (id / n_qtiles) % p.Hq; bz = id / (n_qtiles * p.Hq);
+  }
+  const int qt = n_qtiles - 1 - bx;   // heaviest (latest) tiles first under a causal mask
+  const int hq = by, b = bz;
   const int hkv = hq / (p.Hq / p.Hkv);
   const int q0 = qt * FWD_BM;
   const int pos_off = p.Sk - p.Sq;
@@ -142,6 +240,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int s = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int row = b * p.Sk + (blk_lo + j) * FWD_BN;
+        if (p.cp_world > 1 && !cp_wait_keys(p, b, (blk_lo + j) * FWD_BN)) break;
         if (!mbar_wait(&k_empty[s], ph ^ 1, p.status, kTimeoutStageFree, 11)) break;
         mbar_expect_tx(&k_full[s], L::K_BYTES);
 #pragma unroll
@@ -717,7 +816,7 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
     if (make_tmap_3d(&tq, q, dqk, (uint64_t)B * Sq, Hq, ldq, dqk, 64, F2_T)) return -3;
     if (make_tmap_3d(&tk, k, dqk, (uint64_t)B * Sk, Hkv, ldk, dqk, 64, F2_T)) return -4;
     if (make_tmap_3d(&tv, v, dv, (uint64_t)B * Sk, Hkv, ldv, dv, 64, F2_T)) return -5;
-    AttnFwdParams p;
+    AttnFwdParams p{};
     p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.causal = causal; p.window = window;
@@ -739,7 +838,7 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
   if (make_tmap_3d(&tq, q, dqk, (uint64_t)B * Sq, Hq, ldq, dqk, 64, FWD_BM)) return -3;
   if (make_tmap_3d(&tk, k, dqk, (uint64_t)B * Sk, Hkv, ldk, dqk, 64, FWD_BN)) return -4;
   if (make_tmap_3d(&tv, v, dv, (uint64_t)B * Sk, Hkv, ldv, dv, 64, FWD_BN)) return -5;
-  AttnFwdParams p;
+  AttnFwdParams p{};
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal; p.window = window;
@@ -748,5 +847,61 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
   p.status = status_block();
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   cudaError_t e = dqk == 128 ? launch_fwd<128>(tq, tk, tv, p, stream) : launch_fwd<192>(tq, tk, tv, p, stream);
+  return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+
+// Causal attention forward with the context-parallel K/V exchange fused in (head dim 128).
+// q: this rank's query rows [B*Sq, ...] (row pitch ldq); k_local / v_local: this rank's
+// [B*s_local] key/value rows (row pitches ld_k_local / ld_v_local, Hkv*128 elements used per row);
+// k_all / v_all / flags: tables of every rank's gathered K [B*Sk, Hkv*128], gathered V and flag
+// array [B*Sk/128] in symmetric memory (Sk = world * s_local); entry `rank` is this rank's own.
+// q_pos: absolute positions of the query rows.  `epoch` must differ from the previous call's, and
+// all ranks must have finished reading their gathered buffers before any rank starts this call.
+extern "C" int tpb_attn_fwd_cp(const void* q, const void* k_local, const void* v_local, void* const* k_all,
+                               void* const* v_all, unsigned* const* flags, void* o, float* lse, int B, int Sq,
+                               int s_local, int Hq, int Hkv, long long ldq, long long ld_k_local,
+                               long long ld_v_local, long long ldo, float scale, const int* q_pos, int world, int rank,
+                               int zigzag, int copiers, unsigned epoch, void* stream_) {
+  if (world < 2 || world > 8 || rank < 0 || rank >= world || Hq % Hkv) return -2;
+  if ((ldq % 8) || (ld_k_local % 8) || (ld_v_local % 8) || (ldo % 8)) return -2;
+  if (s_local % (zigzag ? 2 * CP_CHUNK : CP_CHUNK)) return -2;
+  if (B <= 0 || Sq <= 0 || s_local <= 0) return 0;
+  const int Sk = world * s_local;
+  const int row_elems = Hkv * 128;
+  CUtensorMap tq, tk, tv;
+  if (make_tmap_3d(&tq, q, 128, (uint64_t)B * Sq, Hq, ldq, 128, 64, FWD_BM)) return -3;
+  if (make_tmap_3d(&tk, k_all[rank], 128, (uint64_t)B * Sk, Hkv, row_elems, 128, 64, FWD_BN)) return -4;
+  if (make_tmap_3d(&tv, v_all[rank], 128, (uint64_t)B * Sk, Hkv, row_elems, 128, 64, FWD_BN)) return -5;
+  AttnFwdParams p{};
+  p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = 1; p.window = 0;
+  p.q_pos = q_pos; p.q_seg = nullptr; p.kv_seg = nullptr;
+  p.O = reinterpret_cast<__nv_bfloat16*>(o); p.ldo = ldo; p.lse = lse;
+  p.status = status_block();
+  p.cp_world = world; p.cp_rank = rank; p.cp_zigzag = zigzag; p.cp_s_local = s_local;
+  const int n_chunks = B * (s_local / CP_CHUNK);
+  p.cp_copiers = copiers < 1 ? 1 : (copiers > n_chunks ? n_chunks : copiers);
+  p.cp_k_src = reinterpret_cast<const __nv_bfloat16*>(k_local);
+  p.cp_v_src = reinterpret_cast<const __nv_bfloat16*>(v_local);
+  p.cp_ld_k = ld_k_local; p.cp_ld_v = ld_v_local;
+  p.cp_row_elems = row_elems;
+  for (int r = 0; r < 8; ++r) {
+    p.cp_k_dst[r] = r < world ? reinterpret_cast<__nv_bfloat16*>(k_all[r]) : nullptr;
+    p.cp_v_dst[r] = r < world ? reinterpret_cast<__nv_bfloat16*>(v_all[r]) : nullptr;
+    p.cp_flags[r] = r < world ? flags[r] : nullptr;
+  }
+  p.cp_epoch = epoch;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         FwdSmem<128>::TOTAL);
+    if (e != cudaSuccess) return 1000 + (int)e;
+    configured = true;
+  }
+  const int n_qtiles = (Sq + FWD_BM - 1) / FWD_BM;
+  const int grid = p.cp_copiers + n_qtiles * Hq * B;
+  attn_fwd_kernel<128><<<grid, FWD_THREADS, FwdSmem<128>::TOTAL, reinterpret_cast<cudaStream_t>(stream_)>>>(tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }

@@ -75,8 +75,10 @@ struct GemmParams {
   unsigned ag_epoch;
   int ag_local;                 // rank whose shard already sits in ag_dst (not copied, not waited for); -1: none
   // Push mode (ag_push != 0): the copier CTAs of rank ag_local read ITS OWN shard and store it into
-  // every peer's gathered buffer (posted writes, no round trip per chunk), then raise the flag in
-  // the peer's flag array; each rank waits on flags in its own memory.
+  // every peer's gathered buffer with plain 16-byte stores (posted writes: nothing waits for a round
+  // trip until the fence before a chunk's flags), then raise the flag in the peer's flag array; each
+  // rank waits on flags in its own memory.  Measured on 2 GPUs: 11-12 GB/s per copier CTA, against
+  // 7-8 GB/s for pulling (an SM keeps few peer reads in flight).
   int ag_push;
   void* ag_push_dst[8];         // gathered buffer of every rank (symmetric memory)
   unsigned* ag_push_flags[8];   // flag array of every rank (symmetric memory)
@@ -227,77 +229,53 @@ __device__ void ag_copier(const GemmParams& p, uint8_t* smem) {
   if (mine > 0) publish(mine - 1);
 }
 
+// Push with plain stores: all threads of the copier CTA read 16-byte vectors of the local shard and
+// store them into every peer's gathered buffer (posted writes, nothing waits for a round trip
+// until the fence that precedes the chunk's flags).
+__device__ void ag_pusher(const GemmParams& p) {
+  const long long cps = ag_chunks_per_shard(p);
+  const int G = p.ag_copiers, c = blockIdx.x;
+  const int me = p.ag_local;
+  for (long long j = c; j < cps; j += G) {
+    const long long off = j * p.ag_chunk_elems;
+    const long long n = min(p.ag_chunk_elems, p.ag_shard_elems - off);
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.ag_src[me]) + off);
+    const int nvec = (int)(n / 8);
+    for (int i = threadIdx.x; i < nvec; i += 16 * blockDim.x) {
+      uint4 v[16];
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int k = i + u * blockDim.x;
+        if (k < nvec) v[u] = src[k];
+      }
+      for (int r = 0; r < p.ag_world; ++r) {
+        if (r == me) continue;
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.ag_push_dst[r]) +
+                                              (long long)me * p.ag_shard_elems + off);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int k = i + u * blockDim.x;
+          if (k < nvec) dst[k] = v[u];
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int r = 0; r < p.ag_world; ++r) {
+        if (r == me) continue;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ag_push_flags[r] + me * cps + j), "r"(p.ag_epoch)
+                     : "memory");
+      }
+    }
+  }
+}
+
 // PAIR: the kernel runs as clusters of two CTAs on 256 x 256 output tiles.  Each CTA stages its
 // 128 rows of A and ONE 128-row half of B per k-block (32 KB instead of 48 KB, in a 6-deep ring),
 // the even CTA issues tcgen05.mma.cta_group::2 (M = 256) for both, and each CTA drains its own
 // 128 accumulator rows.  Shared-memory traffic per FLOP drops by a third, which is what bounds
 // the single-CTA kernel (TMA writes plus operand reads exceed 128 B/clk).  Dense mode only.
-// Push-mode copier CTA: chunks c, c+G, ... of the local shard go  local memory -> shared memory ->
-// every peer's gathered buffer (plain bulk stores to peer memory), then the chunk's flag is raised
-// in every peer's flag array.
-__device__ void ag_pusher(const GemmParams& p, uint8_t* smem) {
-  constexpr int SLOTS = 6;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SLOTS * 32768);
-  if (threadIdx.x != 0) return;
-  for (int i = 0; i < SLOTS; ++i) mbar_init(&bars[i], 1);
-  fence_barrier_init();
-  const long long cps = ag_chunks_per_shard(p);
-  const int G = p.ag_copiers, c = blockIdx.x;
-  const long long mine = (cps - c + G - 1) / G;
-  const int me = p.ag_local;
-  auto geom = [&](long long k, long long& j, long long& off, uint32_t& bytes) {
-    j = c + k * G;
-    off = j * p.ag_chunk_elems;
-    bytes = (uint32_t)(min(p.ag_chunk_elems, p.ag_shard_elems - off) * 2);
-  };
-  auto issue_load = [&](long long k) {
-    long long j, off; uint32_t bytes;
-    geom(k, j, off, bytes);
-    const int slot = (int)(k % SLOTS);
-    mbar_expect_tx(&bars[slot], bytes);
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(smem + slot * 32768)),
-                 "l"(reinterpret_cast<const uint8_t*>(p.ag_src[me]) + off * 2), "r"(bytes), "r"(smem_u32(&bars[slot]))
-                 : "memory");
-  };
-  auto publish = [&](long long k) {
-    long long j, off; uint32_t bytes;
-    geom(k, j, off, bytes);
-    asm volatile("fence.proxy.async;" ::: "memory");
-    __threadfence_system();
-    for (int r = 0; r < p.ag_world; ++r) {
-      if (r == me) continue;
-      asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.ag_push_flags[r] + me * cps + j), "r"(p.ag_epoch)
-                   : "memory");
-    }
-  };
-  // Up to DEPTH chunks of stores are in flight (a remote store group takes a round trip to
-  // complete); the remaining slots of the ring prefetch the next local chunks.
-  constexpr int DEPTH = 4;
-  for (long long k = 0; k < mine && k < SLOTS; ++k) issue_load(k);
-  for (long long k = 0; k < mine; ++k) {
-    const int slot = (int)(k % SLOTS);
-    if (!mbar_wait(&bars[slot], (uint32_t)((k / SLOTS) & 1), p.status, kTimeoutTmaFull, 7)) return;
-    long long j, off; uint32_t bytes;
-    geom(k, j, off, bytes);
-    for (int r = 0; r < p.ag_world; ++r) {
-      if (r == me) continue;
-      uint8_t* dst = reinterpret_cast<uint8_t*>(p.ag_push_dst[r]) + ((long long)me * p.ag_shard_elems + off) * 2;
-      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
-                   "r"(smem_u32(smem + slot * 32768)), "r"(bytes)
-                   : "memory");
-    }
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    if (k >= DEPTH) {
-      asm volatile("cp.async.bulk.wait_group 4;" ::: "memory");   // the stores of chunk k-DEPTH are complete
-      publish(k - DEPTH);
-      if (k - DEPTH + SLOTS < mine) issue_load(k - DEPTH + SLOTS);
-    }
-  }
-  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-  for (long long k = (mine > DEPTH ? mine - DEPTH : 0); k < mine; ++k) publish(k);
-}
-
 template <bool A_MN, bool B_MN, bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -316,7 +294,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (!PAIR && (int)blockIdx.x < p.ag_copiers) {
-    if (p.ag_push) ag_pusher(p, smem); else ag_copier(p, smem);
+    if (p.ag_push) ag_pusher(p); else ag_copier(p, smem);
     return;
   }
   const int rank = PAIR ? (int)cluster_ctarank() : 0;    // 0: issues the MMAs of the pair
@@ -782,6 +760,7 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.ag_flags = g.ag_flags; p.ag_epoch = g.ag_epoch; p.ag_local = g.ag_world > 0 ? g.ag_local : -1;
   p.rs_world = g.rs_world; p.rs_shard_elems = g.rs_shard_elems; p.rs_c_offset = g.rs_c_offset;
   p.ag_push = (g.ag_world > 0 && g.ag_push_dst != nullptr && g.ag_push_flags != nullptr) ? 1 : 0;
+  if (p.ag_push) p.ag_chunk_elems = 131072;   // 256 KB per flag: a CTA streams a chunk with one fence at its end
   for (int i = 0; i < 8; ++i) {
     p.ag_push_dst[i] = (p.ag_push && i < g.ag_world) ? g.ag_push_dst[i] : nullptr;
     p.ag_push_flags[i] = (p.ag_push && i < g.ag_world) ? g.ag_push_flags[i] : nullptr;

@@ -124,6 +124,11 @@ int tpb_moe_combine_dw(const void* rows, const int* dest, const void* dout, floa
 int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int Hq,
                  int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv, long long ldo, float scale,
                  int causal, int window, const int* q_pos, const int* q_seg, const int* kv_seg, void* stream);
+// Causal forward with the context-parallel K/V exchange fused in (see attention_fwd_sm100.cu).
+int tpb_attn_fwd_cp(const void* q, const void* k_local, const void* v_local, void* const* k_all, void* const* v_all,
+                    unsigned* const* flags, void* o, float* lse, int B, int Sq, int s_local, int Hq, int Hkv,
+                    long long ldq, long long ld_k_local, long long ld_v_local, long long ldo, float scale,
+                    const int* q_pos, int world, int rank, int zigzag, int copiers, unsigned epoch, void* stream);
 // `scratch` holds tpb_attn_bwd_scratch_floats(B, Sq, Hq) floats; dq/dk/dv are fully overwritten.
 long long tpb_attn_bwd_scratch_floats(int B, int Sq, int Hq);
 int tpb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,

@@ -33,7 +33,7 @@ def _worker(rank, world, port, results):
     torch.manual_seed(100 + rank)
     x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
     gathered = torch.empty(shard * world, dtype=torch.bfloat16, device=dev)
-    ag = fc.AllGatherGemm(sb, shard, copiers=4)
+    ag = fc.AllGatherGemm(sb, shard, copiers=4, push=False)
     for it in range(2):                          # twice: epochs, reuse of flags
       gathered.zero_()
       sb.barrier()
@@ -80,6 +80,34 @@ def _worker(rank, world, port, results):
       mine = flat[rank * shard2:(rank + 1) * shard2]
       err = ((gs.local.float() - mine).norm() / (mine.norm() + 1e-9)).item()
       assert err < 2e-2, f"gemm_rs rel err {err}"
+    # ---- context-parallel attention with the K/V exchange fused into the forward kernel
+    from torchprime_b200.dist.mesh import Mesh
+    from torchprime_b200.parallel.cp import ContextParallelAttention
+    mesh = Mesh(shape={"data": 1, "fsdp": 1, "tensor": 1, "expert": 1, "context": world}, rank=rank, world_size=world)
+    for lb in (False, True):
+      ref_cp = ContextParallelAttention(mesh, load_balanced=lb, fused_exchange=False)
+      fus_cp = ContextParallelAttention(mesh, load_balanced=lb, fused_exchange=True, fused_copiers=4)
+      torch.manual_seed(500 + rank)
+      b, s_loc, hq, hkv, d = 2, 512, 8, 2, 128
+      qkv = (torch.randn(b, s_loc, (hq + 2 * hkv) * d, device=dev) * 0.5).to(torch.bfloat16)
+      dout = (torch.randn(b, s_loc, hq, d, device=dev) * 0.1).to(torch.bfloat16)
+      outs = []
+      for cpa in (ref_cp, fus_cp):
+        x = qkv.clone().requires_grad_(True)
+        q = x[..., :hq * d].view(b, s_loc, hq, d)
+        k = x[..., hq * d:(hq + hkv) * d].view(b, s_loc, hkv, d)
+        v = x[..., (hq + hkv) * d:].view(b, s_loc, hkv, d)
+        for _ in range(2):                       # twice: buffers and flags are reused with a new epoch
+          x.grad = None
+          o = cpa.attention(q, k, v)
+          o.backward(dout)
+        torch.cuda.synchronize()
+        outs.append((o.detach().float(), x.grad.float()))
+      (o_ref, g_ref), (o_fus, g_fus) = outs
+      assert fus_cp._fused, "the fused exchange path was not taken"
+      err_o = ((o_fus - o_ref).norm() / o_ref.norm()).item()
+      err_g = ((g_fus - g_ref).norm() / g_ref.norm()).item()
+      assert err_o < 1e-2 and err_g < 2e-2, f"fused cp attention (lb={lb}): out {err_o} grad {err_g}"
     _lib.raise_on_device_timeout()
     results[rank] = "ok"
   except Exception as e:  # noqa: BLE001

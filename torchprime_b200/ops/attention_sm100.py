@@ -11,7 +11,7 @@ query positions (context-parallel shards).
 from __future__ import annotations
 
 import math
-from ctypes import c_float, c_int, c_longlong, c_void_p
+from ctypes import c_uint, c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -22,6 +22,33 @@ P, I, LL, F = c_void_p, c_int, c_longlong, c_float
 _lib.register_signature("tpb_attn_fwd", [P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, F, I, I, P, P, P, P])
 _lib.register_signature("tpb_attn_bwd", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, LL,
                                          LL, LL, F, I, I, P, P, P, P])
+
+
+_lib.register_signature("tpb_attn_fwd_cp", [P, P, P, P, P, P, P, P, I, I, I, I, I, LL, LL, LL, LL, F, P, I, I, I, I,
+                                            c_uint, P])
+
+
+def attn_fwd_cp(q, k_local, v_local, k_all_sb, v_all_sb, flags_sb, q_pos, *, zigzag: bool, epoch: int,
+                copiers: int = 16, scale=None):
+  """Causal attention forward with the context-parallel K/V exchange fused into the kernel.
+
+  ``q`` [B,Sq,Hq,128] are this rank's query rows, ``k_local`` / ``v_local`` [B,S_local,Hkv,128] its
+  keys and values; ``k_all_sb`` / ``v_all_sb`` / ``flags_sb`` are ``SymmetricBuffer`` objects that
+  hold the gathered K, V ([B, world*S_local, Hkv, 128], natural key order) and one flag per 128
+  keys.  Copier CTAs push the local rows into every rank's buffers while the other CTAs compute.
+  Returns (o, lse); afterwards ``k_all_sb.local`` / ``v_all_sb.local`` hold the gathered tensors."""
+  b, sq, hq, d = q.shape
+  s_local, hkv = k_local.shape[1], k_local.shape[2]
+  assert d == 128 and v_local.shape[-1] == 128 and _token_major(q) and _token_major(k_local) and _token_major(v_local)
+  scale = scale if scale is not None else 1.0 / math.sqrt(d)
+  o = torch.empty(b, sq, hq, 128, dtype=q.dtype, device=q.device)
+  lse = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
+  rc = lib().tpb_attn_fwd_cp(ptr(q), ptr(k_local), ptr(v_local), k_all_sb.ptr_table(), v_all_sb.ptr_table(),
+                             flags_sb.ptr_table(), ptr(o), ptr(lse), b, sq, s_local, hq, hkv, q.stride(1),
+                             k_local.stride(1), v_local.stride(1), hq * 128, float(scale), ptr(q_pos),
+                             k_all_sb.world, k_all_sb.rank, int(bool(zigzag)), int(copiers), int(epoch), stream_ptr())
+  check(rc, f"attn_fwd_cp q{tuple(q.shape)} k{tuple(k_local.shape)} world={k_all_sb.world}")
+  return o, lse
 
 
 def _token_major(t: torch.Tensor) -> bool:

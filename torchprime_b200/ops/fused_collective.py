@@ -2,10 +2,12 @@
 
 ``ag_gemm``: ``y = x @ W^T`` where the flat buffer that contains ``W`` is sharded over the ranks of a
 group (FSDP parameter shards, or a row-sharded activation/weight for tensor parallelism).  A few
-copier CTAs of the same kernel pull every remote shard from its owner (plain bulk copies from peer
-memory, no multicast) into the local gathered buffer and publish per-chunk flags; the GEMM CTAs
-load their B tiles locally as soon as the chunks they need have landed.  The rank's own shard is
-put in place by a device-to-device copy on the same stream before the kernel starts.  After the call the whole buffer is
+copier CTAs of the same kernel move the shards while the other CTAs compute: by default every rank
+PUSHES its shard into the peers' gathered buffers with plain 16-byte stores (posted writes over
+NVLink) and raises per-chunk flags in the peers' memory; ``push=False`` makes every rank pull the
+remote shards instead (bulk copies from peer memory through shared memory, no multicast).  The
+GEMM CTAs load their B tiles locally as soon as the chunks they need have landed.  The rank's own
+shard is put in place by a device-to-device copy on the same stream before the kernel starts.  After the call the whole buffer is
 gathered, so the other weights of the same FSDP unit are ready too.
 
 ``gemm_rs``: ``dW = dY^T X`` (or any GEMM) whose epilogue adds ``alpha * tile`` directly into the
@@ -37,7 +39,7 @@ def num_flags(world: int, shard_elems: int) -> int:
 class AllGatherGemm:
   """State for repeated fused all-gather + GEMM calls on one sharded flat buffer."""
 
-  def __init__(self, shard_buffer, shard_elems: int, copiers: int = 32, push: bool = False):
+  def __init__(self, shard_buffer, shard_elems: int, copiers: int = 32, push: bool = True):
     """``push``: every rank sends its shard to the peers (posted stores over NVLink) instead of
     fetching theirs.  The gathered buffer and the flags then live in symmetric memory owned by this
     object (``self.gathered``), and the ranks must be synchronised between two calls (nobody may

@@ -13,19 +13,89 @@ forward-only, kernel_utils.py:124-131).
 from __future__ import annotations
 
 import torch
+import torch.distributed as dist
 
 from ..ops import functional as ops
 from ..utils.parallelism_utils import reorder_sequence
 from .collectives import all_gather_dim
 
 
+class _FusedExchangeAttention(torch.autograd.Function):
+  """Causal attention whose forward kernel also performs the K/V exchange: copier CTAs push this
+  rank's keys and values into every rank's gathered buffers over NVLink while the attention CTAs
+  run.  Backward uses the gathered tensors the forward produced and returns dK/dV to their owners
+  with a reduce-scatter."""
+
+  @staticmethod
+  def forward(ctx, q, k, v, cpa, pos32, scale):
+    from ..ops import attention_sm100 as A
+    st = cpa._fused_state(q, k)
+    st["epoch"] += 1
+    st["k_all"].barrier()            # every rank is done reading the buffers of the previous call
+    o, lse = A.attn_fwd_cp(q, k, v, st["k_all"], st["v_all"], st["flags"], pos32, zigzag=cpa.load_balanced,
+                           epoch=st["epoch"], copiers=cpa.fused_copiers, scale=scale)
+    b, s_local, hkv, d = k.shape
+    sk = s_local * cpa.cp
+    # the symmetric buffers are reused by the next layer: keep this layer's gathered K/V for backward
+    k_all = st["k_all"].local.view(b, sk, hkv, d).clone()
+    v_all = st["v_all"].local.view(b, sk, hkv, d).clone()
+    ctx.save_for_backward(q, k_all, v_all, o, lse, pos32)
+    ctx.cpa, ctx.scale = cpa, scale
+    return o
+
+  @staticmethod
+  def backward(ctx, do):
+    from ..ops import attention_sm100 as A
+    q, k_all, v_all, o, lse, pos32 = ctx.saved_tensors
+    cpa = ctx.cpa
+    dq, dk_all, dv_all = A.attn_bwd(do, q, k_all, v_all, o, lse, causal=True, scale=ctx.scale, q_pos=pos32)
+    if cpa.load_balanced:            # back to rank-major (zig-zag) order, as the owners hold it
+      dk_all = reorder_sequence(dk_all, cpa.cp, seq_dim=1, to_contiguous=False)
+      dv_all = reorder_sequence(dv_all, cpa.cp, seq_dim=1, to_contiguous=False)
+    b, sk, hkv, d = dk_all.shape
+    s_local = sk // cpa.cp
+
+    def scatter(g):
+      parts = g.view(b, cpa.cp, s_local, hkv, d).transpose(0, 1).contiguous()   # [cp, b, s_local, ...]
+      out = torch.empty(b, s_local, hkv, d, dtype=g.dtype, device=g.device)
+      dist.reduce_scatter_tensor(out, parts, group=cpa.group)
+      return out
+
+    return dq, scatter(dk_all), scatter(dv_all), None, None, None
+
+
 class ContextParallelAttention:
-  def __init__(self, mesh, load_balanced: bool = False):
+  def __init__(self, mesh, load_balanced: bool = False, fused_exchange: bool = False, fused_copiers: int = 16):
     self.group = mesh.group("context")
     self.cp = mesh.size("context")
     self.rank = mesh.index("context")
     self.load_balanced = load_balanced
+    self.fused_exchange = fused_exchange      # K/V exchange inside the attention forward kernel
+    self.fused_copiers = fused_copiers
     self._pos_cache = {}
+    self._fused = {}
+
+  def _fused_state(self, q, k):
+    """Symmetric gathered K/V buffers and flags for this shape (allocated once, on every rank)."""
+    from ..dist.symm import SymmetricBuffer
+    b, s_local, hkv, d = k.shape
+    key = (b, s_local, hkv, d)
+    if key not in self._fused:
+      n = b * s_local * self.cp * hkv * d
+      flags = SymmetricBuffer(b * s_local * self.cp // 128, torch.int32, q.device, group=self.group)
+      flags.local.zero_()
+      self._fused[key] = {"k_all": SymmetricBuffer(n, k.dtype, q.device, group=self.group),
+                          "v_all": SymmetricBuffer(n, k.dtype, q.device, group=self.group),
+                          "flags": flags, "epoch": 0}
+      flags.barrier()
+    return self._fused[key]
+
+  def _can_fuse(self, q, k, v, segment_ids) -> bool:
+    if not (self.fused_exchange and q.is_cuda and segment_ids is None and ops.use_kernels(q, k, v)):
+      return False
+    s_local = k.shape[1]
+    return (q.shape[-1] == 128 and v.shape[-1] == 128 and q.dtype == torch.bfloat16
+            and s_local % (256 if self.load_balanced else 128) == 0)
 
   def query_positions(self, s_local: int, device) -> torch.Tensor:
     """Absolute positions of this rank's rows, [s_local] int64."""
@@ -44,6 +114,9 @@ class ContextParallelAttention:
 
   def attention(self, q, k, v, segment_ids=None, scale=None):
     b, s_local = q.shape[0], q.shape[1]
+    if self._can_fuse(q, k, v, segment_ids):
+      pos32 = self.query_positions(s_local, q.device)[None].expand(b, s_local).to(torch.int32).contiguous()
+      return _FusedExchangeAttention.apply(q, k, v, self, pos32, scale)
     k_all = all_gather_dim(k.contiguous(), self.group, 1)
     v_all = all_gather_dim(v.contiguous(), self.group, 1)
     kv_seg = None

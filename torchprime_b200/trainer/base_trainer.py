@@ -99,7 +99,8 @@ class Trainer:
       model.return_logits = not bool(eng.get("chunked_ce", True))
     if cp_enabled(config) and hasattr(model, "cp"):
       from ..parallel.cp import ContextParallelAttention
-      model.cp = ContextParallelAttention(self.mesh, load_balanced=lb_cp_enabled(config))
+      model.cp = ContextParallelAttention(self.mesh, load_balanced=lb_cp_enabled(config),
+                                          fused_exchange=bool(eng.get("fused_collectives", False)) and self.device.type == "cuda")
       if getattr(model, "_head", None) is not None:
         model._head.loss_group = self.mesh.group("context")
       if hasattr(model, "model"):
