@@ -4,7 +4,8 @@
 
 Shapes are one Llama-3-8B decoder layer on one 8192-token sequence per GPU: the FSDP gather of the
 layer's 218 M bf16 parameters fused into the QKV projection, and the gate/up weight-gradient GEMM
-fused with its reduce-scatter.  Roofline = max(FLOPs / measured cuBLAS peak, bytes that cross NVLink /
+fused with its reduce-scatter, and a zig-zag context-parallel attention forward (8192 keys per
+rank) with its K/V exchange inside the kernel.  Roofline = max(FLOPs / measured cuBLAS peak, bytes that cross NVLink /
 770 GB/s per direction).  Times are CUDA-event times, max over ranks.
 """
 
@@ -93,6 +94,28 @@ def main():
   roof2 = max(flops2 / (peak * 1e12), link2 / (NVLINK_GBS * 1e9)) * 1e3
   out["gemm_rs"] = {"fused_ms": t_rs, "gemm_plus_nccl_reduce_scatter_ms": t_nccl_rs, "roofline_ms": roof2,
                     "fraction_of_roofline": roof2 / t_rs, "nvlink_bytes_out": link2}
+  # ---- F5: context-parallel attention forward with the K/V exchange inside the kernel
+  from torchprime_b200.dist.mesh import Mesh
+  from torchprime_b200.parallel.cp import ContextParallelAttention
+  mesh = Mesh(shape={"data": 1, "fsdp": 1, "tensor": 1, "expert": 1, "context": world}, rank=rank, world_size=world)
+  s_loc, hq, hkv, hd = 8192, 32, 8, 128
+  qkv = torch.randn(1, s_loc, (hq + 2 * hkv) * hd, device=dev, dtype=torch.bfloat16)
+  q = qkv[..., :hq * hd].view(1, s_loc, hq, hd)
+  kk = qkv[..., hq * hd:(hq + hkv) * hd].view(1, s_loc, hkv, hd)
+  vv = qkv[..., (hq + hkv) * hd:].view(1, s_loc, hkv, hd)
+  nccl_cp = ContextParallelAttention(mesh, load_balanced=True, fused_exchange=False)
+  fused_cp = ContextParallelAttention(mesh, load_balanced=True, fused_exchange=True,
+                                      fused_copiers=int(os.environ.get("TPB_CP_COPIERS", "16")))
+  with torch.no_grad():
+    t_cp_nccl = timed(lambda: nccl_cp.attention(q, kk, vv))
+    t_cp_fused = timed(lambda: fused_cp.attention(q, kk, vv))
+  sk = s_loc * world
+  flops5 = 4.0 * s_loc * sk * hq * hd / 2          # causal, zig-zag balanced: half of the score matrix
+  link5 = (world - 1) * s_loc * hkv * hd * 2 * 2
+  roof5 = max(flops5 / (peak * 1e12), link5 / (NVLINK_GBS * 1e9)) * 1e3
+  out["cp_attention_fwd"] = {"fused_ms": t_cp_fused, "nccl_allgather_then_attention_ms": t_cp_nccl,
+                             "roofline_ms": roof5, "fraction_of_roofline": roof5 / t_cp_fused,
+                             "nvlink_bytes_in": link5, "keys_per_rank": s_loc}
   torch.cuda.synchronize()
   _lib.raise_on_device_timeout()
   if rank == 0:
