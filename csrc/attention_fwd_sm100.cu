@@ -435,7 +435,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 //   warp 0      TMA producer: both Q tiles once, then 2-stage rings of 128-key K and V tiles.
 //   warp 1      MMA issuer.  Per step j and tile x: O_x += P_x(j) V_j, then S_x(j+1) = Q_x K_{j+1}^T
 //               into the columns P_x(j) has just been read from (S and P share TMEM columns).
-//   warps 2-5   softmax of both tiles, alternately (thread = query row of tile a and of tile b).
+//   warps 2-5   softmax of tile a (thread = query row), warps 6-9 softmax of tile b.
 //   TMEM        S_a [0,128)  S_b [128,256)  O_a [256,384)  O_b [384,512)
 // ------------------------------------------------------------------------------------------
 // 2^x for x <= 0 on the FMA pipe (no MUFU): round-to-nearest split x = n + f with the 1.5 * 2^23
@@ -452,7 +452,7 @@ __device__ __forceinline__ float exp2_fma(float x) {
 }
 
 constexpr int F2_T = 128;                 // tile edge: rows per query tile, keys per step
-constexpr int F2_THREADS = 192;
+constexpr int F2_THREADS = 320;
 constexpr int F2_TILE_BYTES = F2_T * 128 * 2;   // 32 KB
 namespace f2 {
 constexpr int OFF_Q = 0;                          // two tiles
@@ -509,12 +509,12 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   // position range of each query tile
-  for (int t = threadIdx.x; t < 2 * F2_T; t += F2_THREADS) {
-    const int r = q0 + t;
+  if (threadIdx.x < 2 * F2_T) {
+    const int r = q0 + threadIdx.x;
     if (r < p.Sq) {
       const int qp = p.q_pos ? p.q_pos[(long long)b * p.Sq + r] : r + pos_off;
-      atomicMin(&tile_minmax[2 * (t / F2_T)], qp);
-      atomicMax(&tile_minmax[2 * (t / F2_T) + 1], qp);
+      atomicMin(&tile_minmax[2 * (threadIdx.x / F2_T)], qp);
+      atomicMax(&tile_minmax[2 * (threadIdx.x / F2_T) + 1], qp);
     }
   }
   __syncthreads();
@@ -628,151 +628,142 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------ softmax + epilogue
-    // One warpgroup serves both tiles alternately (thread = query row of tile a AND of tile b):
-    // the exponentials are bound by the MUFU rate whatever the number of warps, and with six warps
-    // per CTA a thread may keep the 128 scores of a row in registers.
+    const int x = (warp - 2) >> 2;                // query tile of this warp
     const int q = warp & 3;                       // TMEM lane quarter
     const int r_local = q * 32 + lane;
+    const int row = q0 + x * F2_T + r_local;
+    const bool row_ok = row < p.Sq;
+    const long long grow = (long long)b * p.Sq + row;
+    const int qpos = row_ok ? (p.q_pos ? p.q_pos[grow] : row + pos_off) : -1;
+    const int qseg = (p.q_seg && row_ok) ? p.q_seg[grow] : 0;
+    const int qpos_min = tile_minmax[2 * x], qpos_max = tile_minmax[2 * x + 1];
     const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+    const uint32_t tS = tmem_base + x * F2_T + lane_addr, tO = tmem_base + 256 + x * F2_T + lane_addr;
     const int* ks = p.kv_seg ? p.kv_seg + (long long)b * p.Sk : nullptr;
     const int win = p.window > 0 ? p.window : 0x7fffffff;
-    int row[2], qpos[2], qseg[2], kmax[2], step[2] = {0, 0};
-    bool row_ok[2];
-    float m_used[2] = {-INFINITY, -INFINITY};   // maximum the exponentials are taken against (log2 units)
-    float l[2] = {0.f, 0.f};
-#pragma unroll
-    for (int x = 0; x < 2; ++x) {
-      row[x] = q0 + x * F2_T + r_local;
-      row_ok[x] = row[x] < p.Sq;
-      const long long grow = (long long)b * p.Sq + row[x];
-      qpos[x] = row_ok[x] ? (p.q_pos ? p.q_pos[grow] : row[x] + pos_off) : -1;
-      qseg[x] = (p.q_seg && row_ok[x]) ? p.q_seg[grow] : 0;
-      kmax[x] = p.causal ? min(qpos[x], p.Sk - 1) : p.Sk - 1;   // keep needs kp <= kmax
-    }
+    const int kmax = p.causal ? min(qpos, p.Sk - 1) : p.Sk - 1;   // keep needs kp <= kmax
+
+    float m_used = -INFINITY;   // maximum the exponentials are currently taken against (log2 units)
+    float l = 0.f;
     bool ok = true;
+    int step = 0;
     for (int j = 0; j < nblk && ok; ++j) {
+      if (!active(x, j)) continue;
+      if (!mbar_wait(&s_full[x], step & 1, p.status, kTimeoutAccFull, 48)) { ok = false; break; }
+      tc_fence_after();
+      const int kv0 = (blk_lo + j) * F2_T;
+      const bool need_mask = (p.causal && kv0 + F2_T - 1 > qpos_min) || (kv0 + F2_T > p.Sk) ||
+                             (p.window > 0 && qpos_max - kv0 >= p.window) || p.q_seg != nullptr;
+      // all 128 scores of the row into registers with one wait
+      uint32_t r[128];
+      tmem_ld32(tS, r);
+      tmem_ld32(tS + 32, r + 32);
+      tmem_ld32(tS + 64, r + 64);
+      tmem_ld32(tS + 96, r + 96);
+      tmem_wait_ld();
+      float m_blk = -INFINITY;
+      if (need_mask) {
 #pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        if (!ok || !active(x, j)) continue;
-        const uint32_t tS = tmem_base + x * F2_T + lane_addr, tO = tmem_base + 256 + x * F2_T + lane_addr;
-        if (!mbar_wait(&s_full[x], step[x] & 1, p.status, kTimeoutAccFull, 48)) { ok = false; continue; }
-        tc_fence_after();
-        const int kv0 = (blk_lo + j) * F2_T;
-        const int qpos_min = tile_minmax[2 * x], qpos_max = tile_minmax[2 * x + 1];
-        const bool need_mask = (p.causal && kv0 + F2_T - 1 > qpos_min) || (kv0 + F2_T > p.Sk) ||
-                               (p.window > 0 && qpos_max - kv0 >= p.window) || p.q_seg != nullptr;
-        // all 128 scores of the row into registers with one wait
-        uint32_t r[128];
-        tmem_ld32(tS, r);
-        tmem_ld32(tS + 32, r + 32);
-        tmem_ld32(tS + 64, r + 64);
-        tmem_ld32(tS + 96, r + 96);
-        tmem_wait_ld();
-        float m_blk;
-        if (need_mask) {
-          m_blk = -INFINITY;
-#pragma unroll
-          for (int c = 0; c < 128; ++c) {
-            const int kp = kv0 + c;
-            bool keep = (kp <= kmax[x]) & (qpos[x] - kp < win) & row_ok[x];
-            if (ks) keep = keep & (__ldg(ks + min(kp, p.Sk - 1)) == qseg[x]);
-            r[c] = keep ? r[c] : 0xff800000u;   // -inf
-            m_blk = fmaxf(m_blk, __uint_as_float(r[c]));
-          }
-        } else {
-          float mx[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) mx[e] = __uint_as_float(r[e]);
-#pragma unroll
-          for (int c = 8; c < 128; c += 8)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(r[c + e]));
-          m_blk = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+        for (int c = 0; c < 128; ++c) {
+          const int kp = kv0 + c;
+          bool keep = (kp <= kmax) & (qpos - kp < win) & row_ok;
+          if (ks) keep = keep & (__ldg(ks + min(kp, p.Sk - 1)) == qseg);
+          r[c] = keep ? r[c] : 0xff800000u;   // -inf
+          m_blk = fmaxf(m_blk, __uint_as_float(r[c]));
         }
-        m_blk *= p.scale_log2;     // scale > 0: max(s) * c == max(s * c)
-        // lazy running maximum
-        float alpha = 1.f;
-        bool rescale = false;
-        if (m_blk > m_used[x] + kRescaleThreshold || (m_used[x] == -INFINITY && m_blk > -INFINITY)) {
-          alpha = (m_used[x] == -INFINITY) ? 0.f : exp2f(m_used[x] - m_blk);
-          rescale = (m_used[x] != -INFINITY);
-          m_used[x] = m_blk;
-        }
-        const float m_safe = (m_used[x] == -INFINITY) ? 0.f : m_used[x];
-        // the previous P V of this tile must be complete before O is rescaled
-        if (step[x] > 0) {
-          if (!mbar_wait(&o_done[x], (step[x] - 1) & 1, p.status, kTimeoutAccFull, 49)) { ok = false; continue; }
-          tc_fence_after();
-          if (__any_sync(0xffffffffu, rescale)) {
-#pragma unroll 1
-            for (int c = 0; c < FWD_DV / 32; ++c) {
-              uint32_t o[32];
-              tmem_ld32(tO + c * 32, o);
-              tmem_wait_ld();
+      } else {
+        // eight independent chains instead of one 128-long dependent one
+        float mx[8];
 #pragma unroll
-              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-              tmem_st32(tO + c * 32, o);
-            }
-          }
-        }
-        // P = exp2(s * c - m), packed bf16 over the first 64 of the 128 score columns (masked scores
-        // are -inf and give exactly 0).  Every fourth exponential runs on the FMA pipe (exp2_fma).
-        float sums[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int e = 0; e < 8; ++e) mx[e] = __uint_as_float(r[e]);
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint32_t pk[16];
+        for (int c = 8; c < 128; c += 8)
 #pragma unroll
-          for (int c = 0; c < 32; c += 4) {
-            const float p0 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c]), p.scale_log2, -m_safe));
-            const float p1 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 1]), p.scale_log2, -m_safe));
-            const float p2 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 2]), p.scale_log2, -m_safe));
-            const float p3 = exp2_fma(fmaf(__uint_as_float(r[ch * 32 + c + 3]), p.scale_log2, -m_safe));
-            sums[0] += p0; sums[1] += p1; sums[2] += p2; sums[3] += p3;
-            pk[c / 2] = pack_bf16(p0, p1);
-            pk[c / 2 + 1] = pack_bf16(p2, p3);
-          }
-          tmem_st16(tS + ch * 16, pk);
-        }
-        l[x] = l[x] * alpha + ((sums[0] + sums[1]) + (sums[2] + sums[3]));
-        tmem_wait_st();
-        tc_fence_before();
-        mbar_arrive(&p_full[x]);
-        ++step[x];
+          for (int e = 0; e < 8; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(r[c + e]));
+        m_blk = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
       }
+      m_blk *= p.scale_log2;     // scale > 0: max(s) * c == max(s * c)
+      // lazy running maximum
+      float alpha = 1.f;
+      bool rescale = false;
+      if (m_blk > m_used + kRescaleThreshold || (m_used == -INFINITY && m_blk > -INFINITY)) {
+        alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_blk);
+        rescale = (m_used != -INFINITY);
+        m_used = m_blk;
+      }
+      const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
+      // the previous P V of this tile must be complete before O is rescaled; the score columns are
+      // free anyway (this S was computed after that P V was issued)
+      if (step > 0) {
+        if (!mbar_wait(&o_done[x], (step - 1) & 1, p.status, kTimeoutAccFull, 49)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+          for (int c = 0; c < FWD_DV / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(tO + c * 32, o);
+            tmem_wait_ld();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+            tmem_st32(tO + c * 32, o);
+          }
+        }
+      }
+      // P = exp2(s * c - m), packed bf16 over the first 64 of the 128 score columns (masked scores
+      // are -inf and give exactly 0)
+      // The exponentials of one step cost 2048 MUFU cycles per scheduler for the two tiles, as much
+      // as the step's MMAs; every fourth one is evaluated on the FMA pipe instead (exp2_fma).
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int ch = 0; ch < 4; ++ch) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int c = 0; c < 32; c += 4) {
+          const float p0 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c]), p.scale_log2, -m_safe));
+          const float p1 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 1]), p.scale_log2, -m_safe));
+          const float p2 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 2]), p.scale_log2, -m_safe));
+          const float p3 = exp2_fma(fmaf(__uint_as_float(r[ch * 32 + c + 3]), p.scale_log2, -m_safe));
+          sums[0] += p0; sums[1] += p1; sums[2] += p2; sums[3] += p3;
+          pk[c / 2] = pack_bf16(p0, p1);
+          pk[c / 2 + 1] = pack_bf16(p2, p3);
+        }
+        tmem_st16(tS + ch * 16, pk);
+      }
+      const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
+      l = l * alpha + sum;
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_full[x]);
+      ++step;
     }
 
     // ---- epilogue: O / l, log-sum-exp
+    if (ok && step > 0) ok = mbar_wait(&o_done[x], (step - 1) & 1, p.status, kTimeoutAccFull, 50);
+    tc_fence_after();
+    const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+    if (row_ok && p.lse) {
+      const float lse = (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : INFINITY;
+      p.lse[((long long)b * p.Hq + hq) * p.Sq + row] = lse;
+    }
+    __nv_bfloat16* orow = p.O + grow * p.ldo + (long long)hq * FWD_DV;
 #pragma unroll 1
-    for (int x = 0; x < 2; ++x) {
-      const uint32_t tO = tmem_base + 256 + x * F2_T + lane_addr;
-      bool okx = ok;
-      if (okx && step[x] > 0) okx = mbar_wait(&o_done[x], (step[x] - 1) & 1, p.status, kTimeoutAccFull, 50);
-      tc_fence_after();
-      const float inv_l = (l[x] > 0.f) ? 1.f / l[x] : 0.f;
-      if (row_ok[x] && p.lse) {
-        const float lse = (l[x] > 0.f) ? (m_used[x] + log2f(l[x])) * 0.6931471805599453f : INFINITY;
-        p.lse[((long long)b * p.Hq + hq) * p.Sq + row[x]] = lse;
+    for (int c = 0; c < FWD_DV / 32; ++c) {
+      uint32_t o[32];
+      if (step > 0 && ok) {
+        tmem_ld32(tO + c * 32, o);
+        tmem_wait_ld();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[e] = 0;
       }
-      __nv_bfloat16* orow = p.O + ((long long)b * p.Sq + row[x]) * p.ldo + (long long)hq * FWD_DV;
-#pragma unroll 1
-      for (int c = 0; c < FWD_DV / 32; ++c) {
-        uint32_t o[32];
-        if (step[x] > 0 && okx) {
-          tmem_ld32(tO + c * 32, o);
-          tmem_wait_ld();
-        } else {
+      if (row_ok) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = 0;
-        }
-        if (row_ok[x]) {
+        for (int v = 0; v < 4; ++v) {
+          float f[8];
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            float f[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[8 * v + e]) * inv_l;
-            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) =
-                make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
-          }
+          for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[8 * v + e]) * inv_l;
+          *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) =
+              make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
         }
       }
     }
@@ -817,7 +808,9 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
   // TPB_ATTN_FWD_V2=1 selects the two-tile, 128-key-step kernel.  It is correct but not yet faster
   // than the 64-key kernel (0.63 ms against 0.59 ms at B=1, S=8192, 32/8 heads): with ten warps per
   // CTA a thread gets 168 registers, the 128 scores of a row spill, and the softmax of one step
-  // takes about 2500 clocks against 1024 clocks of MMAs per tile.
+  // takes about 2500 clocks against 1024 clocks of MMAs per tile.  One softmax warpgroup serving
+  // both tiles (six warps, 210 registers, no spills) was slower still (1.04 ms): a single warp per
+  // scheduler cannot hide the TMEM and MUFU latencies.
   static const bool use_v2 = []() { const char* v = getenv("TPB_ATTN_FWD_V2"); return v && v[0] == '1'; }();
   if (dqk == 128 && use_v2) {
     // two query tiles per CTA, 128-key steps

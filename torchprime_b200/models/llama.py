@@ -37,6 +37,10 @@ class LlamaRMSNorm(nn.Module):
   def forward(self, x):
     return ops.rms_norm(x, self.weight, self.variance_epsilon)
 
+  def with_residual(self, x):
+    """(norm(x), x) where the returned ``x`` is the one to feed the residual connection with."""
+    return ops.rms_norm_residual(x, self.weight, self.variance_epsilon)
+
 
 class LlamaMLP(nn.Module):
   def __init__(self, config):
@@ -90,15 +94,19 @@ class LlamaAttention(nn.Module):
         bias = torch.cat([self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
       qkv = ops.linear(x, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], bias=bias)
       qkv = ops.rope_inplace(qkv, rope_cos, rope_sin, hq + hkv, d, s, pos=position_ids)
-      q = qkv[..., : hq * d].view(b, s, hq, d)
-      k = qkv[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
-      v = qkv[..., (hq + hkv) * d:].view(b, s, hkv, d)
-      if cp is not None:
-        o = cp.attention(q, k, v, segment_ids=segment_ids)
-      elif self.attention_kernel is None and not x.is_cuda:
-        o = ref.attention(q, k, v, causal=True, q_segment_ids=segment_ids)
+      if cp is None and x.is_cuda:
+        # one autograd input, one gradient (see ops.attention_qkv)
+        o = ops.attention_qkv(qkv, hq, hkv, d, causal=True, q_segment_ids=segment_ids)
       else:
-        o = ops.attention(q, k, v, causal=True, q_segment_ids=segment_ids)
+        q = qkv[..., : hq * d].view(b, s, hq, d)
+        k = qkv[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+        v = qkv[..., (hq + hkv) * d:].view(b, s, hkv, d)
+        if cp is not None:
+          o = cp.attention(q, k, v, segment_ids=segment_ids)
+        elif self.attention_kernel is None:
+          o = ref.attention(q, k, v, causal=True, q_segment_ids=segment_ids)
+        else:
+          o = ops.attention(q, k, v, causal=True, q_segment_ids=segment_ids)
       o = o.reshape(b, s, hq * d)
       if self.tp_group is not None:
         out = reduce_from_tp(ops.linear(o, self.o_proj.weight), self.tp_group)
@@ -121,10 +129,10 @@ class LlamaDecoderLayer(nn.Module):
 
   def forward(self, hidden_states, rope_cos, rope_sin, position_ids=None, segment_ids=None, cp=None):
     with trace_scope("LlamaDecoderLayer"):
-      x = self.input_layernorm(hidden_states)
+      x, hidden_states = self.input_layernorm.with_residual(hidden_states)
       h = self.self_attn(x, rope_cos, rope_sin, residual=hidden_states, position_ids=position_ids,
                          segment_ids=segment_ids, cp=cp)
-      x = self.post_attention_layernorm(h)
+      x, h = self.post_attention_layernorm.with_residual(h)
       return self.mlp(x, residual=h)
 
 

@@ -160,6 +160,47 @@ class _AttentionFn(torch.autograd.Function):
     return dq, dk, dv, None, None, None, None, None, None
 
 
+class _AttentionQKVFn(torch.autograd.Function):
+  """Attention on one fused projection output ``qkv`` [B, S, (Hq + 2 Hkv) * D] (queries, keys, values
+  back to back in every row).  A single autograd input means a single gradient: the backward
+  kernels write dQ, dK and dV into the column ranges of one buffer, which goes straight to the
+  projection's GEMMs.  With three sliced inputs autograd would materialise each slice's gradient as
+  a zero-filled full-width tensor and add the three (three fills, three copies and two adds of
+  100 MB per layer)."""
+
+  @staticmethod
+  def forward(ctx, qkv, hq, hkv, d, causal, scale, window, q_pos, q_seg, kv_seg):
+    b, s, _ = qkv.shape
+    q = qkv[..., : hq * d].view(b, s, hq, d)
+    k = qkv[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+    v = qkv[..., (hq + hkv) * d:].view(b, s, hkv, d)
+    o, lse = attn_fwd(q, k, v, causal, scale, window, q_pos, q_seg, kv_seg)
+    ctx.save_for_backward(qkv, o, lse, q_pos, q_seg, kv_seg)
+    ctx.args = (hq, hkv, d, causal, scale, window)
+    return o
+
+  @staticmethod
+  def backward(ctx, do):
+    qkv, o, lse, q_pos, q_seg, kv_seg = ctx.saved_tensors
+    hq, hkv, d, causal, scale, window = ctx.args
+    b, s, _ = qkv.shape
+    q = qkv[..., : hq * d].view(b, s, hq, d)
+    k = qkv[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+    v = qkv[..., (hq + hkv) * d:].view(b, s, hkv, d)
+    buf = torch.empty_like(qkv)
+    dq = buf[..., : hq * d].view(b, s, hq, d)
+    dk = buf[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+    dv = buf[..., (hq + hkv) * d:].view(b, s, hkv, d)
+    attn_bwd(do, q, k, v, o, lse, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk, dv)
+    return buf, None, None, None, None, None, None, None, None, None
+
+
+def attention_qkv(qkv, hq, hkv, d, causal=True, scale=None, window=None, q_segment_ids=None, q_positions=None):
+  """Self-attention on a fused [B, S, (Hq + 2 Hkv) * D] projection (head dim 128, contiguous)."""
+  seg = _i32(q_segment_ids)
+  return _AttentionQKVFn.apply(qkv, hq, hkv, d, causal, scale, window, _i32(q_positions), seg, seg)
+
+
 def _fused_qkv_layout(q, k, v):
   if q.shape[-1] != v.shape[-1] or q.shape[1] != k.shape[1]:
     return None

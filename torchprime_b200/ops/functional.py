@@ -269,6 +269,38 @@ def rms_norm(x, w, eps):
   return ref.rms_norm(x, w, eps)
 
 
+class _RMSNormPassFn(torch.autograd.Function):
+  """(rmsnorm(x) * w, x): the second output is ``x`` itself, handed on as the residual input of a
+  later operator.  Its purpose is the backward: the gradient of the normalised branch and the
+  gradient of the residual branch arrive together and are summed inside the norm-backward kernel,
+  instead of by a separate elementwise add of two activation-sized tensors per norm."""
+
+  @staticmethod
+  def forward(ctx, x, w, eps):
+    from . import kernels as k
+    xc = x.contiguous()
+    y, rstd, _ = k.rmsnorm_fwd(xc, w, eps)
+    ctx.save_for_backward(xc, w, rstd)
+    return y, x.view_as(x)
+
+  @staticmethod
+  def backward(ctx, dy, dres):
+    from . import kernels as k
+    x, w, rstd = ctx.saved_tensors
+    if dy is None:
+      return dres, None, None
+    dx, dw = k.rmsnorm_bwd(dy.contiguous(), x, w, rstd, dres=dres.contiguous() if dres is not None else None)
+    return dx, (_norm_wgrad(w, dw) if ctx.needs_input_grad[1] else None), None
+
+
+def rms_norm_residual(x, w, eps):
+  """Returns (rmsnorm(x) * w, x).  Use the second value wherever ``x`` is needed again (the
+  residual connection): its gradient is then added inside the norm's backward kernel."""
+  if use_kernels(x, w) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
+    return _RMSNormPassFn.apply(x, w, eps)
+  return ref.rms_norm(x, w, eps), x
+
+
 def add_rms_norm(x, res, w, eps):
   """(rmsnorm(x + res) * w, x + res) with the add fused into the norm kernel."""
   if use_kernels(x, res, w) and x.shape[-1] % 8 == 0 and x.shape[-1] <= 8192:
@@ -294,7 +326,10 @@ class _RopeInplaceFn(torch.autograd.Function):
     heads, dim, seq_len, interleaved, has_pos, col0, head_stride = ctx.args
     saved = ctx.saved_tensors
     pos = saved[2] if has_pos else None
-    d = dqkv.contiguous().clone() if not dqkv.is_contiguous() else dqkv.clone()
+    # The incoming gradient is a buffer the attention backward produced for this node alone (RoPE is
+    # applied in place on the projection output, so nothing else consumes that tensor's gradient):
+    # rotate it in place instead of cloning 100 MB per layer.
+    d = dqkv if dqkv.is_contiguous() else dqkv.contiguous()
     k.rope_(d.view(-1, d.shape[-1]), col0, heads, dim, saved[0], saved[1], seq_len, pos=pos, inverse=True,
             interleaved=interleaved, head_stride=head_stride)
     return d, None, None, None, None, None, None, None, None, None
@@ -428,6 +463,24 @@ def attention(q, k, v, causal=True, scale=None, window=None, q_segment_ids=None,
   return ref.attention(q, k, v, causal=causal, scale=scale, window=window, q_segment_ids=q_segment_ids,
                        kv_segment_ids=kv_segment_ids, softcap=softcap, q_positions=q_positions,
                        kv_positions=kv_positions)
+
+
+def attention_qkv(qkv, hq, hkv, d, causal=True, scale=None, window=None, q_segment_ids=None, q_positions=None):
+  """Self-attention on a fused projection output ``qkv`` [B, S, (Hq + 2 Hkv) * d]: same result as
+  slicing q, k, v out of it and calling :func:`attention`, but on the kernel path the tensor is a
+  single autograd input, so its gradient is produced in one piece."""
+  b, s, _ = qkv.shape
+  if (_STATE["attention"] in ("auto", "sm100") and _STATE["backend"] != "torch" and qkv.is_cuda
+      and qkv.dtype == torch.bfloat16 and d == 128 and qkv.is_contiguous()):
+    from . import attention_sm100
+    _ATTN_USED["last"] = "sm100 tcgen05 kernel"
+    return attention_sm100.attention_qkv(qkv, hq, hkv, d, causal=causal, scale=scale, window=window,
+                                         q_segment_ids=q_segment_ids, q_positions=q_positions)
+  q = qkv[..., : hq * d].view(b, s, hq, d)
+  k = qkv[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
+  v = qkv[..., (hq + hkv) * d:].view(b, s, hkv, d)
+  return attention(q, k, v, causal=causal, scale=scale, window=window, q_segment_ids=q_segment_ids,
+                   q_positions=q_positions)
 
 
 # --------------------------------------------------------------------------- lm head + CE
