@@ -85,6 +85,7 @@ struct GemmParams {
   // Reduce-scatter fusion (TPB_EPI_RS_BF16): the epilogue adds alpha * acc straight into the
   // owner's bf16 gradient shard over P2P with vector red.add.
   int rs_world;
+  int tile_rot;                 // tiles are visited starting from this one (rotation by rank, see tpb_gemm_rs_bf16)
   void* rs_dst[8];              // gradient shard base of every rank (symmetric memory), bf16
   long long rs_shard_elems;
   long long rs_c_offset;        // element offset of C inside the sharded flat buffer
@@ -108,6 +109,11 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 
 __device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int t, int m_tiles, int n_tiles, int num_kb) {
   TileInfo ti;
+  if (p.tile_rot) {
+    const int total = m_tiles * n_tiles * (p.mode == 2 ? p.num_experts : 1);
+    t += p.tile_rot;
+    if (t >= total) t -= total;
+  }
   ti.e = 0; ti.kb0 = 0; ti.kb1 = num_kb; ti.skip = false;
   if (p.mode == 2) {
     const int per = m_tiles * n_tiles;
@@ -707,6 +713,7 @@ struct GemmCall {
   unsigned* ag_flags; unsigned ag_epoch;
   void* const* ag_push_dst; unsigned* const* ag_push_flags;
   int rs_world; void* const* rs_dst; long long rs_shard_elems, rs_c_offset;
+  int rs_rank;
 };
 
 static int run_gemm(const GemmCall& g, cudaStream_t stream) {
@@ -759,6 +766,7 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.ag_dst = g.ag_dst; p.ag_shard_elems = g.ag_shard_elems; p.ag_chunk_elems = 16384; p.ag_b_offset = g.ag_b_offset;
   p.ag_flags = g.ag_flags; p.ag_epoch = g.ag_epoch; p.ag_local = g.ag_world > 0 ? g.ag_local : -1;
   p.rs_world = g.rs_world; p.rs_shard_elems = g.rs_shard_elems; p.rs_c_offset = g.rs_c_offset;
+  p.tile_rot = 0;
   p.ag_push = (g.ag_world > 0 && g.ag_push_dst != nullptr && g.ag_push_flags != nullptr) ? 1 : 0;
   if (p.ag_push) p.ag_chunk_elems = 131072;   // 256 KB per flag: a CTA streams a chunk with one fence at its end
   for (int i = 0; i < 8; ++i) {
@@ -784,6 +792,8 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   int cap = sm_count() - p.ag_copiers;
   if (g.max_ctas > 0 && g.max_ctas < cap) cap = g.max_ctas;
   const int grid = (tiles > cap ? cap : (int)tiles) + p.ag_copiers;
+  if (g.epi == TPB_EPI_RS_BF16 && g.rs_world > 1 && g.rs_rank > 0)
+    p.tile_rot = (int)(tiles * g.rs_rank / g.rs_world);   // every rank starts in a different owner's part of C
   cudaError_t e;
   // CTA pairs for dense GEMMs with enough 256 x 256 tiles to fill the machine (TPB_GEMM_PAIR=0
   // keeps the single-CTA kernel)
@@ -894,7 +904,7 @@ extern "C" int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, lon
 // barrier) before the first contributing kernel, and a barrier must follow the last one.
 extern "C" int tpb_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
                                 long long ldc, int a_mn, int b_mn, float alpha, void* const* shard_ptrs, int world,
-                                long long shard_elems, long long c_offset, void* stream_) {
+                                long long shard_elems, long long c_offset, int rank, void* stream_) {
   GemmCall g{};
   g.A = A; g.B = B; g.B2 = nullptr; g.C = shard_ptrs[0];
   g.M = M; g.N = N; g.K = K; g.E = 1;
@@ -902,5 +912,6 @@ extern "C" int tpb_gemm_rs_bf16(const void* A, const void* B, int M, int N, int 
   g.a_mn = a_mn; g.b_mn = b_mn; g.epi = TPB_EPI_RS_BF16; g.alpha = alpha;
   g.mode = 0;
   g.rs_world = world; g.rs_dst = shard_ptrs; g.rs_shard_elems = shard_elems; g.rs_c_offset = c_offset;
+  g.rs_rank = rank;
   return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
 }

@@ -103,7 +103,7 @@ int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, long long lda,
                      unsigned* const* push_flags, void* stream);
 int tpb_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, long long ldc,
                      int a_mn, int b_mn, float alpha, void* const* shard_ptrs, int world, long long shard_elems,
-                     long long c_offset, void* stream);
+                     long long c_offset, int rank, void* stream);
 
 // Router: one warp per token.  mode 0 softmax-top-k(-renormalise); mode 1 sigmoid + bias with
 // group-limited selection.  w_out [T,K] fp32, idx_out [T,K] int32, scores_out [T,E] fp32 (optional).

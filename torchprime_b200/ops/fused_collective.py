@@ -27,7 +27,7 @@ from ._lib import check, lib, ptr, stream_ptr
 
 P, I, LL, FL, U = c_void_p, c_int, c_longlong, c_float, c_uint
 _lib.register_signature("tpb_ag_gemm_bf16", [P, P, I, I, I, LL, LL, I, P, LL, P, LL, P, I, LL, P, LL, P, U, I, I, P, P, P])
-_lib.register_signature("tpb_gemm_rs_bf16", [P, P, I, I, I, LL, LL, LL, I, I, FL, P, I, LL, LL, P])
+_lib.register_signature("tpb_gemm_rs_bf16", [P, P, I, I, I, LL, LL, LL, I, I, FL, P, I, LL, LL, I, P])
 
 CHUNK_ELEMS = 16384
 
@@ -94,5 +94,6 @@ def gemm_rs(a, b, *, a_mn, b_mn, m, n, ldc, grad_shards, shard_elems: int, c_off
   k = a.shape[0] if a_mn else a.shape[1]
   table = grad_shards.ptr_table(shard_offset)
   rc = lib().tpb_gemm_rs_bf16(ptr(a), ptr(b), m, n, k, a.stride(0), b.stride(0), ldc, int(a_mn), int(b_mn),
-                              float(alpha), table, grad_shards.world, shard_elems, c_offset, stream_ptr())
+                              float(alpha), table, grad_shards.world, shard_elems, c_offset, grad_shards.rank,
+                              stream_ptr())
   check(rc, f"gemm_rs M={m} N={n} K={k} world={grad_shards.world}")
