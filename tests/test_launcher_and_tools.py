@@ -76,3 +76,16 @@ def test_system_check_and_benchmark_row(tmp_path):
                                                           "task": {"global_batch_size": 8}, "dataset": {"block_size": 128}}))
   row = benchmark_db_util.append_row(str(tmp_path), str(tmp_path / "db.jsonl"))
   assert row["hardware_num_chips"] == 8 and row["metrics_mfu"] == 0.3 and os.path.exists(tmp_path / "db.jsonl")
+
+
+def test_aux_scripts_parse_arguments(tmp_path):
+  """The asset snapshot tool and the comparison scripts are importable and explain themselves."""
+  import importlib
+  import pytest
+  mod = importlib.import_module("torchprime_b200.launcher.save_hf_assets")
+  with pytest.raises(SystemExit):
+    mod.main(["--dest", str(tmp_path)])          # neither a repo nor a dataset given
+  draw = importlib.import_module("torchprime_b200.experimental.hf_trainer_sft.draw_figure")
+  log = tmp_path / "train.log"
+  log.write_text("step 1 loss: 1.25\nstep 2 loss: 0.75 lr: 1e-4\n")
+  assert draw.losses_from_log(str(log)) == [1.25, 0.75]
