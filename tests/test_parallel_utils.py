@@ -141,3 +141,24 @@ def test_model_size_parsing():
   assert extract_model_size_from_model_name("llama-3.1-70b") == 70
   assert extract_model_size_from_model_name("mixtral-8x7b") == 56
   assert extract_model_size_from_model_name("llama-tiny") == -1
+
+
+def test_homogeneous_sequential_passes_keyword_arguments_to_every_layer():
+  import pytest
+  import torch
+  import torch.nn as nn
+  from torchprime_b200.layers import HomogeneousSequential
+
+  class Scale(nn.Module):
+    def __init__(self, k):
+      super().__init__()
+      self.k = k
+
+    def forward(self, x, bias=None):
+      return x * self.k + bias
+
+  stack = HomogeneousSequential(Scale(2.0), Scale(3.0))
+  out = stack(torch.ones(2), bias=torch.full((2,), 1.0))
+  assert torch.equal(out, torch.full((2,), 10.0))          # (1*2+1)*3+1
+  with pytest.raises(AssertionError):
+    HomogeneousSequential(Scale(1.0), nn.ReLU())

@@ -67,3 +67,25 @@ def test_train_loop_writes_metrics_and_profile(cuda_lib, tmp_path):
   assert metrics["num_steps"] == 8 and metrics["step_execution_time"] > 0 and metrics["tokens_per_second"] > 0
   assert os.path.exists(tmp_path / "out" / "train_config.json")
   assert any(f.endswith(".json") for f in os.listdir(tmp_path / "profile"))
+
+
+@pytest.mark.gpu
+def test_graphed_forward_replays_the_kernel_path():
+  """One CUDA-graph launch reproduces the eager forward of a small Llama (all layers, custom kernels)."""
+  import torch
+  from torchprime_b200.config import compose
+  from torchprime_b200.models.model_utils import initialize_model_class
+  from torchprime_b200.utils.cuda_graphs import GraphedForward
+  cfg = compose("default", ["model=llama-tiny"])
+  torch.manual_seed(0)
+  model = initialize_model_class(cfg.model).to("cuda", torch.bfloat16).eval()
+  model.return_logits = True
+  ids = torch.randint(0, cfg.model.vocab_size, (2, 128), device="cuda")
+  with torch.no_grad():
+    want, _ = model(ids)
+    graphed = GraphedForward(lambda x: model(x)[0])
+    got = graphed(ids).clone()
+    ids2 = torch.randint(0, cfg.model.vocab_size, (2, 128), device="cuda")
+    want2, _ = model(ids2)
+    got2 = graphed(ids2).clone()
+  assert torch.equal(got, want) and torch.equal(got2, want2)

@@ -36,24 +36,17 @@ def run_model_eager(model, batch_size: int, number_of_runs: int, device: torch.d
 
 def run_model_graph(model, batch_size: int, number_of_runs: int, device: torch.device) -> list[float]:
   """Capture one forward in a CUDA graph and time replays (the compile-once analogue)."""
+  from ..utils.cuda_graphs import GraphedForward
   assert device.type == "cuda", "graph mode needs a CUDA device"
   model = model.to(device).eval()
   args, kwargs = pytree.tree_map_only(torch.Tensor, lambda t: t.to(device), model.get_sample_inputs(batch_size))
-  with torch.no_grad():
-    s = torch.cuda.Stream()
-    s.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(s):
-      for _ in range(3):
-        model(*args, **kwargs)
-    torch.cuda.current_stream().wait_stream(s)
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g):
-      model(*args, **kwargs)
+  graphed = GraphedForward(model)
+  graphed(*args, **kwargs)          # warm-up and capture
   times = []
   for _ in range(number_of_runs):
     _sync(device)
     t0 = time.perf_counter()
-    g.replay()
+    graphed(*args, **kwargs)
     _sync(device)
     times.append(time.perf_counter() - t0)
   return times
