@@ -112,11 +112,24 @@ def attn_bwd(do, q, k, v, o, lse, causal=True, scale=None, window=None, q_pos=No
 
 
 def _eager_bwd(do, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk, dv):
-  """Gradient through the fp32 eager definition, one batch element at a time.  Used for
-  shapes the backward kernel does not cover yet (q/k head dim 192)."""
+  """Gradients for shapes the backward kernel does not cover yet (q/k head dim 192).  Plain causal
+  or full attention goes through torch's scaled_dot_product_attention (a library call: forward is
+  recomputed with autograd on); masks it cannot express fall back to the fp32 eager definition,
+  one batch element at a time."""
   from . import reference as ref
   b, sq = q.shape[0], q.shape[1]
   sk = k.shape[1]
+  if window is None and q_pos is None and q_seg is None and kv_seg is None and (not causal or sq == sk):
+    try:
+      with torch.enable_grad():
+        qf, kf, vf = (t.detach().transpose(1, 2).requires_grad_(True) for t in (q, k, v))
+        o = torch.nn.functional.scaled_dot_product_attention(qf, kf, vf, is_causal=bool(causal), scale=scale,
+                                                             enable_gqa=q.shape[2] != k.shape[2])
+        gq, gk, gv = torch.autograd.grad(o, (qf, kf, vf), do.transpose(1, 2))
+      dq.copy_(gq.transpose(1, 2)); dk.copy_(gk.transpose(1, 2)); dv.copy_(gv.transpose(1, 2))
+      return dq, dk, dv
+    except RuntimeError:
+      pass   # no backend for this shape: use the eager definition below
   for i in range(b):
     with torch.enable_grad():
       qf, kf, vf = (t[i:i + 1].detach().float().requires_grad_(True) for t in (q, k, v))
