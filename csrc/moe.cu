@@ -233,6 +233,67 @@ static inline int grid_for_items(long long items, int threads, int waves = 8) {
   return blocks < 1 ? 1 : (int)blocks;
 }
 
+
+// ----------------------------------------------------------------------------
+// Variable-size all-to-all of rows over NVLink, done by this GPU's own stores (expert-parallel
+// dispatch and return).  Rows [src_start[r], src_start[r+1]) of `src` go to rank r's receive buffer,
+// starting at row dst_row0[r] there; plain 16-byte stores to peer memory (posted writes).  When the
+// last CTA has finished, the flag "rank `me` has delivered" is raised in every rank's flag array.
+// ----------------------------------------------------------------------------
+struct A2APushParams {
+  const uint4* src;
+  int vec_per_row;
+  int n_rows;
+  int world, me;
+  int src_start[9];
+  long long dst_row0[8];
+  uint4* dst[8];
+  unsigned* flags[8];
+  unsigned epoch;
+  unsigned* done_counter;   // one zero-initialised word of local memory
+};
+
+__global__ void a2a_push_kernel(const A2APushParams p) {
+  for (int row = blockIdx.x; row < p.n_rows; row += gridDim.x) {
+    int r = 0;
+    while (r + 1 < p.world && row >= p.src_start[r + 1]) ++r;
+    const uint4* s = p.src + (long long)row * p.vec_per_row;
+    uint4* d = p.dst[r] + (p.dst_row0[r] + (row - p.src_start[r])) * p.vec_per_row;
+    for (int i = threadIdx.x; i < p.vec_per_row; i += blockDim.x) d[i] = s[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(p.done_counter, 1u);
+    if (prev == gridDim.x - 1) {          // every CTA's stores are fenced: publish
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[r] + p.me), "r"(p.epoch) : "memory");
+      *p.done_counter = 0;
+    }
+  }
+}
+
+// Stream-ordered wait (bounded) until every rank has delivered its rows for `epoch`.
+__global__ void a2a_wait_kernel(const unsigned* flags, int world, unsigned epoch, int* status) {
+  if (threadIdx.x != 0) return;
+  for (int r = 0; r < world; ++r) {
+    long long t0 = 0;
+    int spins = 0;
+    while (true) {
+      unsigned v;
+      asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + r) : "memory");
+      if (v == epoch) break;
+      if (++spins == 64) {
+        spins = 0;
+        if (t0 == 0) t0 = clock64();
+        else if (clock64() - t0 > kSpinBudgetCycles) { report(status, kTimeoutPeerFlag, 61); return; }
+        __nanosleep(200);
+      }
+    }
+  }
+}
+
 }  // namespace tpb
 
 using namespace tpb;
@@ -281,5 +342,31 @@ extern "C" int tpb_moe_combine_dw(const void* rows, const int* dest, const void*
   if (tokens <= 0) return 0;
   moe_combine_dw_kernel<<<grid_for_items(tokens * K * 32, 256), 256, 0, STREAM(stream)>>>(
       (const uint4*)rows, dest, (const uint4*)dout, dw, tokens * K, K, dim / 8);
+  return rc_of(cudaGetLastError());
+}
+
+// src: [n_rows, dim] bf16 rows sorted by destination rank; src_start[world + 1] row offsets of the
+// blocks; dst_row0[r]: first row of this rank's block in rank r's receive buffer dst[r]; flags[r]:
+// rank r's flag array (one word per source rank); done_counter: a zero-initialised local word.
+extern "C" int tpb_a2a_push_rows(const void* src, int n_rows, int dim, int world, int me, const int* src_start,
+                                 const long long* dst_row0, void* const* dst, unsigned* const* flags, unsigned epoch,
+                                 unsigned* done_counter, void* stream) {
+  if (dim % 8 || world < 1 || world > 8 || me < 0 || me >= world) return -2;
+  A2APushParams p{};
+  p.src = (const uint4*)src; p.vec_per_row = dim / 8; p.n_rows = n_rows; p.world = world; p.me = me;
+  for (int r = 0; r <= world; ++r) p.src_start[r] = src_start[r];
+  for (int r = 0; r < world; ++r) {
+    p.dst_row0[r] = dst_row0[r];
+    p.dst[r] = (uint4*)dst[r];
+    p.flags[r] = flags[r];
+  }
+  p.epoch = epoch; p.done_counter = done_counter;
+  int grid = n_rows < 1 ? 1 : (n_rows < 4 * sm_count() ? n_rows : 4 * sm_count());
+  a2a_push_kernel<<<grid, 256, 0, STREAM(stream)>>>(p);
+  return rc_of(cudaGetLastError());
+}
+
+extern "C" int tpb_a2a_wait(const unsigned* flags, int world, unsigned epoch, void* stream) {
+  a2a_wait_kernel<<<1, 32, 0, STREAM(stream)>>>(flags, world, epoch, status_block());
   return rc_of(cudaGetLastError());
 }

@@ -120,6 +120,12 @@ int tpb_moe_combine(const void* rows, const int* dest, const float* w, void* out
 int tpb_moe_combine_dw(const void* rows, const int* dest, const void* dout, float* dw, long long tokens, int K,
                        int dim, void* stream);
 
+// Variable-size all-to-all of rows by plain stores into the peers' receive buffers (moe.cu).
+int tpb_a2a_push_rows(const void* src, int n_rows, int dim, int world, int me, const int* src_start,
+                      const long long* dst_row0, void* const* dst, unsigned* const* flags, unsigned epoch,
+                      unsigned* done_counter, void* stream);
+int tpb_a2a_wait(const unsigned* flags, int world, unsigned epoch, void* stream);
+
 // Flash attention (attention_fwd_sm100.cu / attention_bwd_sm100.cu); token-major [B*S, heads*dim] views.
 int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int Hq,
                  int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv, long long ldo, float scale,

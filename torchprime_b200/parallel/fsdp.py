@@ -85,7 +85,8 @@ class FSDPEngine:
   def __init__(self, model: nn.Module, mesh, plan=None, *, device=None, param_dtype=torch.bfloat16,
                grad_dtype=None, master_weights: bool = True, remat_classes=(), offload_tensors=(),
                init_std: float | None = None, seed: int = 42, materialize: bool | None = None,
-               fused_collectives: bool = False, remat_policy: str | int = "all"):
+               fused_collectives: bool = False, remat_policy: str | int = "all",
+               fused_expert_exchange: bool = False):
     self.model = model
     self.mesh = mesh
     self.plan = plan
@@ -112,6 +113,7 @@ class FSDPEngine:
     self.seed = seed
     self.init_std = init_std if init_std is not None else getattr(getattr(model, "config", None), "initializer_range", 0.02)
     self.fused_collectives = fused_collectives
+    self.fused_expert_exchange = fused_expert_exchange   # expert-parallel dispatch/return by PushAllToAll
     self.remat_classes = set(remat_classes or ())
     self.offload_tensors = set(offload_tensors or ())
     # Which of the units named by ``remat_classes`` really recompute their forward in backward:
@@ -330,7 +332,8 @@ class FSDPEngine:
       from .ep import ExpertParallelMLP
       for mod in self.model.modules():
         if hasattr(mod, "ep") and hasattr(mod, "num_experts"):
-          mod.ep = ExpertParallelMLP(self.mesh, mod.num_experts)
+          mod.ep = ExpertParallelMLP(self.mesh, mod.num_experts,
+                                     fused_exchange=self.fused_expert_exchange and self.is_cuda)
 
   def unwrap(self):
     for u in self.units:

@@ -93,7 +93,8 @@ class Trainer:
       master_weights=bool(eng.get("master_weights", True)),
       remat_classes=self.remat_plan.remat_classes, offload_tensors=self.remat_plan.offload_tensors,
       seed=int(self.config.get("seed", 42)), fused_collectives=bool(eng.get("fused_collectives", False)),
-      remat_policy=_remat_policy(eng.get("remat_layers", "auto")))
+      remat_policy=_remat_policy(eng.get("remat_layers", "auto")),
+      fused_expert_exchange=bool(eng.get("fused_expert_exchange", False)))
     _move_buffers(model, self.device)
     if hasattr(model, "return_logits"):
       model.return_logits = not bool(eng.get("chunked_ce", True))
