@@ -116,6 +116,27 @@ def main():
   out["cp_attention_fwd"] = {"fused_ms": t_cp_fused, "nccl_allgather_then_attention_ms": t_cp_nccl,
                              "roofline_ms": roof5, "fraction_of_roofline": roof5 / t_cp_fused,
                              "nvlink_bytes_in": link5, "keys_per_rank": s_loc}
+  # ---- F4: expert-parallel MLP forward (Mixtral layer: 8 experts, top-2), dispatch/return by push kernel
+  from torchprime_b200.parallel.ep import ExpertParallelMLP
+  emesh = Mesh(shape={"data": 1, "fsdp": 1, "tensor": 1, "expert": world, "context": 1}, rank=rank, world_size=world)
+  E, topk, Tm = 8, 2, 8192
+  el = E // world
+  wg = (torch.randn(el, D, F, device=dev) * 0.02).to(torch.bfloat16)
+  wu = (torch.randn(el, D, F, device=dev) * 0.02).to(torch.bfloat16)
+  wd = (torch.randn(el, F, D, device=dev) * 0.02).to(torch.bfloat16)
+  xm = torch.randn(Tm, D, device=dev, dtype=torch.bfloat16)
+  gidx = torch.stack([torch.randperm(E, device=dev)[:topk] for _ in range(Tm)]).to(torch.int32)
+  gw = torch.rand(Tm, topk, device=dev)
+  ep_nccl = ExpertParallelMLP(emesh, E, fused_exchange=False)
+  ep_push = ExpertParallelMLP(emesh, E, fused_exchange=True)
+  with torch.no_grad():
+    t_ep_nccl = timed(lambda: ep_nccl.grouped_mlp(xm, gw, gidx, wg, wu, wd))
+    t_ep_push = timed(lambda: ep_push.grouped_mlp(xm, gw, gidx, wg, wu, wd))
+  flops4 = 2.0 * Tm * topk * 3 * D * F
+  link4 = 2.0 * Tm * topk * D * 2 * (world - 1) / world        # rows out and back, remote fraction
+  roof4 = max(flops4 / (peak * 1e12), link4 / (NVLINK_GBS * 1e9)) * 1e3
+  out["ep_mlp_fwd"] = {"push_ms": t_ep_push, "nccl_all_to_all_ms": t_ep_nccl, "roofline_ms": roof4,
+                       "fraction_of_roofline": roof4 / t_ep_push, "nvlink_bytes_each_way": link4 / 2}
   torch.cuda.synchronize()
   _lib.raise_on_device_timeout()
   if rank == 0:
