@@ -203,3 +203,32 @@ def test_embedding(cuda_lib):
   dts = torch.zeros(250, D, device="cuda", dtype=torch.float32)
   k.embedding_bwd_(dout, ids, dts, row0=250)
   assert _rel_err(dts, want[250:500]) < 1e-5
+
+
+def test_tensor_kernels_are_bit_reproducible(cuda_lib):
+  """Two runs of the GEMM and of the attention forward and backward give identical bits: no result
+  depends on the order in which CTAs or atomics happen to run (a missing fence or a racy barrier
+  protocol shows up here as a flaky mismatch)."""
+  import torch
+  from torchprime_b200.ops import attention_sm100 as A
+  from torchprime_b200.ops import kernels as k
+  torch.manual_seed(3)
+  a = torch.randn(1024, 768, device="cuda", dtype=torch.bfloat16)
+  b = torch.randn(1280, 768, device="cuda", dtype=torch.bfloat16)
+  outs = [k.gemm(a, b).clone() for _ in range(3)]
+  assert all(torch.equal(outs[0], o) for o in outs[1:])
+  w = [k.gemm(a.t().contiguous(), b.t().contiguous()[:, :1024].contiguous(), a_mn=True, b_mn=True,
+              epi=k.EPI_F32).clone() for _ in range(2)]
+  assert torch.equal(w[0], w[1])
+  qkv = torch.randn(2, 640, (8 + 2 * 2) * 128, device="cuda", dtype=torch.bfloat16)
+  q = qkv[..., : 8 * 128].view(2, 640, 8, 128)
+  kk = qkv[..., 8 * 128: 10 * 128].view(2, 640, 2, 128)
+  v = qkv[..., 10 * 128:].view(2, 640, 2, 128)
+  res = []
+  for _ in range(2):
+    o, lse = A.attn_fwd(q, kk, v, causal=True)
+    do = torch.ones_like(o) * 0.01
+    dq, dk, dv = A.attn_bwd(do, q, kk, v, o, lse, causal=True)
+    res.append((o.clone(), lse.clone(), dq.clone(), dk.clone(), dv.clone()))
+  for x, y in zip(res[0], res[1]):
+    assert torch.equal(x, y)
