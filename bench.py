@@ -15,6 +15,10 @@ barrier + device synchronisation and timed with CUDA events (max over ranks):
   e2e    the public ``Trainer`` loop body: every step copies its batch from pinned host
          memory to the device and reads the loss back to the host.
 
+Other meshes of the same model: ``--override ici_mesh.tensor=2 --override model/sharding=llama-fsdp-tp``
+puts two ranks on the tensor axis (the rest stay on fsdp; global batch = per-GPU batch x the
+ranks that hold different sequences), likewise ``ici_mesh.context``.
+
 ``--impl reference`` reports why the unmodified reference cannot run here;
 ``--impl baseline`` runs this framework's cuBLAS + SDPA + torch-eager mode (no hand-written
 kernels) as the same-box comparator.  Rank 0 prints one JSON line.
@@ -139,11 +143,25 @@ def main():
     args.warmup = 3
 
   device = rt.init()
-  global_batch = args.per_gpu_batch * n
+  # Mesh: all N ranks on the fsdp axis unless overrides put some on tensor / context / expert / data.
+  mesh_ov = {}
+  for ov in args.override:
+    if ov.startswith("ici_mesh.") and "=" in ov:
+      mesh_ov[ov.split("=")[0][len("ici_mesh."):]] = int(ov.split("=")[1])
+  other = 1
+  for axis, size in mesh_ov.items():
+    if axis != "fsdp":
+      other *= size
+  fsdp = mesh_ov.get("fsdp", max(1, n // other))
+  batch_shards = fsdp * mesh_ov.get("data", 1)              # ranks that hold different sequences
+  global_batch = args.per_gpu_batch * batch_shards
+  parallelism = " x ".join(f"{a}{v}" for a, v in [("fsdp", fsdp)] + [(a, v) for a, v in sorted(mesh_ov.items())
+                                                                       if a != "fsdp" and v > 1])
+  parallelism = parallelism.replace(" x ", "_") if " x " in parallelism else parallelism
   overrides = [
     f"model={args.model}", "dataset=synthetic", f"dataset.block_size={args.seq_len}",
     f"task.global_batch_size={global_batch}", f"task.max_steps={args.steps * 2 + args.warmup + 8}",
-    "task.optimizer.type=adamw", "task.max_grad_norm=1.0", f"ici_mesh.fsdp={n}", "profile_start_step=-1",
+    "task.optimizer.type=adamw", "task.max_grad_norm=1.0", f"ici_mesh.fsdp={fsdp}", "profile_start_step=-1",
     "logging_steps=1000000", f"output_dir={tempfile.mkdtemp(prefix='tpb_bench_')}",
     f"dataset.num_samples={max(64, global_batch * 8)}",
   ]
@@ -232,7 +250,7 @@ def main():
       "gpu_launches": int(launches),
       "clocks": clocks,
       "config": {"model": args.model, "global_batch": global_batch, "seq_len": args.seq_len,
-                 "parallelism": f"fsdp{n}", "remat": trainer.engine.remat_summary(),
+                 "parallelism": parallelism, "remat": trainer.engine.remat_summary(),
                  "peak_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1), "optimizer": "adamw fp32 master+moments",
                  "l2": "no flush needed: each step streams >16 GB of weights/optimizer state, far above the 126 MB L2",
                  "baseline": "vs_baseline = value / (6.91k tok/s/chip x n_gpus), Llama-3-8B seq 8192 on TPU v6e-256",

@@ -143,6 +143,15 @@ int tpb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, co
                  long long lddk, long long lddv, float scale, int causal, int window, const int* q_pos,
                  const int* q_seg, const int* kv_seg, void* stream);
 
+// ---- symmetric-memory runtime (symm_runtime.cu): segments that every rank maps, and a bounded
+// device-side barrier on their signal pads.
+int tpb_symm_alloc(long long bytes, void** payload, unsigned char* handle64);
+int tpb_symm_open(const unsigned char* handle64, void** payload);
+int tpb_symm_release(void* payload);
+int tpb_symm_copy(void* dst, const void* src, long long bytes, void* stream);
+int tpb_symm_live_segments(void);
+int tpb_symm_barrier(void* const* payloads, int rank, int world, unsigned epoch, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -13,7 +13,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def _worker(rank, world, port, results):
   os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
-                     "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+                     "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0",
+                     "TPB_SYMM_STRICT": "1"})      # the native symmetric-memory runtime, no silent fallback
   sys.path.insert(0, ROOT)
   import torch.distributed as dist
   from torchprime_b200.dist import runtime as rt
@@ -21,6 +22,24 @@ def _worker(rank, world, port, results):
   from torchprime_b200.ops import _lib, fused_collective as fc, kernels as k
   dev = rt.init()
   try:
+    # ---- symmetric-memory runtime: peers see each other's writes after the device barrier
+    from torchprime_b200.dist import symm
+    for backend in ("native", "torch"):
+      t = SymmetricBuffer(1024, torch.float32, dev, backend=backend)
+      assert t.backend == backend and t.local.numel() == 1024 and len(set(t.ptrs)) == world
+      for it in range(3):
+        t.local.fill_(float(10 * it + rank))
+        t.barrier()
+        peer = (rank + 1) % world
+        got = torch.empty(1024, device=dev)
+        t.copy_from_rank(got, peer)                # copy engine, through the mapped pointer
+        torch.cuda.synchronize()
+        assert torch.all(got == float(10 * it + peer)), f"{backend}: peer copy not visible after the barrier"
+        t.barrier()                                # nobody overwrites before everyone has read
+      if backend == "native":
+        before = symm.live_native_segments()
+        t.close()
+        assert symm.live_native_segments() == before - world
     torch.manual_seed(0)
     N, K, M = 1536, 512, 640
     extra = 4096 + 8 * 13                       # other tensors of the "unit" after the weight

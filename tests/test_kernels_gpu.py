@@ -232,3 +232,34 @@ def test_tensor_kernels_are_bit_reproducible(cuda_lib):
     res.append((o.clone(), lse.clone(), dq.clone(), dk.clone(), dv.clone()))
   for x, y in zip(res[0], res[1]):
     assert torch.equal(x, y)
+
+
+def test_symmetric_runtime_single_rank(cuda_lib):
+  """Allocation, the signal-pad barrier with one rank, the copy helper and release of the C++
+  symmetric-memory runtime (the multi-rank mapping is covered by the two-GPU test)."""
+  import ctypes
+  import torch
+  from torchprime_b200.dist import symm
+  from torchprime_b200.ops import _lib
+  L = symm._native_lib()
+  assert L is not None
+  before = L.tpb_symm_live_segments()
+  payload, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+  assert L.tpb_symm_alloc(4096, ctypes.byref(payload), handle) == 0
+  assert payload.value % 256 == 0 and handle.raw != b"\0" * 64
+  assert L.tpb_symm_live_segments() == before + 1
+  t = torch.as_tensor(symm._DeviceMemoryView(payload.value, 4096), device="cuda").view(torch.float32)
+  assert float(t.abs().sum()) == 0.0                       # segments start zeroed
+  t.copy_(torch.arange(1024, device="cuda", dtype=torch.float32))
+  table = (ctypes.c_void_p * 1)(payload.value)
+  for epoch in (1, 2, 3):
+    assert L.tpb_symm_barrier(table, 0, 1, epoch, _lib.stream_ptr()) == 0
+  out = torch.empty(1024, device="cuda")
+  assert L.tpb_symm_copy(out.data_ptr(), payload.value, 4096, _lib.stream_ptr()) == 0
+  torch.cuda.synchronize()
+  assert torch.equal(out, torch.arange(1024, device="cuda", dtype=torch.float32))
+  _lib.raise_on_device_timeout()
+  del t
+  assert L.tpb_symm_release(payload) == 0 and L.tpb_symm_live_segments() == before
+  assert L.tpb_symm_release(payload) == -2                 # unknown segment
+  assert L.tpb_symm_barrier(table, 1, 1, 1, _lib.stream_ptr()) == -2
