@@ -58,8 +58,16 @@ def main():
   # ---- F1: all-gather fused into the QKV GEMM
   ag = fc.AllGatherGemm(sb, shard, copiers=int(os.environ.get("TPB_AG_COPIERS", "32")), push=False)
   t_fused = timed(lambda: ag(x, gathered, 0, HQKV, D), pre=sb.barrier)
-  agp = fc.AllGatherGemm(sb, shard, copiers=int(os.environ.get("TPB_AG_COPIERS", "32")), push=True)
+  agp = fc.AllGatherGemm(sb, shard, copiers=int(os.environ.get("TPB_AG_COPIERS", "32")), push=True, multicast=False)
   t_push = timed(lambda: agp(x, None, 0, HQKV, D), pre=sb.barrier)
+  # multicast push (one multimem store reaches every rank), swept over the number of copier CTAs
+  mc = {}
+  for cop in [int(c) for c in os.environ.get("TPB_AG_MC_COPIERS", "8,16,32").split(",")]:
+    agm = fc.AllGatherGemm(sb, shard, copiers=cop, push=True, multicast=True)
+    if not agm.multicast_ptr:
+      mc = {"unavailable": "no multicast mapping on this platform"}
+      break
+    mc[str(cop)] = timed(lambda: agm(x, None, 0, HQKV, D), pre=sb.barrier)
   def nccl_then_gemm():
     dist.all_gather_into_tensor(gathered, sb.local)
     k.gemm(x, gathered[:HQKV * D].view(HQKV, D))
@@ -68,7 +76,10 @@ def main():
   flops = 2.0 * T * HQKV * D
   link_bytes = (world - 1) * shard * 2
   roof = max(flops / (peak * 1e12), link_bytes / (NVLINK_GBS * 1e9)) * 1e3
-  out["ag_gemm"] = {"fused_push_ms": t_push, "fraction_of_roofline_push": roof / t_push,
+  best_mc = min([v for v in mc.values() if isinstance(v, float)], default=None)
+  out["ag_gemm"] = {"fused_push_multicast_ms_by_copiers": mc,
+                    "fraction_of_roofline_push_multicast": roof / best_mc if best_mc else None,
+                    "fused_push_ms": t_push, "fraction_of_roofline_push": roof / t_push,
                     "fused_pull_ms": t_fused, "nccl_allgather_plus_gemm_ms": t_nccl, "gemm_only_ms": t_gemm,
                     "roofline_ms": roof, "fraction_of_roofline": roof / t_fused, "nvlink_bytes_in": link_bytes,
                     "copier_ctas": ag.copiers}
@@ -104,16 +115,28 @@ def main():
   kk = qkv[..., hq * hd:(hq + hkv) * hd].view(1, s_loc, hkv, hd)
   vv = qkv[..., (hq + hkv) * hd:].view(1, s_loc, hkv, hd)
   nccl_cp = ContextParallelAttention(mesh, load_balanced=True, fused_exchange=False)
-  fused_cp = ContextParallelAttention(mesh, load_balanced=True, fused_exchange=True,
+  fused_cp = ContextParallelAttention(mesh, load_balanced=True, fused_exchange=True, fused_multicast=False,
                                       fused_copiers=int(os.environ.get("TPB_CP_COPIERS", "16")))
+  cp_mc = {}
   with torch.no_grad():
     t_cp_nccl = timed(lambda: nccl_cp.attention(q, kk, vv))
     t_cp_fused = timed(lambda: fused_cp.attention(q, kk, vv))
+    for cop in [int(c) for c in os.environ.get("TPB_CP_MC_COPIERS", "4,8,16").split(",")]:
+      cpm = ContextParallelAttention(mesh, load_balanced=True, fused_exchange=True, fused_multicast=True,
+                                     fused_copiers=cop)
+      t = timed(lambda: cpm.attention(q, kk, vv))
+      if not next(iter(cpm._fused.values()))["k_all"].multicast_ptr:
+        cp_mc = {"unavailable": "no multicast mapping on this platform"}
+        break
+      cp_mc[str(cop)] = t
   sk = s_loc * world
   flops5 = 4.0 * s_loc * sk * hq * hd / 2          # causal, zig-zag balanced: half of the score matrix
   link5 = (world - 1) * s_loc * hkv * hd * 2 * 2
   roof5 = max(flops5 / (peak * 1e12), link5 / (NVLINK_GBS * 1e9)) * 1e3
-  out["cp_attention_fwd"] = {"fused_ms": t_cp_fused, "nccl_allgather_then_attention_ms": t_cp_nccl,
+  best5 = min([v for v in cp_mc.values() if isinstance(v, float)], default=None)
+  out["cp_attention_fwd"] = {"fused_multicast_ms_by_copiers": cp_mc,
+                             "fraction_of_roofline_multicast": roof5 / best5 if best5 else None,
+                             "fused_ms": t_cp_fused, "nccl_allgather_then_attention_ms": t_cp_nccl,
                              "roofline_ms": roof5, "fraction_of_roofline": roof5 / t_cp_fused,
                              "nvlink_bytes_in": link5, "keys_per_rank": s_loc}
   # ---- F4: expert-parallel MLP forward (Mixtral layer: 8 experts, top-2), dispatch/return by push kernel

@@ -61,6 +61,8 @@ struct AttnFwdParams {
   int cp_row_elems;                    // Hkv * 128: elements per key row in the gathered buffers
   __nv_bfloat16* cp_k_dst[8];          // gathered K [B * Sk, Hkv * 128] of every rank
   __nv_bfloat16* cp_v_dst[8];
+  __nv_bfloat16* cp_k_mc;              // NVSwitch multicast addresses of the gathered K / V (one store reaches
+  __nv_bfloat16* cp_v_mc;              // every rank), or null: one store per rank
   unsigned* cp_flags[8];               // [B * Sk / 128] of every rank
   unsigned cp_epoch;
 };
@@ -95,6 +97,20 @@ __device__ void cp_pusher(const AttnFwdParams& p) {
           const int k = i + u * blockDim.x;
           if (k < nvec)
             v[u] = *reinterpret_cast<const uint4*>(src + (src_row0 + k / vec_per_row) * ld + (k % vec_per_row) * 8);
+        }
+        __nv_bfloat16* mc = which == 0 ? p.cp_k_mc : p.cp_v_mc;
+        if (mc != nullptr) {
+          uint4* dst = reinterpret_cast<uint4*>(mc + dst_row0 * p.cp_row_elems);
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int k = i + u * blockDim.x;
+            if (k < nvec)
+              asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + k),
+                           "f"(__uint_as_float(v[u].x)), "f"(__uint_as_float(v[u].y)),
+                           "f"(__uint_as_float(v[u].z)), "f"(__uint_as_float(v[u].w))
+                           : "memory");
+          }
+          continue;
         }
         for (int r = 0; r < p.cp_world; ++r) {
           uint4* dst = reinterpret_cast<uint4*>((which == 0 ? p.cp_k_dst[r] : p.cp_v_dst[r]) +
@@ -857,13 +873,15 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
 // [B*s_local] key/value rows (row pitches ld_k_local / ld_v_local, Hkv*128 elements used per row);
 // k_all / v_all / flags: tables of every rank's gathered K [B*Sk, Hkv*128], gathered V and flag
 // array [B*Sk/128] in symmetric memory (Sk = world * s_local); entry `rank` is this rank's own.
+// k_multicast / v_multicast: multicast addresses of the same gathered buffers, or null.
 // q_pos: absolute positions of the query rows.  `epoch` must differ from the previous call's, and
 // all ranks must have finished reading their gathered buffers before any rank starts this call.
 extern "C" int tpb_attn_fwd_cp(const void* q, const void* k_local, const void* v_local, void* const* k_all,
                                void* const* v_all, unsigned* const* flags, void* o, float* lse, int B, int Sq,
                                int s_local, int Hq, int Hkv, long long ldq, long long ld_k_local,
                                long long ld_v_local, long long ldo, float scale, const int* q_pos, int world, int rank,
-                               int zigzag, int copiers, unsigned epoch, void* stream_) {
+                               int zigzag, int copiers, unsigned epoch, void* k_multicast, void* v_multicast,
+                               void* stream_) {
   if (world < 2 || world > 8 || rank < 0 || rank >= world || Hq % Hkv) return -2;
   if ((ldq % 8) || (ld_k_local % 8) || (ld_v_local % 8) || (ldo % 8)) return -2;
   if (s_local % (zigzag ? 2 * CP_CHUNK : CP_CHUNK)) return -2;
@@ -894,6 +912,9 @@ extern "C" int tpb_attn_fwd_cp(const void* q, const void* k_local, const void* v
     p.cp_flags[r] = r < world ? flags[r] : nullptr;
   }
   p.cp_epoch = epoch;
+  const bool mc = k_multicast != nullptr && v_multicast != nullptr;
+  p.cp_k_mc = mc ? reinterpret_cast<__nv_bfloat16*>(k_multicast) : nullptr;
+  p.cp_v_mc = mc ? reinterpret_cast<__nv_bfloat16*>(v_multicast) : nullptr;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,

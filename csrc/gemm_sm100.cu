@@ -82,6 +82,7 @@ struct GemmParams {
   int ag_push;
   void* ag_push_dst[8];         // gathered buffer of every rank (symmetric memory)
   unsigned* ag_push_flags[8];   // flag array of every rank (symmetric memory)
+  void* ag_push_mc;             // NVSwitch multicast address of the gathered buffers (one store reaches every rank), or null
   // Reduce-scatter fusion (TPB_EPI_RS_BF16): the epilogue adds alpha * acc straight into the
   // owner's bf16 gradient shard over P2P with vector red.add.
   int rs_world;
@@ -253,6 +254,21 @@ __device__ void ag_pusher(const GemmParams& p) {
       for (int u = 0; u < 16; ++u) {
         const int k = i + u * blockDim.x;
         if (k < nvec) v[u] = src[k];
+      }
+      if (p.ag_push_mc != nullptr) {
+        // one multimem store per 16 bytes: the switch replicates it into every rank's gathered buffer
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.ag_push_mc) +
+                                              (long long)me * p.ag_shard_elems + off);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const int k = i + u * blockDim.x;
+          if (k < nvec)
+            asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + k),
+                         "f"(__uint_as_float(v[u].x)), "f"(__uint_as_float(v[u].y)), "f"(__uint_as_float(v[u].z)),
+                         "f"(__uint_as_float(v[u].w))
+                         : "memory");
+        }
+        continue;
       }
       for (int r = 0; r < p.ag_world; ++r) {
         if (r == me) continue;
@@ -711,7 +727,7 @@ struct GemmCall {
   // fusion with collectives (0 / null when unused)
   int ag_world, ag_copiers, ag_local; const void* const* ag_src; void* ag_dst; long long ag_shard_elems, ag_b_offset;
   unsigned* ag_flags; unsigned ag_epoch;
-  void* const* ag_push_dst; unsigned* const* ag_push_flags;
+  void* const* ag_push_dst; unsigned* const* ag_push_flags; void* ag_push_mc;
   int rs_world; void* const* rs_dst; long long rs_shard_elems, rs_c_offset;
   int rs_rank;
 };
@@ -768,6 +784,7 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.rs_world = g.rs_world; p.rs_shard_elems = g.rs_shard_elems; p.rs_c_offset = g.rs_c_offset;
   p.tile_rot = 0;
   p.ag_push = (g.ag_world > 0 && g.ag_push_dst != nullptr && g.ag_push_flags != nullptr) ? 1 : 0;
+  p.ag_push_mc = p.ag_push ? g.ag_push_mc : nullptr;
   if (p.ag_push) p.ag_chunk_elems = 131072;   // 256 KB per flag: a CTA streams a chunk with one fence at its end
   for (int i = 0; i < 8; ++i) {
     p.ag_push_dst[i] = (p.ag_push && i < g.ag_world) ? g.ag_push_dst[i] : nullptr;
@@ -884,7 +901,8 @@ extern "C" int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, lon
                                 const void* aux, long long ldaux, void* c2, long long ldc2,
                                 const void* const* shard_ptrs, int world, long long shard_elems, void* gathered,
                                 long long b_offset, unsigned* flags, unsigned epoch, int copiers, int local_rank,
-                                void* const* push_gathered, unsigned* const* push_flags, void* stream_) {
+                                void* const* push_gathered, unsigned* const* push_flags, void* push_multicast,
+                                void* stream_) {
   GemmCall g{};
   g.A = A; g.B = reinterpret_cast<const __nv_bfloat16*>(gathered) + b_offset; g.B2 = nullptr; g.C = C;
   g.M = M; g.N = N; g.K = K; g.E = 1;
@@ -894,7 +912,7 @@ extern "C" int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, lon
   g.ag_world = world; g.ag_copiers = copiers; g.ag_src = shard_ptrs; g.ag_dst = gathered;
   g.ag_shard_elems = shard_elems; g.ag_b_offset = b_offset; g.ag_flags = flags; g.ag_epoch = epoch;
   g.ag_local = local_rank;
-  g.ag_push_dst = push_gathered; g.ag_push_flags = push_flags;
+  g.ag_push_dst = push_gathered; g.ag_push_flags = push_flags; g.ag_push_mc = push_multicast;
   return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
 }
 

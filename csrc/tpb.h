@@ -100,7 +100,7 @@ int tpb_ag_gemm_bf16(const void* A, void* C, int M, int N, int K, long long lda,
                      const void* aux, long long ldaux, void* c2, long long ldc2, const void* const* shard_ptrs,
                      int world, long long shard_elems, void* gathered, long long b_offset, unsigned* flags,
                      unsigned epoch, int copiers, int local_rank, void* const* push_gathered,
-                     unsigned* const* push_flags, void* stream);
+                     unsigned* const* push_flags, void* push_multicast, void* stream);
 int tpb_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb, long long ldc,
                      int a_mn, int b_mn, float alpha, void* const* shard_ptrs, int world, long long shard_elems,
                      long long c_offset, int rank, void* stream);
@@ -134,7 +134,8 @@ int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* ls
 int tpb_attn_fwd_cp(const void* q, const void* k_local, const void* v_local, void* const* k_all, void* const* v_all,
                     unsigned* const* flags, void* o, float* lse, int B, int Sq, int s_local, int Hq, int Hkv,
                     long long ldq, long long ld_k_local, long long ld_v_local, long long ldo, float scale,
-                    const int* q_pos, int world, int rank, int zigzag, int copiers, unsigned epoch, void* stream);
+                    const int* q_pos, int world, int rank, int zigzag, int copiers, unsigned epoch, void* k_multicast,
+                    void* v_multicast, void* stream);
 // `scratch` holds tpb_attn_bwd_scratch_floats(B, Sq, Hq) floats; dq/dk/dv are fully overwritten.
 long long tpb_attn_bwd_scratch_floats(int B, int Sq, int Hq);
 int tpb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,

@@ -63,19 +63,23 @@ def _worker(rank, world, port, results):
       err = ((y.float() - want).norm() / want.norm()).item()
       assert err < 1e-2, f"ag_gemm rel err {err}"
       assert torch.equal(gathered, full), "gathered buffer differs from the concatenated shards"
-    # ---- push mode: every rank sends its shard, flags are raised in the peers' memory
-    agp = fc.AllGatherGemm(sb, shard, copiers=4, push=True)
-    for it in range(2):
-      agp.gathered.zero_()
-      torch.cuda.synchronize()
-      sb.barrier()
-      y = agp(x, None, 0, N, K)
-      torch.cuda.synchronize()
-      sb.barrier()
-      torch.cuda.synchronize()
-      err = ((y.float() - want).norm() / want.norm()).item()
-      assert err < 1e-2, f"ag_gemm (push) rel err {err}"
-      assert torch.equal(agp.gathered, full), "pushed gathered buffer differs from the concatenated shards"
+    # ---- push mode: every rank sends its shard, flags are raised in the peers' memory; with per-peer
+    # stores and, where the switch offers it, with one multicast store for all peers
+    for mc in (False, True):
+      agp = fc.AllGatherGemm(sb, shard, copiers=4, push=True, multicast=mc)
+      assert mc or agp.multicast_ptr == 0
+      results[f"multicast_{rank}"] = bool(agp.multicast_ptr)
+      for it in range(2):
+        agp.gathered.zero_()
+        torch.cuda.synchronize()
+        sb.barrier()
+        y = agp(x, None, 0, N, K)
+        torch.cuda.synchronize()
+        sb.barrier()
+        torch.cuda.synchronize()
+        err = ((y.float() - want).norm() / want.norm()).item()
+        assert err < 1e-2, f"ag_gemm (push, multicast={mc}) rel err {err}"
+        assert torch.equal(agp.gathered, full), f"pushed gathered buffer differs (multicast={mc})"
     # ---- reduce-scatter fused into a wgrad-layout GEMM
     T, Nw, Kw = 768, 512, 256
     c_off = 8 * 5
@@ -103,9 +107,10 @@ def _worker(rank, world, port, results):
     from torchprime_b200.dist.mesh import Mesh
     from torchprime_b200.parallel.cp import ContextParallelAttention
     mesh = Mesh(shape={"data": 1, "fsdp": 1, "tensor": 1, "expert": 1, "context": world}, rank=rank, world_size=world)
-    for lb in (False, True):
+    for lb, mc in ((False, False), (True, True), (True, False)):
       ref_cp = ContextParallelAttention(mesh, load_balanced=lb, fused_exchange=False)
-      fus_cp = ContextParallelAttention(mesh, load_balanced=lb, fused_exchange=True, fused_copiers=4)
+      fus_cp = ContextParallelAttention(mesh, load_balanced=lb, fused_exchange=True, fused_copiers=4,
+                                        fused_multicast=mc)
       torch.manual_seed(500 + rank)
       b, s_loc, hq, hkv, d = 2, 512, 8, 2, 128
       qkv = (torch.randn(b, s_loc, (hq + 2 * hkv) * d, device=dev) * 0.5).to(torch.bfloat16)
@@ -126,7 +131,7 @@ def _worker(rank, world, port, results):
       assert fus_cp._fused, "the fused exchange path was not taken"
       err_o = ((o_fus - o_ref).norm() / o_ref.norm()).item()
       err_g = ((g_fus - g_ref).norm() / g_ref.norm()).item()
-      assert err_o < 1e-2 and err_g < 2e-2, f"fused cp attention (lb={lb}): out {err_o} grad {err_g}"
+      assert err_o < 1e-2 and err_g < 2e-2, f"fused cp attention (lb={lb}, multicast={mc}): out {err_o} grad {err_g}"
     # ---- expert-parallel MLP with dispatch / return by the push all-to-all kernel
     from torchprime_b200.parallel.ep import ExpertParallelMLP
     emesh = Mesh(shape={"data": 1, "fsdp": 1, "tensor": 1, "expert": world, "context": 1}, rank=rank, world_size=world)
@@ -176,3 +181,4 @@ def test_ag_gemm_and_gemm_rs_two_gpus(cuda_lib):
   results = mgr.dict()
   mp.spawn(_worker, args=(world, 29641, results), nprocs=world, join=True)
   assert all(results.get(r) == "ok" for r in range(world)), dict(results)
+  print("multicast push used:", [results.get(f"multicast_{r}") for r in range(world)])

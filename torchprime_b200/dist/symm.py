@@ -64,6 +64,7 @@ class SymmetricBuffer:
     self._elem = torch.empty(0, dtype=dtype).element_size()
     self._epoch = 0
     self._closed = False
+    self.multicast_ptr = 0            # NVSwitch multicast address of the buffers (torch backend only), else 0
     backend = backend or os.environ.get("TPB_SYMM_BACKEND", "native")
     assert backend in ("native", "torch"), backend
     self.backend = None
@@ -124,7 +125,11 @@ class SymmetricBuffer:
     import torch.distributed._symmetric_memory as symm_mem
     self.local = symm_mem.empty(numel, dtype=dtype, device=device)
     self.handle = symm_mem.rendezvous(self.local, group=self.group)
-    self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+    off = int(getattr(self.handle, "offset", 0) or 0)
+    self.ptrs = [int(p) + off for p in self.handle.buffer_ptrs]
+    assert self.ptrs[self.rank] == self.local.data_ptr(), "symmetric buffer pointer table does not match the tensor"
+    mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+    self.multicast_ptr = mc + off if mc else 0
     self.backend = "torch"
 
   # ---------------------------------------------------------------- common surface

@@ -25,17 +25,19 @@ _lib.register_signature("tpb_attn_bwd", [P, P, P, P, P, P, P, P, P, P, I, I, I, 
 
 
 _lib.register_signature("tpb_attn_fwd_cp", [P, P, P, P, P, P, P, P, I, I, I, I, I, LL, LL, LL, LL, F, P, I, I, I, I,
-                                            c_uint, P])
+                                            c_uint, P, P, P])
 
 
 def attn_fwd_cp(q, k_local, v_local, k_all_sb, v_all_sb, flags_sb, q_pos, *, zigzag: bool, epoch: int,
-                copiers: int = 16, scale=None):
+                copiers: int = 16, scale=None, multicast: bool = True):
   """Causal attention forward with the context-parallel K/V exchange fused into the kernel.
 
   ``q`` [B,Sq,Hq,128] are this rank's query rows, ``k_local`` / ``v_local`` [B,S_local,Hkv,128] its
   keys and values; ``k_all_sb`` / ``v_all_sb`` / ``flags_sb`` are ``SymmetricBuffer`` objects that
   hold the gathered K, V ([B, world*S_local, Hkv, 128], natural key order) and one flag per 128
-  keys.  Copier CTAs push the local rows into every rank's buffers while the other CTAs compute.
+  keys.  Copier CTAs push the local rows into every rank's buffers while the other CTAs compute
+  (with one ``multimem.st`` for all ranks when both buffers have a multicast mapping and
+  ``multicast`` is on, else with one store per rank).
   Returns (o, lse); afterwards ``k_all_sb.local`` / ``v_all_sb.local`` hold the gathered tensors."""
   b, sq, hq, d = q.shape
   s_local, hkv = k_local.shape[1], k_local.shape[2]
@@ -46,7 +48,9 @@ def attn_fwd_cp(q, k_local, v_local, k_all_sb, v_all_sb, flags_sb, q_pos, *, zig
   rc = lib().tpb_attn_fwd_cp(ptr(q), ptr(k_local), ptr(v_local), k_all_sb.ptr_table(), v_all_sb.ptr_table(),
                              flags_sb.ptr_table(), ptr(o), ptr(lse), b, sq, s_local, hq, hkv, q.stride(1),
                              k_local.stride(1), v_local.stride(1), hq * 128, float(scale), ptr(q_pos),
-                             k_all_sb.world, k_all_sb.rank, int(bool(zigzag)), int(copiers), int(epoch), stream_ptr())
+                             k_all_sb.world, k_all_sb.rank, int(bool(zigzag)), int(copiers), int(epoch),
+                             (k_all_sb.multicast_ptr or None) if multicast else None,
+                             (v_all_sb.multicast_ptr or None) if multicast else None, stream_ptr())
   check(rc, f"attn_fwd_cp q{tuple(q.shape)} k{tuple(k_local.shape)} world={k_all_sb.world}")
   return o, lse
 

@@ -7,8 +7,12 @@ PUSHES its shard into the peers' gathered buffers with plain 16-byte stores (pos
 NVLink) and raises per-chunk flags in the peers' memory; ``push=False`` makes every rank pull the
 remote shards instead (bulk copies from peer memory through shared memory, no multicast).  The
 GEMM CTAs load their B tiles locally as soon as the chunks they need have landed.  The rank's own
-shard is put in place by a device-to-device copy on the same stream before the kernel starts.  After the call the whole buffer is
-gathered, so the other weights of the same FSDP unit are ready too.
+shard is put in place by a device-to-device copy on the same stream before the kernel starts.
+Where the gathered buffers are bound to an NVSwitch multicast object (``multicast=True``, or by
+default when the platform offers it), the push is one ``multimem.st`` per 16 bytes that the switch
+replicates into every rank's buffer, so each rank sends its shard once instead of once per peer.
+After the call the whole buffer is gathered, so the other weights of the same FSDP unit are ready
+too.
 
 ``gemm_rs``: ``dW = dY^T X`` (or any GEMM) whose epilogue adds ``alpha * tile`` directly into the
 owning rank's bf16 gradient shard with 16-byte ``red.add`` over P2P, replacing the separate
@@ -26,7 +30,7 @@ from . import _lib
 from ._lib import check, lib, ptr, stream_ptr
 
 P, I, LL, FL, U = c_void_p, c_int, c_longlong, c_float, c_uint
-_lib.register_signature("tpb_ag_gemm_bf16", [P, P, I, I, I, LL, LL, I, P, LL, P, LL, P, I, LL, P, LL, P, U, I, I, P, P, P])
+_lib.register_signature("tpb_ag_gemm_bf16", [P, P, I, I, I, LL, LL, I, P, LL, P, LL, P, I, LL, P, LL, P, U, I, I, P, P, P, P])
 _lib.register_signature("tpb_gemm_rs_bf16", [P, P, I, I, I, LL, LL, LL, I, I, FL, P, I, LL, LL, I, P])
 
 CHUNK_ELEMS = 16384
@@ -39,11 +43,14 @@ def num_flags(world: int, shard_elems: int) -> int:
 class AllGatherGemm:
   """State for repeated fused all-gather + GEMM calls on one sharded flat buffer."""
 
-  def __init__(self, shard_buffer, shard_elems: int, copiers: int = 32, push: bool = True):
+  def __init__(self, shard_buffer, shard_elems: int, copiers: int = 32, push: bool = True,
+               multicast: bool | None = None):
     """``push``: every rank sends its shard to the peers (posted stores over NVLink) instead of
     fetching theirs.  The gathered buffer and the flags then live in symmetric memory owned by this
     object (``self.gathered``), and the ranks must be synchronised between two calls (nobody may
-    still be reading the previous gather when the next one starts to arrive)."""
+    still be reading the previous gather when the next one starts to arrive).  ``multicast``: push
+    through the NVSwitch multicast mapping of the gathered buffers (None: when available and not
+    disabled with ``TPB_AG_MULTICAST=0``)."""
     self.sb = shard_buffer                     # dist.symm.SymmetricBuffer holding this rank's shard
     self.world = shard_buffer.world
     self.shard_elems = shard_elems
@@ -53,7 +60,18 @@ class AllGatherGemm:
     self.epoch = 0
     if push:
       from ..dist.symm import SymmetricBuffer
-      self.gathered_sb = SymmetricBuffer(shard_elems * self.world, torch.bfloat16, dev, group=shard_buffer.group)
+      import os
+      if multicast is None:
+        multicast = os.environ.get("TPB_AG_MULTICAST", "1") != "0"
+      self.gathered_sb, self.multicast_ptr = None, 0
+      if multicast:
+        # multicast objects come with torch's symmetric allocations (CUDA VMM + cuMulticast); without
+        # multicast support the same buffer is used with per-peer stores
+        self.gathered_sb = SymmetricBuffer(shard_elems * self.world, torch.bfloat16, dev, group=shard_buffer.group,
+                                           backend="torch")
+        self.multicast_ptr = self.gathered_sb.multicast_ptr
+      if self.gathered_sb is None:
+        self.gathered_sb = SymmetricBuffer(shard_elems * self.world, torch.bfloat16, dev, group=shard_buffer.group)
       self.flags_sb = SymmetricBuffer(num_flags(self.world, shard_elems), torch.int32, dev, group=shard_buffer.group)
       self.flags_sb.local.zero_()
       self.gathered = self.gathered_sb.local
@@ -82,7 +100,8 @@ class AllGatherGemm:
                                 table, self.world, self.shard_elems, ptr(gathered), b_offset, ptr(self.flags),
                                 self.epoch, self.copiers, rank,
                                 self.gathered_sb.ptr_table() if self.push else None,
-                                self.flags_sb.ptr_table() if self.push else None, stream_ptr())
+                                self.flags_sb.ptr_table() if self.push else None,
+                                (self.multicast_ptr or None) if self.push else None, stream_ptr())
     check(rc, f"ag_gemm M={m} N={n} K={k} world={self.world}")
     return out
 

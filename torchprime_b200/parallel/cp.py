@@ -33,7 +33,9 @@ class _FusedExchangeAttention(torch.autograd.Function):
     st["epoch"] += 1
     st["k_all"].barrier()            # every rank is done reading the buffers of the previous call
     o, lse = A.attn_fwd_cp(q, k, v, st["k_all"], st["v_all"], st["flags"], pos32, zigzag=cpa.load_balanced,
-                           epoch=st["epoch"], copiers=cpa.fused_copiers, scale=scale)
+                           epoch=st["epoch"], copiers=cpa.fused_copiers, scale=scale, multicast=cpa.fused_multicast)
+    from ..ops import functional as ops
+    ops._ATTN_USED["last"] = "sm100 tcgen05 kernel with the K/V exchange inside (context parallel)"
     b, s_local, hkv, d = k.shape
     sk = s_local * cpa.cp
     # the symmetric buffers are reused by the next layer: keep this layer's gathered K/V for backward
@@ -65,13 +67,18 @@ class _FusedExchangeAttention(torch.autograd.Function):
 
 
 class ContextParallelAttention:
-  def __init__(self, mesh, load_balanced: bool = False, fused_exchange: bool = False, fused_copiers: int = 16):
+  def __init__(self, mesh, load_balanced: bool = False, fused_exchange: bool = False, fused_copiers: int = 16,
+               fused_multicast: bool | None = None):
     self.group = mesh.group("context")
     self.cp = mesh.size("context")
     self.rank = mesh.index("context")
     self.load_balanced = load_balanced
     self.fused_exchange = fused_exchange      # K/V exchange inside the attention forward kernel
     self.fused_copiers = fused_copiers
+    if fused_multicast is None:
+      import os
+      fused_multicast = os.environ.get("TPB_CP_MULTICAST", "1") != "0"
+    self.fused_multicast = fused_multicast    # push K/V with one multimem store for all ranks where available
     self._pos_cache = {}
     self._fused = {}
 
@@ -84,8 +91,11 @@ class ContextParallelAttention:
       n = b * s_local * self.cp * hkv * d
       flags = SymmetricBuffer(b * s_local * self.cp // 128, torch.int32, q.device, group=self.group)
       flags.local.zero_()
-      self._fused[key] = {"k_all": SymmetricBuffer(n, k.dtype, q.device, group=self.group),
-                          "v_all": SymmetricBuffer(n, k.dtype, q.device, group=self.group),
+      # with multicast the gathered buffers come from torch's symmetric allocator (it binds them
+      # to an NVSwitch multicast object where the platform has one)
+      backend = "torch" if self.fused_multicast else None
+      self._fused[key] = {"k_all": SymmetricBuffer(n, k.dtype, q.device, group=self.group, backend=backend),
+                          "v_all": SymmetricBuffer(n, k.dtype, q.device, group=self.group, backend=backend),
                           "flags": flags, "epoch": 0}
       flags.barrier()
     return self._fused[key]
