@@ -274,6 +274,57 @@ __global__ void a2a_push_kernel(const A2APushParams p) {
   }
 }
 
+// Block form of the push: the source rows are a sequence of `n_blocks` contiguous blocks, block b =
+// rows [start[b], start[b+1]) going to rank dst_rank[b] at row dst_row0[b] of its receive buffer.
+// The descriptors live in device memory as 64-bit words: start[n_blocks + 1], dst_rank[n_blocks],
+// dst_row0[n_blocks].  One block per (destination rank, expert) lets rows land at the receiver
+// already grouped by expert, whatever rank they came from.
+struct A2ABlocksParams {
+  const uint4* src;
+  int vec_per_row;
+  int n_rows;
+  int n_blocks;
+  int world, me;
+  const long long* desc;
+  uint4* dst[8];
+  unsigned* flags[8];
+  unsigned epoch;
+  unsigned* done_counter;
+};
+
+__global__ void a2a_push_blocks_kernel(const A2ABlocksParams p) {
+  extern __shared__ long long a2a_desc[];
+  const int nd = 3 * p.n_blocks + 1;
+  for (int i = threadIdx.x; i < nd; i += blockDim.x) a2a_desc[i] = p.desc[i];
+  __syncthreads();
+  const long long* start = a2a_desc;
+  const long long* dst_rank = a2a_desc + p.n_blocks + 1;
+  const long long* dst_row0 = dst_rank + p.n_blocks;
+  for (int row = blockIdx.x; row < p.n_rows; row += gridDim.x) {
+    int lo = 0, hi = p.n_blocks - 1;                    // last block whose first row is <= row
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (start[mid] <= row) lo = mid; else hi = mid - 1;
+    }
+    const int r = (int)dst_rank[lo];
+    if (r < 0 || r >= p.world) continue;
+    const uint4* s = p.src + (long long)row * p.vec_per_row;
+    uint4* d = p.dst[r] + (dst_row0[lo] + (row - start[lo])) * p.vec_per_row;
+    for (int i = threadIdx.x; i < p.vec_per_row; i += blockDim.x) d[i] = s[i];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(p.done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      __threadfence_system();
+      for (int r = 0; r < p.world; ++r)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[r] + p.me), "r"(p.epoch) : "memory");
+      *p.done_counter = 0;
+    }
+  }
+}
+
 // Stream-ordered wait (bounded) until every rank has delivered its rows for `epoch`.
 __global__ void a2a_wait_kernel(const unsigned* flags, int world, unsigned epoch, int* status) {
   if (threadIdx.x != 0) return;
@@ -363,6 +414,24 @@ extern "C" int tpb_a2a_push_rows(const void* src, int n_rows, int dim, int world
   p.epoch = epoch; p.done_counter = done_counter;
   int grid = n_rows < 1 ? 1 : (n_rows < 4 * sm_count() ? n_rows : 4 * sm_count());
   a2a_push_kernel<<<grid, 256, 0, STREAM(stream)>>>(p);
+  return rc_of(cudaGetLastError());
+}
+
+extern "C" int tpb_a2a_push_blocks(const void* src, int n_rows, int dim, int n_blocks, int world, int me,
+                                   const long long* desc_dev, void* const* dst, unsigned* const* flags,
+                                   unsigned epoch, unsigned* done_counter, void* stream) {
+  if (dim % 8 || world < 1 || world > 8 || me < 0 || me >= world || n_blocks < 1 || n_blocks > 1024 || !desc_dev)
+    return -2;
+  A2ABlocksParams p{};
+  p.src = (const uint4*)src; p.vec_per_row = dim / 8; p.n_rows = n_rows; p.n_blocks = n_blocks;
+  p.world = world; p.me = me; p.desc = desc_dev;
+  for (int r = 0; r < world; ++r) {
+    p.dst[r] = (uint4*)dst[r];
+    p.flags[r] = flags[r];
+  }
+  p.epoch = epoch; p.done_counter = done_counter;
+  int grid = n_rows < 1 ? 1 : (n_rows < 4 * sm_count() ? n_rows : 4 * sm_count());
+  a2a_push_blocks_kernel<<<grid, 256, (3 * n_blocks + 1) * sizeof(long long), STREAM(stream)>>>(p);
   return rc_of(cudaGetLastError());
 }
 

@@ -124,6 +124,9 @@ int tpb_moe_combine_dw(const void* rows, const int* dest, const void* dout, floa
 int tpb_a2a_push_rows(const void* src, int n_rows, int dim, int world, int me, const int* src_start,
                       const long long* dst_row0, void* const* dst, unsigned* const* flags, unsigned epoch,
                       unsigned* done_counter, void* stream);
+int tpb_a2a_push_blocks(const void* src, int n_rows, int dim, int n_blocks, int world, int me,
+                        const long long* desc_dev, void* const* dst, unsigned* const* flags, unsigned epoch,
+                        unsigned* done_counter, void* stream);
 int tpb_a2a_wait(const unsigned* flags, int world, unsigned epoch, void* stream);
 
 // Flash attention (attention_fwd_sm100.cu / attention_bwd_sm100.cu); token-major [B*S, heads*dim] views.

@@ -162,3 +162,51 @@ def test_homogeneous_sequential_passes_keyword_arguments_to_every_layer():
   assert torch.equal(out, torch.full((2,), 10.0))          # (1*2+1)*3+1
   with pytest.raises(AssertionError):
     HomogeneousSequential(Scale(1.0), nn.ReLU())
+
+
+def test_expert_exchange_plan_groups_rows_by_expert_and_returns_them():
+  """The host-side plan of the expert-parallel exchange, checked by replaying the block-push kernel's
+  rule in Python: rows land at the owner grouped by expert in padded segments, padding rows are the
+  ones listed for zeroing, and the return blocks bring every row back to its place."""
+  import random
+
+  import torch
+  from torchprime_b200.parallel.ep import _ExchangePlan
+  random.seed(0)
+  ep, el = 4, 3
+  E = ep * el
+  C = [[random.choice([0, 0, 1, 5, 130, 257]) for _ in range(E)] for _ in range(ep)]
+  C[2] = [0] * E                                           # a rank that sends nothing
+  plans = [_ExchangePlan(C, me, ep, el, "cpu") for me in range(ep)]
+
+  def push(src_rows, desc, nb, dst):
+    start, rank, row0 = desc[:nb + 1].tolist(), desc[nb + 1:2 * nb + 1].tolist(), desc[2 * nb + 1:].tolist()
+    for row, item in enumerate(src_rows):
+      b = max(i for i in range(nb) if start[i] <= row)
+      if rank[b] >= 0:
+        dst[rank[b]][row0[b] + row - start[b]] = item
+
+  send = [[(s, e, i) for e in range(E) for i in range(C[s][e])] for s in range(ep)]
+  recv = [dict() for _ in range(ep)]
+  for s in range(ep):
+    assert plans[s].n_send == len(send[s])
+    push(send[s], plans[s].dispatch, plans[s].dispatch_blocks, recv)
+  for r in range(ep):
+    p = plans[r]
+    koff = p.k_offsets.tolist()
+    assert p.n_pad == koff[-1] and all(v % 128 == 0 for v in koff)
+    assert p.tile_expert.tolist() == [j for j in range(el) for _ in range((koff[j + 1] - koff[j]) // 128)]
+    filled = set(recv[r])
+    zero = set(p.zero_rows.tolist()) if p.zero_rows is not None else set()
+    assert filled | zero == set(range(p.n_pad)) and not (filled & zero)
+    for j in range(el):
+      seg = [recv[r][i] for i in range(koff[j], koff[j + 1]) if i in recv[r]]
+      assert all(e == r * el + j for _, e, _ in seg)
+      assert seg == sorted(seg)                          # sources in order, rows of a source in order
+      assert len(seg) == sum(C[s][r * el + j] for s in range(ep))
+  back = [dict() for _ in range(ep)]
+  for r in range(ep):
+    rows = [recv[r].get(i) for i in range(plans[r].n_pad)]
+    push(rows, plans[r].ret, plans[r].ret_blocks, back)
+  for s in range(ep):
+    assert [back[s][i] for i in range(len(send[s]))] == send[s]

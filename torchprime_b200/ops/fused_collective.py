@@ -49,8 +49,8 @@ class AllGatherGemm:
     fetching theirs.  The gathered buffer and the flags then live in symmetric memory owned by this
     object (``self.gathered``), and the ranks must be synchronised between two calls (nobody may
     still be reading the previous gather when the next one starts to arrive).  ``multicast``: push
-    through the NVSwitch multicast mapping of the gathered buffers (None: when available and not
-    disabled with ``TPB_AG_MULTICAST=0``)."""
+    through the NVSwitch multicast mapping of the gathered buffers (None: with more than two ranks,
+    when available; ``TPB_AG_MULTICAST=0/1`` overrides)."""
     self.sb = shard_buffer                     # dist.symm.SymmetricBuffer holding this rank's shard
     self.world = shard_buffer.world
     self.shard_elems = shard_elems
@@ -62,7 +62,8 @@ class AllGatherGemm:
       from ..dist.symm import SymmetricBuffer
       import os
       if multicast is None:
-        multicast = os.environ.get("TPB_AG_MULTICAST", "1") != "0"
+        # measured: equal to per-peer stores on 8 GPUs with half the copier CTAs, slower on 2
+        multicast = os.environ.get("TPB_AG_MULTICAST", "1" if self.world > 2 else "0") != "0"
       self.gathered_sb, self.multicast_ptr = None, 0
       if multicast:
         # multicast objects come with torch's symmetric allocations (CUDA VMM + cuMulticast); without

@@ -77,7 +77,7 @@ class ContextParallelAttention:
     self.fused_copiers = fused_copiers
     if fused_multicast is None:
       import os
-      fused_multicast = os.environ.get("TPB_CP_MULTICAST", "1") != "0"
+      fused_multicast = os.environ.get("TPB_CP_MULTICAST", "1" if self.cp > 2 else "0") != "0"
     self.fused_multicast = fused_multicast    # push K/V with one multimem store for all ranks where available
     self._pos_cache = {}
     self._fused = {}

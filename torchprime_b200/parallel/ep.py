@@ -36,6 +36,31 @@ class PushAllToAll:
     self.epoch = 0
     self.flags.barrier()
 
+  def exchange_blocks(self, x, desc, n_blocks: int, n_out: int, zero_rows=None):
+    """Block form (not differentiable; the expert-parallel MLP function drives it in both passes):
+    ``x`` rows are ``n_blocks`` consecutive blocks described by the device tensor ``desc`` (int64:
+    ``start[n_blocks+1]``, ``dst_rank[n_blocks]`` (-1: skip), ``dst_row0[n_blocks]``).  Returns a
+    copy of the first ``n_out`` rows of this rank's receive buffer with ``zero_rows`` cleared."""
+    import ctypes
+
+    from ..ops import _lib
+    from ..ops._lib import check, lib, ptr, stream_ptr
+    assert n_out <= self.max_rows, f"receive buffer holds {self.max_rows} rows, {n_out} needed"
+    assert x.shape[1] == self.dim and x.is_contiguous() and desc.numel() == 3 * n_blocks + 1
+    P, I, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint
+    _lib.register_signature("tpb_a2a_push_blocks", [P, I, I, I, I, I, P, P, P, U, P, P])
+    _lib.register_signature("tpb_a2a_wait", [P, I, U, P])
+    self.epoch += 1
+    self.recv.barrier()            # nobody is still reading its receive buffer from the previous exchange
+    check(lib().tpb_a2a_push_blocks(ptr(x), x.shape[0], self.dim, n_blocks, self.world, self.rank, ptr(desc),
+                                    self.recv.ptr_table(), self.flags.ptr_table(), self.epoch, ptr(self.counter),
+                                    stream_ptr()), "a2a_push_blocks")
+    check(lib().tpb_a2a_wait(ptr(self.flags.local), self.world, self.epoch, stream_ptr()), "a2a_wait")
+    out = self.recv.local[: n_out * self.dim].view(n_out, self.dim).clone()
+    if zero_rows is not None:
+      out.index_fill_(0, zero_rows, 0)
+    return out
+
   def exchange(self, x, count_matrix):
     """``x``: rows sorted by destination rank; ``count_matrix[s][r]``: rows rank s sends to rank r
     (host integers, the same on every rank).  Returns the rows this rank receives, source-major."""
@@ -77,6 +102,140 @@ class _PushAllToAllFn(torch.autograd.Function):
     return out, None, None
 
 
+def _prefix(v):
+  out = [0]
+  for a in v:
+    out.append(out[-1] + int(a))
+  return out
+
+
+class _ExchangePlan:
+  """Host-side description of one dispatch / return pair, computed from the count matrix
+  ``C[s][e]`` (pairs of rank s routed to global expert e), the same on every rank.
+
+  Send layout (on every rank): its pairs sorted by expert, compact.  Receive layout on the owner:
+  expert-major, every expert's segment padded to a multiple of 128 rows, inside a segment the rows
+  of source 0, 1, ... in order.  So rows arrive grouped for the grouped GEMMs, whatever rank they
+  came from, and no expert ids travel."""
+
+  def __init__(self, C, me: int, ep: int, el: int, device):
+    E = ep * el
+    tot = [[sum(int(C[s][r * el + j]) for s in range(ep)) for j in range(el)] for r in range(ep)]
+    offpad = [_prefix([(v + 127) // 128 * 128 for v in tot[r]]) for r in range(ep)]
+    send_off = [_prefix(C[s]) for s in range(ep)]
+    # dispatch: one block per global expert, in send order
+    start = send_off[me]
+    rank = [e // el for e in range(E)]
+    row0 = [offpad[e // el][e % el] + sum(int(C[s][e]) for s in range(me)) for e in range(E)]
+    self.dispatch = torch.tensor(start + rank + row0, dtype=torch.int64, device=device)
+    self.dispatch_blocks = E
+    self.n_send = start[-1]
+    # return: walk the receive layout; padding rows form blocks that go nowhere (rank -1)
+    start, rank, row0, zero = [], [], [], []
+    for j in range(el):
+      e = me * el + j
+      pos = offpad[me][j]
+      for s in range(ep):
+        start.append(pos); rank.append(s); row0.append(send_off[s][e])
+        pos += int(C[s][e])
+      start.append(pos); rank.append(-1); row0.append(0)
+      zero.extend(range(pos, offpad[me][j + 1]))
+    start.append(offpad[me][el])
+    self.ret = torch.tensor(start + rank + row0, dtype=torch.int64, device=device)
+    self.ret_blocks = len(rank)
+    self.n_pad = offpad[me][el]
+    self.zero_rows = torch.tensor(zero, dtype=torch.int64, device=device) if zero else None
+    tiles = []
+    for j in range(el):
+      tiles += [j] * ((offpad[me][j + 1] - offpad[me][j]) // 128)
+    self.tile_expert = torch.tensor(tiles, dtype=torch.int32, device=device)
+    self.k_offsets = torch.tensor(offpad[me], dtype=torch.int32, device=device)
+    self.num_rows = self.n_pad
+
+
+class _EPGroupedMLPFn(torch.autograd.Function):
+  """Routed SwiGLU experts across the expert group with this framework's own exchange kernels in both
+  passes: sort pairs by expert, push rows to the owners (they land grouped by expert), grouped
+  GEMMs, push results back, weighted combine.  One host synchronisation per call (the count matrix)."""
+
+  @staticmethod
+  def forward(ctx, x, weights, w_gate, w_up, w_down, epm, idx, fused_gate_up):
+    from ..ops import _lib
+    t, k = idx.shape
+    dev = x.device
+    flat = idx.reshape(-1).long()
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=epm.num_experts)
+    cm = torch.empty(epm.ep, epm.num_experts, dtype=counts.dtype, device=dev)
+    dist.all_gather_into_tensor(cm, counts, group=epm.group)
+    plan = _ExchangePlan(cm.tolist(), epm.rank, epm.ep, epm.local_experts, dev)
+    src_tok = (order // k).to(torch.int32).contiguous()
+    dest_pos = torch.empty(t * k, dtype=torch.int32, device=dev)
+    dest_pos[order] = torch.arange(t * k, dtype=torch.int32, device=dev)
+    dest_pos = dest_pos.view(t, k)
+    a2a_d, a2a_r = epm._push_pair(t, k, x.shape[-1], dev)
+    send = moe_ops.gather_rows(x, src_tok)
+    xg = a2a_d.exchange_blocks(send, plan.dispatch, plan.dispatch_blocks, plan.n_pad, plan.zero_rows)
+    need_grad = any(ctx.needs_input_grad)
+    gu = act = None
+    if plan.n_pad > 0:
+      n2 = w_gate.shape[2] if fused_gate_up else 2 * w_gate.shape[2]
+      gu = torch.empty(plan.n_pad, n2, dtype=x.dtype, device=dev) if need_grad else None
+      act = moe_ops.grouped_gemm_rows(xg, w_gate, plan, b_mn=True, b2=None if fused_gate_up else w_up,
+                                      epi=_lib.EPI_SWIGLU, c2=gu, n_total=n2)
+      rows = moe_ops.grouped_gemm_rows(act, w_down, plan, b_mn=True)
+    else:
+      rows = xg
+    back = a2a_r.exchange_blocks(rows, plan.ret, plan.ret_blocks, t * k)
+    y = moe_ops.combine_rows(back, dest_pos, weights)
+    ctx.epm, ctx.plan, ctx.fused, ctx.tk = epm, plan, fused_gate_up, (t, k)
+    if need_grad:
+      ctx.save_for_backward(weights, w_gate, w_up, w_down, xg, gu, act, back, order, src_tok, dest_pos)
+    return y
+
+  @staticmethod
+  def backward(ctx, dy):
+    from ..ops import kernels as kk
+    weights, w_gate, w_up, w_down, xg, gu, act, back, order, src_tok, dest_pos = ctx.saved_tensors
+    epm, plan, fused = ctx.epm, ctx.plan, ctx.fused
+    t, k = ctx.tk
+    dy = dy.contiguous()
+    a2a_d, a2a_r = epm._push_pair(t, k, dy.shape[-1], dy.device)
+    dweights = moe_ops.combine_dw(back, dest_pos, dy) if ctx.needs_input_grad[1] else None
+    w_sorted = weights.reshape(-1)[order].float().contiguous()
+    d_back = moe_ops.gather_rows(dy, src_tok, w_sorted)
+    d_rows = a2a_d.exchange_blocks(d_back, plan.dispatch, plan.dispatch_blocks, plan.n_pad, plan.zero_rows)
+    deliver = moe_ops._deliver_wgrad
+    if plan.n_pad > 0:
+      f = gu.shape[1] // 2
+      dact = moe_ops.grouped_gemm_rows(d_rows, w_down, plan, b_mn=False)
+      g_down = deliver(w_down, lambda out, acc: moe_ops.grouped_gemm_wgrad(act, d_rows, plan, out, acc))
+      dgu = kk.swiglu_bwd(dact, gu)
+      if fused:
+        d_xg = moe_ops.grouped_gemm_rows(dgu, w_gate, plan, b_mn=False)
+        g_gate = deliver(w_gate, lambda out, acc: moe_ops.grouped_gemm_wgrad(xg, dgu, plan, out, acc))
+        g_up = None
+      else:
+        dg, du = dgu[:, :f], dgu[:, f:]
+        d_xg = moe_ops.grouped_gemm_rows(dg, w_gate, plan, b_mn=False)
+        moe_ops.grouped_gemm_rows(du, w_up, plan, b_mn=False, epi=_lib_epi_acc(), out=d_xg)
+        g_gate = deliver(w_gate, lambda out, acc: moe_ops.grouped_gemm_wgrad(xg, dg, plan, out, acc))
+        g_up = deliver(w_up, lambda out, acc: moe_ops.grouped_gemm_wgrad(xg, du, plan, out, acc))
+    else:
+      d_xg = d_rows
+      zero = lambda out, acc: None if acc else out.zero_()   # noqa: E731
+      g_down, g_gate = deliver(w_down, zero), deliver(w_gate, zero)
+      g_up = None if fused else deliver(w_up, zero)
+    d_send = a2a_r.exchange_blocks(d_xg, plan.ret, plan.ret_blocks, t * k)
+    dx = moe_ops.combine_rows(d_send, dest_pos, None) if ctx.needs_input_grad[0] else None
+    return dx, dweights, g_gate, g_up, g_down, None, None, None
+
+
+def _lib_epi_acc():
+  from ..ops import _lib
+  return _lib.EPI_BF16_ACC
+
+
 class ExpertParallelMLP:
   def __init__(self, mesh, num_experts: int, fused_exchange: bool = False):
     self.group = mesh.group("expert")
@@ -93,7 +252,7 @@ class ExpertParallelMLP:
     every rank lands on one rank)."""
     key = (t, k, dim)
     if key not in self._push:
-      self._push[key] = (PushAllToAll(self.group, self.ep * t * k, dim, device),
+      self._push[key] = (PushAllToAll(self.group, self.ep * t * k + self.local_experts * 128, dim, device),
                          PushAllToAll(self.group, t * k, dim, device))
     return self._push[key]
 
@@ -102,6 +261,12 @@ class ExpertParallelMLP:
     """Same contract as :func:`ops.moe.grouped_mlp` but ``w_*`` hold only the local experts."""
     t, k = idx.shape
     e, el = self.num_experts, self.local_experts
+    if (self.fused_exchange and capacity is None and x.is_cuda and x.dtype == torch.bfloat16
+        and x.shape[-1] % 64 == 0 and w_down.shape[1] % 64 == 0 and dist.get_backend(self.group) == "nccl"
+        and moe_ops._kernels_ok(x, w_gate, w_down)):
+      wu = w_gate if fused_gate_up else w_up
+      return _EPGroupedMLPFn.apply(x.contiguous(), weights.float().contiguous(), w_gate, wu, w_down, self,
+                                   idx, fused_gate_up)
     flat = idx.reshape(-1).long()
     keep = torch.ones_like(flat, dtype=torch.bool)
     if capacity is not None:
