@@ -14,6 +14,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ..ops import _lib
 from ..ops import moe as moe_ops
 from .collectives import all_to_all_rows
 
@@ -160,7 +161,6 @@ class _EPGroupedMLPFn(torch.autograd.Function):
 
   @staticmethod
   def forward(ctx, x, weights, w_gate, w_up, w_down, epm, idx, fused_gate_up):
-    from ..ops import _lib
     t, k = idx.shape
     dev = x.device
     flat = idx.reshape(-1).long()
@@ -218,7 +218,7 @@ class _EPGroupedMLPFn(torch.autograd.Function):
       else:
         dg, du = dgu[:, :f], dgu[:, f:]
         d_xg = moe_ops.grouped_gemm_rows(dg, w_gate, plan, b_mn=False)
-        moe_ops.grouped_gemm_rows(du, w_up, plan, b_mn=False, epi=_lib_epi_acc(), out=d_xg)
+        moe_ops.grouped_gemm_rows(du, w_up, plan, b_mn=False, epi=_lib.EPI_BF16_ACC, out=d_xg)
         g_gate = deliver(w_gate, lambda out, acc: moe_ops.grouped_gemm_wgrad(xg, dg, plan, out, acc))
         g_up = deliver(w_up, lambda out, acc: moe_ops.grouped_gemm_wgrad(xg, du, plan, out, acc))
     else:
@@ -229,11 +229,6 @@ class _EPGroupedMLPFn(torch.autograd.Function):
     d_send = a2a_r.exchange_blocks(d_xg, plan.ret, plan.ret_blocks, t * k)
     dx = moe_ops.combine_rows(d_send, dest_pos, None) if ctx.needs_input_grad[0] else None
     return dx, dweights, g_gate, g_up, g_down, None, None, None
-
-
-def _lib_epi_acc():
-  from ..ops import _lib
-  return _lib.EPI_BF16_ACC
 
 
 class ExpertParallelMLP:
