@@ -87,6 +87,7 @@ struct GemmParams {
   // owner's bf16 gradient shard over P2P with vector red.add.
   int rs_world;
   int tile_rot;                 // tiles are visited starting from this one (rotation by rank, see tpb_gemm_rs_bf16)
+  int te_stride;                // tile_expert entries per m-tile (2 for CTA-pair tiles of 256 rows)
   void* rs_dst[8];              // gradient shard base of every rank (symmetric memory), bf16
   long long rs_shard_elems;
   long long rs_c_offset;        // element offset of C inside the sharded flat buffer
@@ -125,7 +126,7 @@ __device__ __forceinline__ TileInfo tile_info(const GemmParams& p, int t, int m_
   } else {
     tile_coords(t, m_tiles, n_tiles, p.group_m, ti.tm, ti.tn);
     if (p.mode == 1) {
-      ti.e = p.tile_expert[ti.tm];
+      ti.e = p.tile_expert[ti.tm * p.te_stride];   // entries are per 128 rows; a pair tile covers two
       ti.skip = ti.e < 0;
     }
   }
@@ -400,10 +401,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const CUtensorMap* mb = (swiglu && rank == 1) ? &tmB2 : &tmB;
             const int nb = (swiglu && rank == 1) ? p.b2_off + n0 : n0 + rank * 128;
             if (!B_MN) {
-              tma_load_3d_pair(sB, mb, bar, k0, nb, 0);
+              tma_load_3d_pair(sB, mb, bar, k0, nb, ez);
             } else {
 #pragma unroll
-              for (int c = 0; c < 2; ++c) tma_load_3d_pair(sB + c * 8192, mb, bar, nb + c * 64, k0, 0);
+              for (int c = 0; c < 2; ++c) tma_load_3d_pair(sB + c * 8192, mb, bar, nb + c * 64, k0, ez);
             }
           } else {
           mbar_expect_tx(&full[stage], STAGE_BYTES);
@@ -724,6 +725,7 @@ struct GemmCall {
   void* c2; long long ldc2;
   int max_ctas;
   int mode; const int* tile_expert; const int* k_offsets; long long c_stride;
+  int row_align;                // grouped rows mode: expert segments are padded to this many rows (128 or 256)
   // fusion with collectives (0 / null when unused)
   int ag_world, ag_copiers, ag_local; const void* const* ag_src; void* ag_dst; long long ag_shard_elems, ag_b_offset;
   unsigned* ag_flags; unsigned ag_epoch;
@@ -783,6 +785,7 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.ag_flags = g.ag_flags; p.ag_epoch = g.ag_epoch; p.ag_local = g.ag_world > 0 ? g.ag_local : -1;
   p.rs_world = g.rs_world; p.rs_shard_elems = g.rs_shard_elems; p.rs_c_offset = g.rs_c_offset;
   p.tile_rot = 0;
+  p.te_stride = 1;
   p.ag_push = (g.ag_world > 0 && g.ag_push_dst != nullptr && g.ag_push_flags != nullptr) ? 1 : 0;
   p.ag_push_mc = p.ag_push ? g.ag_push_mc : nullptr;
   if (p.ag_push) p.ag_chunk_elems = 131072;   // 256 KB per flag: a CTA streams a chunk with one fence at its end
@@ -832,9 +835,13 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
     (void)cudaGetLastError();
     return n < sm_count() / 2 ? n : sm_count() / 2;
   }();
-  const long long pair_tiles = (long long)((g.M + 2 * BM - 1) / (2 * BM)) * n_tiles;
-  if (pair_mode != 0 && max_pairs > 0 && g.mode == 0 && g.ag_world == 0 && g.epi != TPB_EPI_RS_BF16 &&
+  const long long pair_tiles = (long long)((g.M + 2 * BM - 1) / (2 * BM)) * n_tiles * (g.mode == 2 ? g.E : 1);
+  // grouped modes: rows mode needs expert segments padded to whole 256-row tiles; the per-expert
+  // K-range mode (weight gradients) has no such condition
+  const bool pair_shape_ok = g.mode == 0 || g.mode == 2 || (g.mode == 1 && g.row_align > 0 && g.row_align % (2 * BM) == 0);
+  if (pair_mode != 0 && max_pairs > 0 && pair_shape_ok && g.ag_world == 0 && g.epi != TPB_EPI_RS_BF16 &&
       g.max_ctas == 0 && (pair_mode == 2 || pair_tiles >= max_pairs)) {
+    p.te_stride = 2;
     const int pairs = pair_tiles > max_pairs ? max_pairs : (int)pair_tiles;
     const int m_tiles2 = (g.M + 2 * BM - 1) / (2 * BM);
     p.group_m = m_tiles2 < 8 ? m_tiles2 : 8;
@@ -873,7 +880,7 @@ extern "C" int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B
                                      int E, long long lda, long long ldb, long long b_expert_stride, long long ldc,
                                      int a_mn, int b_mn, int epi, float alpha, void* c2, long long ldc2, int mode,
                                      const int* tile_expert, const int* k_offsets, long long c_stride,
-                                     void* stream_) {
+                                     int row_align, void* stream_) {
   if (mode != 1 && mode != 2) return -2;
   if (mode == 1 && !tile_expert) return -2;
   if (mode == 2 && !k_offsets) return -2;
@@ -884,6 +891,7 @@ extern "C" int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B
   g.a_mn = a_mn; g.b_mn = b_mn; g.epi = epi; g.alpha = alpha;
   g.aux = nullptr; g.ldaux = 0; g.c2 = c2; g.ldc2 = ldc2; g.max_ctas = 0;
   g.mode = mode; g.tile_expert = tile_expert; g.k_offsets = k_offsets; g.c_stride = c_stride;
+  g.row_align = row_align;
   return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
 }
 

@@ -274,6 +274,79 @@ __global__ void a2a_push_kernel(const A2APushParams p) {
   }
 }
 
+// ----------------------------------------------------------------------------
+// Dispatch plan: a stable counting sort of the (token, slot) pairs by expert into 128-row padded
+// segments, in one CTA.  Every warp owns a contiguous range of pairs; sweep 1 counts per (warp,
+// expert), a prefix over warps gives each warp its first row in every expert's segment, sweep 2
+// walks the range again and hands out rows in order (match_any groups equal experts inside a
+// warp, the lane order breaks ties), so the result does not depend on scheduling.
+// Outputs: counts[E], k_offsets[E+1] (multiples of 128), dest[n] (row of each pair), src_row[M]
+// (token feeding a row) and src_pair[M] (pair feeding a row), both pre-filled with -1 by the
+// host, tile_expert[M/128] (pre-filled with -1).
+// ----------------------------------------------------------------------------
+constexpr int PLAN_THREADS = 1024;
+constexpr int PLAN_MAX_E = 256;
+
+__global__ void __launch_bounds__(PLAN_THREADS, 1)
+moe_plan_kernel(const int* __restrict__ idx, int n, int K, int E, int align, int* __restrict__ counts,
+                int* __restrict__ k_offsets, int* __restrict__ dest, int* __restrict__ src_row,
+                long long* __restrict__ src_pair, int* __restrict__ tile_expert) {
+  __shared__ int wcount[32][PLAN_MAX_E];     // sweep 1: pairs of (warp, expert); sweep 2: next row
+  __shared__ int off_pad[PLAN_MAX_E + 1];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < 32 * PLAN_MAX_E; i += PLAN_THREADS) (&wcount[0][0])[i] = 0;
+  __syncthreads();
+  const int per_warp = ((n + 31) / 32 + 31) / 32 * 32;      // multiple of 32 so that lanes stay aligned
+  const int lo = warp * per_warp, hi = min(n, lo + per_warp);
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const int e = i < hi ? idx[i] : -1;
+    const bool ok = e >= 0 && e < E;
+    const unsigned m = __match_any_sync(0xffffffffu, ok ? e : -1);
+    if (ok && (m & ((1u << lane) - 1)) == 0) wcount[warp][e] += __popc(m);
+    __syncwarp();
+  }
+  __syncthreads();
+  if (threadIdx.x < E) {
+    int total = 0;
+    for (int w = 0; w < 32; ++w) total += wcount[w][threadIdx.x];
+    counts[threadIdx.x] = total;
+    off_pad[threadIdx.x + 1] = (total + align - 1) / align * align;
+  }
+  if (threadIdx.x == 0) off_pad[0] = 0;
+  __syncthreads();
+  if (threadIdx.x == 0)
+    for (int e = 0; e < E; ++e) off_pad[e + 1] += off_pad[e];
+  __syncthreads();
+  if (threadIdx.x <= E) k_offsets[threadIdx.x] = off_pad[threadIdx.x];
+  if (threadIdx.x < E) {
+    int run = off_pad[threadIdx.x];
+    for (int w = 0; w < 32; ++w) {
+      const int c = wcount[w][threadIdx.x];
+      wcount[w][threadIdx.x] = run;
+      run += c;
+    }
+    for (int t = off_pad[threadIdx.x] / 128; t < off_pad[threadIdx.x + 1] / 128; ++t) tile_expert[t] = threadIdx.x;
+  }
+  __syncthreads();
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const int e = i < hi ? idx[i] : -1;
+    const bool ok = e >= 0 && e < E;
+    const unsigned m = __match_any_sync(0xffffffffu, ok ? e : -1);
+    int pos = -1;
+    if (ok) pos = wcount[warp][e] + __popc(m & ((1u << lane) - 1));
+    __syncwarp();
+    if (ok && (m & ((1u << lane) - 1)) == 0) wcount[warp][e] += __popc(m);
+    __syncwarp();
+    if (i < hi) dest[i] = pos;
+    if (ok) {
+      src_row[pos] = i / K;
+      src_pair[pos] = i;
+    }
+  }
+}
+
 // Block form of the push: the source rows are a sequence of `n_blocks` contiguous blocks, block b =
 // rows [start[b], start[b+1]) going to rank dst_rank[b] at row dst_row0[b] of its receive buffer.
 // The descriptors live in device memory as 64-bit words: start[n_blocks + 1], dst_rank[n_blocks],
@@ -414,6 +487,22 @@ extern "C" int tpb_a2a_push_rows(const void* src, int n_rows, int dim, int world
   p.epoch = epoch; p.done_counter = done_counter;
   int grid = n_rows < 1 ? 1 : (n_rows < 4 * sm_count() ? n_rows : 4 * sm_count());
   a2a_push_kernel<<<grid, 256, 0, STREAM(stream)>>>(p);
+  return rc_of(cudaGetLastError());
+}
+
+// idx [tokens, K] int32 (entries outside [0, E) are dropped: dest = -1).  align: 128 or 256 rows per
+// segment step.  rows = static row count of the padded layout (>= round_up(tokens * K, align) + align * E).  Everything is on the device; no host read.
+extern "C" int tpb_moe_plan(const int* idx, int tokens, int K, int E, int rows, int align, int* counts, int* k_offsets,
+                            int* dest, int* src_row, long long* src_pair, int* tile_expert, void* stream) {
+  if (E < 1 || E > PLAN_MAX_E || K < 1 || tokens < 0 || (align != 128 && align != 256) || rows % align) return -2;
+  const long long n = (long long)tokens * K;
+  if (n > (1LL << 30) || rows < (n + align - 1) / align * align + (long long)align * E) return -2;
+  cudaError_t e = cudaMemsetAsync(src_row, 0xFF, sizeof(int) * rows, STREAM(stream));
+  if (e == cudaSuccess) e = cudaMemsetAsync(src_pair, 0xFF, sizeof(long long) * rows, STREAM(stream));
+  if (e == cudaSuccess) e = cudaMemsetAsync(tile_expert, 0xFF, sizeof(int) * (rows / 128), STREAM(stream));
+  if (e != cudaSuccess) return rc_of(e);
+  moe_plan_kernel<<<1, PLAN_THREADS, 0, STREAM(stream)>>>(idx, (int)n, K, E, align, counts, k_offsets, dest, src_row, src_pair,
+                                                          tile_expert);
   return rc_of(cudaGetLastError());
 }
 

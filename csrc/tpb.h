@@ -89,10 +89,11 @@ int tpb_cast_f32_to_bf16(const float* src, void* dst, long long n, float scale, 
 //          B (and B2 for the "up" half of a SwiGLU epilogue) hold E matrices b_expert_stride apart.
 //  mode 2: per-expert wgrad C[e] = A[:, rows of e] * B[:, rows of e]^T with both operands stored
 //          row-major over the grouped rows (a_mn = b_mn = 1); k_offsets[E+1] are 64-aligned.
+// row_align: rows to which expert segments are padded in mode 1 (128, or 256: CTA-pair tiles may be used).
 int tpb_grouped_gemm_bf16(const void* A, const void* B, const void* B2, void* C, int M, int N, int K, int E,
                           long long lda, long long ldb, long long b_expert_stride, long long ldc, int a_mn, int b_mn,
                           int epi, float alpha, void* c2, long long ldc2, int mode, const int* tile_expert,
-                          const int* k_offsets, long long c_stride, void* stream);
+                          const int* k_offsets, long long c_stride, int row_align, void* stream);
 
 // GEMM fused with the all-gather of the (flat, sharded) buffer that holds B, and GEMM fused with the
 // reduce-scatter of C into the owners' shards; see the comments at the definitions in gemm_sm100.cu.
@@ -121,6 +122,9 @@ int tpb_moe_combine_dw(const void* rows, const int* dest, const void* dout, floa
                        int dim, void* stream);
 
 // Variable-size all-to-all of rows by plain stores into the peers' receive buffers (moe.cu).
+// Stable counting sort of (token, slot) pairs by expert into 128-row padded segments (see moe.cu).
+int tpb_moe_plan(const int* idx, int tokens, int K, int E, int rows, int align, int* counts, int* k_offsets,
+                 int* dest, int* src_row, long long* src_pair, int* tile_expert, void* stream);
 int tpb_a2a_push_rows(const void* src, int n_rows, int dim, int world, int me, const int* src_start,
                       const long long* dst_row0, void* const* dst, unsigned* const* flags, unsigned epoch,
                       unsigned* done_counter, void* stream);

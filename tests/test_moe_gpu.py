@@ -5,7 +5,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-from torchprime_b200.ops import moe, reference as ref
+from torchprime_b200.ops import _lib, moe, reference as ref
 
 
 def _rel(a, b):
@@ -75,6 +75,53 @@ def test_dispatch_plan(cuda_lib, capacity):
   for i, e in enumerate(te.tolist()):
     if e >= 0:
       assert plan.k_offsets[e] <= i * 128 < plan.k_offsets[e + 1]
+
+
+@pytest.mark.parametrize("T,K,E", [(3000, 6, 64), (1111, 8, 256), (5, 1, 3), (8192, 2, 8)])
+def test_dispatch_plan_kernel_equals_the_sort_based_plan(cuda_lib, T, K, E):
+  """One-CTA counting sort against the torch formulation (stable argsort): identical rows."""
+  torch.manual_seed(11)
+  idx = torch.randint(0, E, (T, K), device="cuda", dtype=torch.int32)
+  if E > 4:
+    idx[idx == 1] = 2                                       # an expert that receives nothing
+  for align in (128, 256):
+    a = moe.build_dispatch_plan(idx, E, use_kernel=True, row_align=align)
+    b = moe.build_dispatch_plan(idx, E, use_kernel=False, row_align=align)
+    assert a.row_align == align and all(v % align == 0 for v in a.k_offsets.tolist())
+    assert torch.equal(a.k_offsets, b.k_offsets) and torch.equal(a.dest, b.dest)
+    assert torch.equal(a.tile_expert, b.tile_expert) and torch.equal(a.src_pair, b.src_pair)
+  assert a.num_rows == b.num_rows
+  assert torch.equal(a.counts.long(), b.counts.long()) and torch.equal(a.k_offsets, b.k_offsets)
+  assert torch.equal(a.dest, b.dest) and torch.equal(a.src_pair, b.src_pair) and torch.equal(a.src_row, b.src_row)
+  assert torch.equal(a.tile_expert, b.tile_expert)
+  again = moe.build_dispatch_plan(idx, E, use_kernel=True, row_align=256)
+  assert torch.equal(a.dest, again.dest)
+
+
+def test_grouped_mlp_on_cta_pair_tiles(cuda_lib):
+  """Enough rows per expert for 256-row segments: the forward, input-gradient and weight-gradient
+  grouped GEMMs run on 256x256 CTA-pair tiles; one expert gets no rows at all."""
+  torch.manual_seed(5)
+  T, K, E, D, Fd = 2048, 2, 4, 1024, 2048
+  x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+  wg = (torch.randn(E, D, Fd, device="cuda") / D ** 0.5).to(torch.bfloat16).requires_grad_(True)
+  wu = (torch.randn(E, D, Fd, device="cuda") / D ** 0.5).to(torch.bfloat16).requires_grad_(True)
+  wd = (torch.randn(E, Fd, D, device="cuda") / Fd ** 0.5).to(torch.bfloat16).requires_grad_(True)
+  logits = torch.randn(T, E, device="cuda")
+  logits[:, 3] = -1e9                                        # expert 3 is never chosen
+  w, idx, _ = moe.router_topk(logits, K, mode="softmax")
+  assert moe.build_dispatch_plan(idx, E).row_align == 256
+  w = w.detach().requires_grad_(True)
+  y = moe.grouped_mlp(x, w, idx, wg, wu, wd)
+  dy = torch.randn_like(y)
+  y.backward(dy)
+  xs, wgs, wus, wds, ws = (t.detach().float().requires_grad_(True) for t in (x, wg, wu, wd, w))
+  yr = moe.grouped_mlp_reference(xs, ws, idx, wgs, wus, wds)
+  yr.backward(dy.float())
+  assert _rel(y, yr) < 2e-2 and _rel(x.grad, xs.grad) < 3e-2
+  assert _rel(wd.grad, wds.grad) < 3e-2 and _rel(wg.grad, wgs.grad) < 3e-2 and _rel(wu.grad, wus.grad) < 3e-2
+  assert float(wd.grad[3].abs().max()) == 0.0 and float(wg.grad[3].abs().max()) == 0.0
+  _lib.raise_on_device_timeout()
 
 
 @pytest.mark.parametrize("E,K,D,Fd,fused", [(4, 2, 128, 256, False), (8, 2, 256, 192, False), (4, 1, 128, 128, True)])

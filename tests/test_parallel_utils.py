@@ -164,7 +164,8 @@ def test_homogeneous_sequential_passes_keyword_arguments_to_every_layer():
     HomogeneousSequential(Scale(1.0), nn.ReLU())
 
 
-def test_expert_exchange_plan_groups_rows_by_expert_and_returns_them():
+@pytest.mark.parametrize("scale,align", [(1, 128), (20, 256)])
+def test_expert_exchange_plan_groups_rows_by_expert_and_returns_them(scale, align):
   """The host-side plan of the expert-parallel exchange, checked by replaying the block-push kernel's
   rule in Python: rows land at the owner grouped by expert in padded segments, padding rows are the
   ones listed for zeroing, and the return blocks bring every row back to its place."""
@@ -175,9 +176,10 @@ def test_expert_exchange_plan_groups_rows_by_expert_and_returns_them():
   random.seed(0)
   ep, el = 4, 3
   E = ep * el
-  C = [[random.choice([0, 0, 1, 5, 130, 257]) for _ in range(E)] for _ in range(ep)]
+  C = [[scale * random.choice([0, 0, 1, 5, 130, 257]) for _ in range(E)] for _ in range(ep)]
   C[2] = [0] * E                                           # a rank that sends nothing
   plans = [_ExchangePlan(C, me, ep, el, "cpu") for me in range(ep)]
+  assert all(p.row_align == align for p in plans)
 
   def push(src_rows, desc, nb, dst):
     start, rank, row0 = desc[:nb + 1].tolist(), desc[nb + 1:2 * nb + 1].tolist(), desc[2 * nb + 1:].tolist()
@@ -194,7 +196,7 @@ def test_expert_exchange_plan_groups_rows_by_expert_and_returns_them():
   for r in range(ep):
     p = plans[r]
     koff = p.k_offsets.tolist()
-    assert p.n_pad == koff[-1] and all(v % 128 == 0 for v in koff)
+    assert p.n_pad == koff[-1] and all(v % p.row_align == 0 for v in koff) and p.row_align in (128, 256)
     assert p.tile_expert.tolist() == [j for j in range(el) for _ in range((koff[j + 1] - koff[j]) // 128)]
     filled = set(recv[r])
     zero = set(p.zero_rows.tolist()) if p.zero_rows is not None else set()

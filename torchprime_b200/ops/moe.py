@@ -26,8 +26,9 @@ from ._lib import check, lib, ptr, stream_ptr
 
 P, I, LL, FL = c_void_p, c_int, c_longlong, c_float
 _lib.register_signature("tpb_grouped_gemm_bf16", [P, P, P, P, I, I, I, I, LL, LL, LL, LL, I, I, I, FL, P, LL, I, P, P,
-                                                  LL, P])
+                                                  LL, I, P])
 _lib.register_signature("tpb_router_topk", [P, I, P, P, P, P, I, I, I, I, I, I, I, FL, P])
+_lib.register_signature("tpb_moe_plan", [P, I, I, I, I, I, P, P, P, P, P, P, P])
 _lib.register_signature("tpb_moe_gather", [P, P, P, P, LL, I, P])
 _lib.register_signature("tpb_moe_combine", [P, P, P, P, LL, I, I, P])
 _lib.register_signature("tpb_moe_combine_dw", [P, P, P, P, LL, I, I, P])
@@ -108,10 +109,12 @@ class DispatchPlan:
   num_rows: int              # M (static upper bound)
   num_experts: int
   top_k: int
+  row_align: int = 128       # expert segments are padded to this many rows (256 lets the CTA-pair GEMM run)
 
 
 def build_dispatch_plan(idx: torch.Tensor, num_experts: int, capacity: int | None = None,
-                        rows_per_group: int | None = None) -> DispatchPlan:
+                        rows_per_group: int | None = None, use_kernel: bool | None = None,
+                        row_align: int | None = None) -> DispatchPlan:
   """Sort (token, slot) pairs by expert into 128-aligned segments, entirely on the device.
 
   ``capacity``: maximum rows per expert *per group of ``rows_per_group`` consecutive tokens*
@@ -120,6 +123,16 @@ def build_dispatch_plan(idx: torch.Tensor, num_experts: int, capacity: int | Non
   t, k = idx.shape
   e = num_experts
   dev = idx.device
+  if row_align is None:
+    # 256-row segments let the grouped GEMMs use 256x256 CTA-pair tiles; worth the extra padding
+    # when an expert sees about a thousand rows or more
+    row_align = 256 if (capacity is None and (t * k) // e >= 1024) else ROW_ALIGN
+  assert row_align in (128, 256)
+  if use_kernel is None:
+    use_kernel = capacity is None and idx.is_cuda and _kernels_ok() and e <= 256
+  if use_kernel:
+    return _build_dispatch_plan_kernel(idx, e, row_align)
+  align = row_align
   flat = idx.reshape(-1).long()
   n = flat.numel()
   if capacity is not None:
@@ -138,7 +151,7 @@ def build_dispatch_plan(idx: torch.Tensor, num_experts: int, capacity: int | Non
   sorted_e = flat[order]
   counts_all = torch.bincount(flat, minlength=e + 1)
   counts = counts_all[:e]
-  padded = (counts + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN
+  padded = (counts + align - 1) // align * align
   ends_pad = torch.cumsum(padded, 0)
   off_pad = ends_pad - padded
   off = torch.cumsum(counts_all, 0) - counts_all
@@ -146,7 +159,7 @@ def build_dispatch_plan(idx: torch.Tensor, num_experts: int, capacity: int | Non
   valid = sorted_e < e
   dest_sorted = torch.where(valid, torch.cat([off_pad, off_pad.new_zeros(1)])[sorted_e] + rank,
                             torch.full_like(rank, -1))
-  m = (n + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN + e * ROW_ALIGN
+  m = (n + align - 1) // align * align + e * align
   dest = torch.empty(n, dtype=torch.long, device=dev)
   dest[order] = dest_sorted
   src_pair = torch.full((m + 1,), -1, dtype=torch.long, device=dev)
@@ -159,7 +172,24 @@ def build_dispatch_plan(idx: torch.Tensor, num_experts: int, capacity: int | Non
   k_offsets = torch.cat([ends_pad.new_zeros(1), ends_pad]).to(torch.int32)
   return DispatchPlan(src_row=src_row.contiguous(), src_pair=src_pair, dest=dest.view(t, k).to(torch.int32).contiguous(),
                       tile_expert=tile_expert.contiguous(), k_offsets=k_offsets.contiguous(), counts=counts, num_rows=m,
-                      num_experts=e, top_k=k)
+                      num_experts=e, top_k=k, row_align=align)
+
+
+def _build_dispatch_plan_kernel(idx: torch.Tensor, e: int, align: int = ROW_ALIGN) -> DispatchPlan:
+  """The same plan from one kernel launch (a stable counting sort in a single CTA) instead of about
+  twenty-five torch kernels; nothing is read back to the host."""
+  t, k = idx.shape
+  dev = idx.device
+  n = t * k
+  m = (n + align - 1) // align * align + e * align
+  idx32 = idx.to(torch.int32).contiguous()
+  ints = torch.empty(e + (e + 1) + n + m + m // ROW_ALIGN, dtype=torch.int32, device=dev)
+  counts, k_offsets, dest, src_row, tile_expert = torch.split(ints, [e, e + 1, n, m, m // ROW_ALIGN])
+  src_pair = torch.empty(m, dtype=torch.int64, device=dev)
+  check(lib().tpb_moe_plan(ptr(idx32), t, k, e, m, align, ptr(counts), ptr(k_offsets), ptr(dest), ptr(src_row), ptr(src_pair),
+                           ptr(tile_expert), stream_ptr()), "moe_plan")
+  return DispatchPlan(src_row=src_row, src_pair=src_pair, dest=dest.view(t, k), tile_expert=tile_expert,
+                      k_offsets=k_offsets, counts=counts, num_rows=m, num_experts=e, top_k=k, row_align=align)
 
 
 # ----------------------------------------------------------------------------- raw kernels
@@ -203,7 +233,8 @@ def grouped_gemm_rows(a, b, plan: DispatchPlan, *, b_mn: bool, b2=None, epi=_lib
   ldb = b.stride(1)
   rc = lib().tpb_grouped_gemm_bf16(ptr(a), ptr(b), ptr(b2), ptr(out), m, n, k, e, a.stride(0), ldb, b.stride(0),
                                    out.stride(0), 0, int(b_mn), epi, 1.0, ptr(c2), c2.stride(0) if c2 is not None else 0,
-                                   1, ptr(plan.tile_expert), None, 0, stream_ptr())
+                                   1, ptr(plan.tile_expert), None, 0, int(getattr(plan, "row_align", ROW_ALIGN)),
+                                   stream_ptr())
   check(rc, f"grouped_gemm rows M={m} N={n} K={k} E={e}")
   return out
 
@@ -218,7 +249,7 @@ def grouped_gemm_wgrad(a_rows, b_rows, plan: DispatchPlan, out, accumulate: bool
     epi = _lib.EPI_BF16_ACC if accumulate else _lib.EPI_BF16
   rc = lib().tpb_grouped_gemm_bf16(ptr(a_rows), ptr(b_rows), None, ptr(out), da, db, a_rows.shape[0], e,
                                    a_rows.stride(0), b_rows.stride(0), 0, out.stride(1), 1, 1, epi, 1.0, None, 0, 2,
-                                   None, ptr(plan.k_offsets), out.stride(0), stream_ptr())
+                                   None, ptr(plan.k_offsets), out.stride(0), 0, stream_ptr())
   check(rc, f"grouped_gemm wgrad E={e} {da}x{db}")
   return out
 

@@ -119,10 +119,16 @@ class _ExchangePlan:
   of source 0, 1, ... in order.  So rows arrive grouped for the grouped GEMMs, whatever rank they
   came from, and no expert ids travel."""
 
+
   def __init__(self, C, me: int, ep: int, el: int, device):
     E = ep * el
     tot = [[sum(int(C[s][r * el + j]) for s in range(ep)) for j in range(el)] for r in range(ep)]
-    offpad = [_prefix([(v + 127) // 128 * 128 for v in tot[r]]) for r in range(ep)]
+    # 256-row segments (CTA-pair GEMM tiles) when experts see about a thousand rows or more; the
+    # choice is made from the whole matrix, so every rank pads every owner's layout the same way
+    total = sum(sum(row) for row in tot)
+    al = 256 if total // E >= 1024 else 128
+    self.row_align = al
+    offpad = [_prefix([(v + al - 1) // al * al for v in tot[r]]) for r in range(ep)]
     send_off = [_prefix(C[s]) for s in range(ep)]
     # dispatch: one block per global expert, in send order
     start = send_off[me]
@@ -247,7 +253,7 @@ class ExpertParallelMLP:
     every rank lands on one rank)."""
     key = (t, k, dim)
     if key not in self._push:
-      self._push[key] = (PushAllToAll(self.group, self.ep * t * k + self.local_experts * 128, dim, device),
+      self._push[key] = (PushAllToAll(self.group, self.ep * t * k + self.local_experts * 256, dim, device),
                          PushAllToAll(self.group, t * k, dim, device))
     return self._push[key]
 
