@@ -619,8 +619,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + (long long)row * p.ldc + col;
             const __nv_bfloat16* R = nullptr;
             if (p.epi == TPB_EPI_BF16_ACC) R = C;
-            if (p.epi == TPB_EPI_BF16_RES)
+            if (p.epi == TPB_EPI_BF16_RES || (p.epi == TPB_EPI_AR_BF16 && p.aux != nullptr))
               R = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + col;
+            const bool all_reduce = p.epi == TPB_EPI_AR_BF16;   // C is a multicast address: add into every rank's copy
             if (full_chunk) {
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
@@ -633,10 +634,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                   f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
                   f[4] += cc.x; f[5] += cc.y; f[6] += d.x; f[7] += d.y;
                 }
-                *reinterpret_cast<uint4*>(C + 8 * v) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]),
-                                                                  pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+                const uint4 o = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]),
+                                           pack_bf16(f[6], f[7]));
+                if (all_reduce)
+                  asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(C + 8 * v),
+                               "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
+                               : "memory");
+                else
+                  *reinterpret_cast<uint4*>(C + 8 * v) = o;
               }
-            } else {
+            } else if (!all_reduce) {             // the all-reduce form requires N % 32 == 0 (checked on the host)
               for (int j = 0; j < 32 && col + j < p.N; ++j) {
                 float o = __uint_as_float(r[j]) * p.alpha;
                 if (R) o += __bfloat162float(R[j]);
@@ -800,6 +807,7 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
     if (g.ldb != g.K || (g.ag_shard_elems % 8) || p.ag_copiers < 1 || p.ag_copiers >= sm_count()) return -2;
     if (p.ag_push && (g.ag_local < 0 || g.ag_local >= g.ag_world)) return -2;
   }
+  if (g.epi == TPB_EPI_AR_BF16 && ((g.N % 32) || (g.ldc % 8) || g.mode != 0 || g.ag_world > 0)) return -2;
   if (g.epi == TPB_EPI_RS_BF16) {
     if (g.rs_world < 1 || g.rs_world > 8 || (g.N % 8) || (g.ldc % 8) || (g.rs_shard_elems % 8) || (g.rs_c_offset % 8))
       return -2;

@@ -17,6 +17,8 @@ enum {
   TPB_EPI_BF16_RES = 4,  // C(bf16) = aux + alpha * acc   (residual add)
   TPB_EPI_SWIGLU = 5,    // B = [gate; up] rows, C[M, N/2] = silu(g) * u, optional c2[M, N] = [g | u]
   TPB_EPI_RS_BF16 = 6,   // reduce-scatter: red.add alpha * acc into the owner's bf16 shard over P2P
+  TPB_EPI_AR_BF16 = 7,   // all-reduce: C is the NVSwitch multicast address of a zeroed symmetric buffer;
+                         // multimem.red adds alpha * acc (+ aux, if given) into every rank's copy
 };
 
 // Status block: {code, site, block, thread}; code 0 = no kernel ever timed out.

@@ -103,6 +103,29 @@ def _worker(rank, world, port, results):
       mine = flat[rank * shard2:(rank + 1) * shard2]
       err = ((gs.local.float() - mine).norm() / (mine.norm() + 1e-9)).item()
       assert err < 2e-2, f"gemm_rs rel err {err}"
+    # ---- tensor-parallel all-reduce inside the GEMM epilogue (multimem.red through the multicast mapping)
+    ar = fc.AllReduceGemm(dist.group.WORLD, dev)
+    Ma, Na, Ka = 640, 256, 512
+    torch.manual_seed(7)
+    res_ar = torch.randn(Ma, Na, device=dev).to(torch.bfloat16)          # the same residual on every rank
+    torch.manual_seed(700 + rank)
+    a_ar = torch.randn(Ma, Ka, device=dev).to(torch.bfloat16)
+    w_ar = (torch.randn(Na, Ka, device=dev) * 0.05).to(torch.bfloat16)
+    wt_ar = (torch.randn(Ka, Na, device=dev) * 0.05).to(torch.bfloat16)   # [K, N] storage (input-gradient layout)
+    results[f"tp_multicast_{rank}"] = bool(ar.usable(Ma, Na, Ka))
+    if ar.usable(Ma, Na, Ka):
+      for it in range(2):                          # the buffer is zeroed and reused
+        y = ar.gemm_allreduce(a_ar, w_ar, res_ar)
+        want = a_ar.float() @ w_ar.float().t()
+        dist.all_reduce(want)
+        want += res_ar.float()
+        err = ((y.float() - want).norm() / want.norm()).item()
+        assert err < 1e-2, f"gemm_allreduce rel err {err}"
+        y2 = ar.gemm_allreduce(a_ar, wt_ar, None, b_mn=True)
+        want2 = a_ar.float() @ wt_ar.float()
+        dist.all_reduce(want2)
+        err2 = ((y2.float() - want2).norm() / want2.norm()).item()
+        assert err2 < 1e-2, f"gemm_allreduce (transposed weight) rel err {err2}"
     # ---- context-parallel attention with the K/V exchange fused into the forward kernel
     from torchprime_b200.dist.mesh import Mesh
     from torchprime_b200.parallel.cp import ContextParallelAttention
@@ -181,4 +204,5 @@ def test_ag_gemm_and_gemm_rs_two_gpus(cuda_lib):
   results = mgr.dict()
   mp.spawn(_worker, args=(world, 29641, results), nprocs=world, join=True)
   assert all(results.get(r) == "ok" for r in range(world)), dict(results)
-  print("multicast push used:", [results.get(f"multicast_{r}") for r in range(world)])
+  print("multicast push used:", [results.get(f"multicast_{r}") for r in range(world)],
+        "all-reduce in GEMM used:", [results.get(f"tp_multicast_{r}") for r in range(world)])

@@ -52,16 +52,35 @@ class LlamaMLP(nn.Module):
     self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
     assert config.get("hidden_act", "silu") == "silu", "only SiLU-gated MLPs are implemented"
     self.tp_group = None   # set by the engine when the tensor axis is > 1 (gate/up column-, down row-parallel)
+    self.tp_reducer = None  # ops.fused_collective.AllReduceGemm, set by the engine with fused collectives on
 
   def forward(self, x, residual=None):
     with trace_scope("LlamaMLP"):
       if self.tp_group is not None:
+        r = _fused_reducer(self, x, self.down_proj.weight.shape[0], self.down_proj.weight.shape[1],
+                           2 * self.gate_proj.weight.shape[0])
+        if r is not None:      # both all-reduces of the block happen inside GEMM epilogues
+          act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight, tp_reduce_grad=r)
+          return ops.linear(act, self.down_proj.weight, residual=residual, tp_reduce=r)
         x = copy_to_tp(x, self.tp_group)
         act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight)
         y = reduce_from_tp(ops.linear(act, self.down_proj.weight), self.tp_group)
         return y if residual is None else y + residual
       act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight)
       return ops.linear(act, self.down_proj.weight, residual=residual)
+
+
+def _fused_reducer(module, x, n_out: int, k_in: int, n_col: int):
+  """The module's all-reduce-in-GEMM object if it can take this block: hidden size ``n_out`` out of
+  a row-parallel weight with ``k_in`` local inputs, and the input gradient of a column-parallel
+  weight with ``n_col`` local outputs.  The answer is the same on every rank of the tensor group."""
+  r = getattr(module, "tp_reducer", None)
+  if r is None or not x.is_cuda or x.dtype != torch.bfloat16 or not ops.use_kernels(x):
+    return None
+  rows = x.numel() // x.shape[-1]
+  if r.usable(rows, n_out, k_in) and r.usable(rows, x.shape[-1], n_col):
+    return r
+  return None
 
 
 class LlamaAttention(nn.Module):
@@ -80,6 +99,7 @@ class LlamaAttention(nn.Module):
     self.o_proj = nn.Linear(self.num_heads * self.head_dim, self.hidden_size, bias=bias)
     self.attention_kernel = config.get("attention_kernel", None)
     self.tp_group = None   # set by the engine: q/k/v column-parallel (heads split), o row-parallel
+    self.tp_reducer = None  # ops.fused_collective.AllReduceGemm, set by the engine with fused collectives on
 
   def forward(self, x, rope_cos, rope_sin, residual=None, position_ids=None, segment_ids=None, cp=None):
     with trace_scope("LlamaAttention"):
@@ -87,12 +107,17 @@ class LlamaAttention(nn.Module):
       d = self.head_dim
       # local head counts follow the (possibly tensor-parallel sliced) weights
       hq, hkv = self.q_proj.weight.shape[0] // d, self.k_proj.weight.shape[0] // d
-      if self.tp_group is not None:
-        x = copy_to_tp(x, self.tp_group)
       bias = None
       if self.q_proj.bias is not None:
         bias = torch.cat([self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
-      qkv = ops.linear(x, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], bias=bias)
+      r = None
+      if self.tp_group is not None:
+        if bias is None and self.o_proj.bias is None:
+          r = _fused_reducer(self, x, self.o_proj.weight.shape[0], self.o_proj.weight.shape[1], (hq + 2 * hkv) * d)
+        if r is None:
+          x = copy_to_tp(x, self.tp_group)
+      qkv = ops.linear(x, [self.q_proj.weight, self.k_proj.weight, self.v_proj.weight], bias=bias,
+                       tp_reduce_grad=r)
       qkv = ops.rope_inplace(qkv, rope_cos, rope_sin, hq + hkv, d, s, pos=position_ids)
       if cp is None and x.is_cuda:
         # one autograd input, one gradient (see ops.attention_qkv)
@@ -108,6 +133,8 @@ class LlamaAttention(nn.Module):
         else:
           o = ops.attention(q, k, v, causal=True, q_segment_ids=segment_ids)
       o = o.reshape(b, s, hq * d)
+      if r is not None:
+        return ops.linear(o, self.o_proj.weight, residual=residual, tp_reduce=r)
       if self.tp_group is not None:
         out = reduce_from_tp(ops.linear(o, self.o_proj.weight), self.tp_group)
         if self.o_proj.bias is not None:

@@ -18,6 +18,7 @@ _LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file_
 _lib = None
 
 EPI_BF16, EPI_F32, EPI_F32_ACC, EPI_BF16_ACC, EPI_BF16_RES, EPI_SWIGLU = range(6)
+EPI_RS_BF16, EPI_AR_BF16 = 6, 7     # reduce-scatter / all-reduce epilogues of the fused collective GEMMs
 
 _STATUS_NAMES = {
   1: "consumer timed out waiting for a TMA stage",

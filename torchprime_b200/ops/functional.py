@@ -102,10 +102,20 @@ def _wgrad_into(sink, weights, dy2, x2):
 # --------------------------------------------------------------------------- linear
 class _LinearFn(torch.autograd.Function):
   @staticmethod
-  def forward(ctx, x, residual, n_w, *weights):
+  def forward(ctx, x, residual, n_w, reducers, *weights):
     from . import kernels as k
     w = _fused_view(list(weights))
     x2 = x.reshape(-1, x.shape[-1])
+    out_reduce, ctx.grad_reduce = reducers if reducers is not None else (None, None)
+    if out_reduce is not None:
+      # row-parallel linear of tensor parallelism: the all-reduce over the tensor group happens in
+      # the GEMM epilogue (rank 0 also adds the residual)
+      res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
+      y = out_reduce.gemm_allreduce(x2, w, res2).view(*x.shape[:-1], w.shape[0])
+      ctx.save_for_backward(x2, *weights)
+      ctx.has_res = residual is not None
+      ctx.x_shape = x.shape
+      return y
     # the result is allocated in its final shape (not returned as a view) so that later
     # in-place operators such as RoPE may modify it
     y = torch.empty(*x.shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
@@ -129,9 +139,12 @@ class _LinearFn(torch.autograd.Function):
       dy2 = dy2.contiguous()
     dx = None
     if ctx.needs_input_grad[0]:
-      dx = k.gemm(dy2, w, b_mn=True).view(ctx.x_shape)
+      if ctx.grad_reduce is not None:      # column-parallel linear: the input gradient is summed over the group
+        dx = ctx.grad_reduce.gemm_allreduce(dy2, w, None, b_mn=True).view(ctx.x_shape)
+      else:
+        dx = k.gemm(dy2, w, b_mn=True).view(ctx.x_shape)
     wgrads = [None] * len(weights)
-    if any(ctx.needs_input_grad[3:]):
+    if any(ctx.needs_input_grad[4:]):
       sink = _grad_sink(weights)
       if sink is not None:
         _wgrad_into(sink, weights, dy2, x2)
@@ -142,7 +155,7 @@ class _LinearFn(torch.autograd.Function):
           wgrads.append(dw[r:r + wt.shape[0]])
           r += wt.shape[0]
     dres = dy if ctx.has_res else None
-    return (dx, dres, None, *wgrads)
+    return (dx, dres, None, None, *wgrads)
 
 
 def _gemm_friendly(x, ws) -> bool:
@@ -153,14 +166,35 @@ def _gemm_friendly(x, ws) -> bool:
           and x.shape[-1] == k and x.reshape(-1, k).stride(-1) == 1 and x.reshape(-1, k).stride(0) % 8 == 0)
 
 
-def linear(x, weights, bias=None, residual=None):
+def _reducer_ok(reducer, x, n_out, k_in) -> bool:
+  return reducer is not None and reducer.usable(x.numel() // x.shape[-1], n_out, k_in)
+
+
+def linear(x, weights, bias=None, residual=None, tp_reduce=None, tp_reduce_grad=None):
   """y = x @ cat(weights)^T (+ bias) (+ residual).  ``weights`` is one tensor or a list of
   row-adjacent tensors (q/k/v or gate/up laid out back to back) which then run as
-  one GEMM."""
+  one GEMM.
+
+  Tensor parallelism with the all-reduce inside the GEMM (``ops.fused_collective.AllReduceGemm``):
+  ``tp_reduce`` sums the OUTPUT over the tensor group (row-parallel weight; the caller must not
+  reduce again), ``tp_reduce_grad`` sums the INPUT GRADIENT (column-parallel weight).  Callers ask
+  ``reducer.usable(rows, n, k)`` first; a request that cannot be honoured raises."""
   ws = list(weights) if isinstance(weights, (list, tuple)) else [weights]
   if (use_kernels(x, *ws) and bias is None and (len(ws) == 1 or _adjacent(ws)) and _gemm_friendly(x, ws)
       and (residual is None or residual.dtype == x.dtype)):
-    return _LinearFn.apply(x, residual, len(ws), *ws)
+    n_out, k_in = sum(w.shape[0] for w in ws), ws[0].shape[1]
+    reducers = None
+    if tp_reduce is not None or tp_reduce_grad is not None:
+      out_r = tp_reduce if _reducer_ok(tp_reduce, x, n_out, k_in) else None
+      grad_r = tp_reduce_grad if _reducer_ok(tp_reduce_grad, x, k_in, n_out) else None
+      if tp_reduce is not None and out_r is None:
+        raise RuntimeError("fused tensor-parallel all-reduce requested but not available for this shape")
+      if tp_reduce_grad is not None and grad_r is None:
+        raise RuntimeError("fused tensor-parallel gradient all-reduce requested but not available for this shape")
+      reducers = (out_r, grad_r)
+    return _LinearFn.apply(x, residual, len(ws), reducers, *ws)
+  if tp_reduce is not None or tp_reduce_grad is not None:
+    raise RuntimeError("fused tensor-parallel all-reduce requested on a path without kernels")
   if len(ws) == 1:
     y = F.linear(x, ws[0], bias)
   else:
@@ -172,8 +206,9 @@ def linear(x, weights, bias=None, residual=None):
 
 class _LinearSwigluFn(torch.autograd.Function):
   @staticmethod
-  def forward(ctx, x, w_gate, w_up):
+  def forward(ctx, x, w_gate, w_up, grad_reduce=None):
     from . import kernels as k
+    ctx.grad_reduce = grad_reduce
     w = _fused_view([w_gate, w_up])
     x2 = x.reshape(-1, x.shape[-1])
     need_grad = any(ctx.needs_input_grad)
@@ -191,7 +226,12 @@ class _LinearSwigluFn(torch.autograd.Function):
     x2, gu, w_gate, w_up = ctx.saved_tensors
     w = _fused_view([w_gate, w_up])
     dgu = k.swiglu_bwd(dact.reshape(-1, dact.shape[-1]).contiguous(), gu)
-    dx = k.gemm(dgu, w, b_mn=True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+    dx = None
+    if ctx.needs_input_grad[0]:
+      if ctx.grad_reduce is not None:      # column-parallel gate/up: the input gradient is summed over the group
+        dx = ctx.grad_reduce.gemm_allreduce(dgu, w, None, b_mn=True).view(ctx.x_shape)
+      else:
+        dx = k.gemm(dgu, w, b_mn=True).view(ctx.x_shape)
     grads = [None, None]
     if ctx.needs_input_grad[1] or ctx.needs_input_grad[2]:
       sink = _grad_sink([w_gate, w_up])
@@ -200,14 +240,18 @@ class _LinearSwigluFn(torch.autograd.Function):
       else:
         dw = k.gemm(dgu, x2, a_mn=True, b_mn=True)
         grads = [dw[: w_gate.shape[0]], dw[w_gate.shape[0]:]]
-    return (dx, *grads)
+    return (dx, *grads, None)
 
 
-def linear_swiglu(x, w_gate, w_up):
+def linear_swiglu(x, w_gate, w_up, tp_reduce_grad=None):
   """silu(x @ w_gate^T) * (x @ w_up^T) as one GEMM with a fused epilogue."""
   if (use_kernels(x, w_gate, w_up) and _adjacent([w_gate, w_up]) and w_gate.shape[0] % 8 == 0
       and _gemm_friendly(x, [w_gate, w_up])):
-    return _LinearSwigluFn.apply(x, w_gate, w_up)
+    if tp_reduce_grad is not None and not _reducer_ok(tp_reduce_grad, x, x.shape[-1], 2 * w_gate.shape[0]):
+      raise RuntimeError("fused tensor-parallel gradient all-reduce requested but not available for this shape")
+    return _LinearSwigluFn.apply(x, w_gate, w_up, tp_reduce_grad)
+  if tp_reduce_grad is not None:
+    raise RuntimeError("fused tensor-parallel gradient all-reduce requested on a path without kernels")
   return F.silu(F.linear(x, w_gate)) * F.linear(x, w_up)
 
 

@@ -117,3 +117,60 @@ def gemm_rs(a, b, *, a_mn, b_mn, m, n, ldc, grad_shards, shard_elems: int, c_off
                               float(alpha), table, grad_shards.world, shard_elems, c_offset, grad_shards.rank,
                               stream_ptr())
   check(rc, f"gemm_rs M={m} N={n} K={k} world={grad_shards.world}")
+
+
+class AllReduceGemm:
+  """``sum over the ranks of a group of (A_r @ B_r^T) (+ residual)`` with the all-reduce inside the GEMM
+  epilogue: the output lives in a symmetric buffer bound to an NVSwitch multicast object, every rank's
+  epilogue adds its tile into ALL ranks' copies with one ``multimem.red`` per 16 bytes, and when the
+  kernels have finished every rank holds the sum.  This is the row-parallel linear of tensor
+  parallelism (and, in the backward pass, the input gradient of the column-parallel one) without a
+  separate all-reduce pass.
+
+  Per call: zero the local copy, device barrier (all copies are zero), GEMM, device barrier (all
+  contributions have landed), copy the result out of the shared buffer.  The residual, when given,
+  is added by rank 0 only.  ``available`` is False where the platform offers no multicast mapping;
+  callers then use the NCCL all-reduce."""
+
+  def __init__(self, group, device):
+    import torch.distributed as dist
+    self.group = group
+    self.device = device
+    self.world = dist.get_world_size(group)
+    self.rank = dist.get_rank(group)
+    self._bufs = {}
+    self.available = True
+    self.calls = 0
+
+  def _buffer(self, m: int, n: int):
+    from ..dist.symm import SymmetricBuffer
+    key = (m, n)
+    if key not in self._bufs:
+      sb = SymmetricBuffer(m * n, torch.bfloat16, self.device, group=self.group, backend="torch")
+      if not sb.multicast_ptr:
+        self.available = False
+      self._bufs[key] = sb
+    return self._bufs[key]
+
+  def usable(self, m: int, n: int, k: int) -> bool:
+    if not self.available or n % 32 or k % 8:
+      return False
+    self._buffer(m, n)                      # collective on first use of a shape: every rank takes this path
+    return self.available
+
+  def gemm_allreduce(self, a2d, b, residual2d=None, b_mn: bool = False):
+    """a2d [M, K]; b [N, K] (or [K, N] with ``b_mn``); returns the reduced [M, N] bf16 tensor."""
+    m, kdim = a2d.shape
+    n = b.shape[1] if b_mn else b.shape[0]
+    sb = self._buffer(m, n)
+    assert sb.multicast_ptr and a2d.stride(1) == 1 and b.stride(1) == 1
+    sb.local.zero_()
+    sb.barrier()
+    aux = residual2d if (residual2d is not None and self.rank == 0) else None
+    rc = lib().tpb_gemm_bf16(ptr(a2d), ptr(b), c_void_p(sb.multicast_ptr), m, n, kdim, a2d.stride(0), b.stride(0), n,
+                             0, int(b_mn), _lib.EPI_AR_BF16, 1.0, ptr(aux), aux.stride(0) if aux is not None else 0,
+                             None, 0, 0, stream_ptr())
+    check(rc, f"gemm_allreduce M={m} N={n} K={kdim} world={self.world}")
+    sb.barrier()
+    self.calls += 1
+    return sb.local.view(m, n).clone()

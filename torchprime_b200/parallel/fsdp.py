@@ -26,6 +26,7 @@ from __future__ import annotations
 
 import logging
 import math
+import os
 import zlib
 from dataclasses import dataclass, field
 
@@ -325,9 +326,17 @@ class FSDPEngine:
       return
     if self.tp > 1:
       grp = self.mesh.group("tensor")
+      reducer = None
+      if self.fused_collectives and self.is_cuda and os.environ.get("TPB_TP_FUSED", "1") != "0":
+        # the all-reduces of tensor parallelism run inside GEMM epilogues (multimem.red through the
+        # NVSwitch multicast mapping of the output); modules fall back to NCCL where it does not apply
+        from ..ops.fused_collective import AllReduceGemm
+        reducer = AllReduceGemm(grp, self.device)
       for mod in self.model.modules():
         if hasattr(mod, "tp_group"):
           mod.tp_group = grp
+          if hasattr(mod, "tp_reducer"):
+            mod.tp_reducer = reducer
     if self.ep > 1:
       from .ep import ExpertParallelMLP
       for mod in self.model.modules():
