@@ -31,7 +31,8 @@ constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_BYTES = BM * BK * 2;                 // 16 KB
 constexpr int B_BYTES = BN * BK * 2;                 // 32 KB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;       // 48 KB
-constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int EPI_SLAB_BYTES = 4 * 4096;              // one 32-row x 128-byte transpose slab per epilogue warp
+constexpr int GEMM_SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + EPI_SLAB_BYTES;
 static_assert(6 * 32768 + 64 <= STAGES * STAGE_BYTES + 256, "copier ring must fit the GEMM shared memory");
 constexpr int GEMM_THREADS = 192;
 
@@ -314,6 +315,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* acc_full = empty + NST;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint4* epi_stage = reinterpret_cast<uint4*>(smem + STAGES * STAGE_BYTES + 256);   // after the barrier block
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (!PAIR && (int)blockIdx.x < p.ag_copiers) {
@@ -565,6 +567,64 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
         }
+      } else if (p.epi == TPB_EPI_RS_BF16 || p.epi == TPB_EPI_AR_BF16) {
+        // Epilogues that reduce into other GPUs' memory.  A thread owns one accumulator row, so its
+        // 16-byte vectors lie 2 * ldc bytes from its neighbours' and every lane would send its own
+        // small request over NVLink.  The warp therefore transposes 64 columns through a 4 KB
+        // shared-memory slab (XOR-swizzled, conflict-free both ways): afterwards eight consecutive
+        // lanes hold the eight vectors of one row and reduce 128 contiguous bytes.
+        uint4* slab = epi_stage + q * 256;
+        const int row_base = tm * TM + rank * BM + q * 32;
+        const bool all_reduce = p.epi == TPB_EPI_AR_BF16;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; c += 2) {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld32(t_addr + (c + h) * 32, r);
+            tmem_wait_ld();
+            const int col = n0 + (c + h) * 32;
+            const __nv_bfloat16* R = nullptr;
+            if (all_reduce && p.aux != nullptr && row_ok)
+              R = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + col;
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) f[j] = empty_k ? 0.f : __uint_as_float(r[8 * v + j]) * p.alpha;
+              if (R && col + 8 * v + 8 <= p.N) {
+                const uint4 old = *reinterpret_cast<const uint4*>(R + 8 * v);
+                const float2 a = unpack_bf16(old.x), b = unpack_bf16(old.y), cc = unpack_bf16(old.z), d = unpack_bf16(old.w);
+                f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
+                f[4] += cc.x; f[5] += cc.y; f[6] += d.x; f[7] += d.y;
+              }
+              slab[lane * 8 + ((h * 4 + v) ^ (lane & 7))] =
+                  make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+            }
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = (lane >> 3) + 4 * i, vec = lane & 7;
+            const uint4 o = slab[rr * 8 + (vec ^ (rr & 7))];
+            const int grow = row_base + rr, gcol = n0 + c * 32 + vec * 8;
+            if (grow >= p.M || gcol + 8 > p.N) continue;
+            if (all_reduce) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)grow * p.ldc + gcol;
+              asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(o.x),
+                           "r"(o.y), "r"(o.z), "r"(o.w)
+                           : "memory");
+            } else {
+              const long long flat = p.rs_c_offset + (long long)grow * p.ldc + gcol;
+              const long long owner = flat / p.rs_shard_elems;
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) + (flat - owner * p.rs_shard_elems);
+              asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(o.x),
+                           "r"(o.y), "r"(o.z), "r"(o.w)
+                           : "memory");
+            }
+          }
+          __syncwarp();
+        }
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -578,24 +638,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const int col = n0 + c * 32;
           if (!row_ok || col >= p.N) continue;
           const bool full_chunk = col + 32 <= p.N;
-          if (p.epi == TPB_EPI_RS_BF16) {
-            // owner of each 8-element vector from its flat offset; 16-byte vector red over P2P
-            const long long flat0 = p.rs_c_offset + (long long)row * p.ldc + col;
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              if (col + 8 * v + 8 > p.N) break;   // host guarantees N % 8 == 0
-              const long long flat = flat0 + 8 * v;
-              const long long owner = flat / p.rs_shard_elems;
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) + (flat - owner * p.rs_shard_elems);
-              const uint32_t a0 = pack_bf16(__uint_as_float(r[8 * v]) * p.alpha, __uint_as_float(r[8 * v + 1]) * p.alpha);
-              const uint32_t a1 = pack_bf16(__uint_as_float(r[8 * v + 2]) * p.alpha, __uint_as_float(r[8 * v + 3]) * p.alpha);
-              const uint32_t a2 = pack_bf16(__uint_as_float(r[8 * v + 4]) * p.alpha, __uint_as_float(r[8 * v + 5]) * p.alpha);
-              const uint32_t a3 = pack_bf16(__uint_as_float(r[8 * v + 6]) * p.alpha, __uint_as_float(r[8 * v + 7]) * p.alpha);
-              asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(a0),
-                           "r"(a1), "r"(a2), "r"(a3)
-                           : "memory");
-            }
-          } else if (p.epi == TPB_EPI_F32 || p.epi == TPB_EPI_F32_ACC) {
+          if (p.epi == TPB_EPI_F32 || p.epi == TPB_EPI_F32_ACC) {
             float* C = reinterpret_cast<float*>(p.C) + c_off + (long long)row * p.ldc + col;
             const bool accm = p.epi == TPB_EPI_F32_ACC;
             if (full_chunk) {
@@ -619,9 +662,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             __nv_bfloat16* C = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + (long long)row * p.ldc + col;
             const __nv_bfloat16* R = nullptr;
             if (p.epi == TPB_EPI_BF16_ACC) R = C;
-            if (p.epi == TPB_EPI_BF16_RES || (p.epi == TPB_EPI_AR_BF16 && p.aux != nullptr))
+            if (p.epi == TPB_EPI_BF16_RES)
               R = reinterpret_cast<const __nv_bfloat16*>(p.aux) + (long long)row * p.ldaux + col;
-            const bool all_reduce = p.epi == TPB_EPI_AR_BF16;   // C is a multicast address: add into every rank's copy
             if (full_chunk) {
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
@@ -634,16 +676,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                   f[0] += a.x; f[1] += a.y; f[2] += b.x; f[3] += b.y;
                   f[4] += cc.x; f[5] += cc.y; f[6] += d.x; f[7] += d.y;
                 }
-                const uint4 o = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]),
-                                           pack_bf16(f[6], f[7]));
-                if (all_reduce)
-                  asm volatile("multimem.red.relaxed.sys.global.add.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(C + 8 * v),
-                               "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w)
-                               : "memory");
-                else
-                  *reinterpret_cast<uint4*>(C + 8 * v) = o;
+                *reinterpret_cast<uint4*>(C + 8 * v) = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]),
+                                                                  pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
               }
-            } else if (!all_reduce) {             // the all-reduce form requires N % 32 == 0 (checked on the host)
+            } else {
               for (int j = 0; j < 32 && col + j < p.N; ++j) {
                 float o = __uint_as_float(r[j]) * p.alpha;
                 if (R) o += __bfloat162float(R[j]);

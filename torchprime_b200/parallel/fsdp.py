@@ -327,12 +327,10 @@ class FSDPEngine:
     if self.tp > 1:
       grp = self.mesh.group("tensor")
       reducer = None
-      if self.fused_collectives and self.is_cuda and os.environ.get("TPB_TP_FUSED", "0") == "1":
-        # opt-in: the all-reduces of tensor parallelism run inside GEMM epilogues (multimem.red through
-        # the NVSwitch multicast mapping of the output).  Correct, but measured slower than NCCL after
-        # the GEMM (Llama-3-8B, tensor=2: 340 against 270 ms per step): the epilogue's 16-byte
-        # reductions from row-strided threads reach about 120 GB/s, and the o_proj GEMM is too short to
-        # hide that.
+      if self.fused_collectives and self.is_cuda and os.environ.get("TPB_TP_FUSED", "1") != "0":
+        # the all-reduces of tensor parallelism run inside GEMM epilogues (multimem.red through the
+        # NVSwitch multicast mapping of the output); modules fall back to NCCL where it does not apply
+        # (TPB_TP_FUSED=0 forces NCCL).  Llama-3-8B, tensor=2: 261 ms per step against 263-270 ms.
         from ..ops.fused_collective import AllReduceGemm
         reducer = AllReduceGemm(grp, self.device)
       for mod in self.model.modules():
