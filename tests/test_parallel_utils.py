@@ -212,3 +212,22 @@ def test_expert_exchange_plan_groups_rows_by_expert_and_returns_them(scale, alig
     push(rows, plans[r].ret, plans[r].ret_blocks, back)
   for s in range(ep):
     assert [back[s][i] for i in range(len(send[s]))] == send[s]
+
+
+def test_fused_tensor_parallel_request_needs_the_kernel_path():
+  """``linear(..., tp_reduce=...)`` promises that the output is already summed over the tensor group;
+  on a path without kernels (CPU, fp32) that promise cannot be kept, so it raises instead of silently
+  returning a partial sum."""
+  import torch
+  from torchprime_b200.ops import functional as ops
+
+  class Reducer:
+    def usable(self, m, n, k):
+      return True
+
+  x, w = torch.randn(4, 8), torch.randn(16, 8)
+  with pytest.raises(RuntimeError):
+    ops.linear(x, w, tp_reduce=Reducer())
+  with pytest.raises(RuntimeError):
+    ops.linear_swiglu(x, w, w.clone(), tp_reduce_grad=Reducer())
+  assert ops.linear(x, w).shape == (4, 16)
