@@ -115,10 +115,9 @@ class _ExchangePlan:
   ``C[s][e]`` (pairs of rank s routed to global expert e), the same on every rank.
 
   Send layout (on every rank): its pairs sorted by expert, compact.  Receive layout on the owner:
-  expert-major, every expert's segment padded to a multiple of 128 rows, inside a segment the rows
-  of source 0, 1, ... in order.  So rows arrive grouped for the grouped GEMMs, whatever rank they
-  came from, and no expert ids travel."""
-
+  expert-major, every expert's segment padded to a multiple of ``row_align`` (128 or 256) rows, inside
+  a segment the rows of source 0, 1, ... in order.  So rows arrive grouped for the grouped GEMMs,
+  whatever rank they came from, and no expert ids travel."""
 
   def __init__(self, C, me: int, ep: int, el: int, device):
     E = ep * el
