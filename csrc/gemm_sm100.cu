@@ -92,6 +92,8 @@ struct GemmParams {
   void* rs_dst[8];              // gradient shard base of every rank (symmetric memory), bf16
   long long rs_shard_elems;
   long long rs_c_offset;        // element offset of C inside the sharded flat buffer
+  int rs_store;                 // 1: plain 16-byte stores instead of red.add (each source writes its own staging
+                                // slot at the owner, which adds the slots in rank order afterwards)
 };
 
 struct TileInfo {
@@ -159,7 +161,7 @@ __device__ __forceinline__ bool ag_wait_range(const GemmParams& p, long long lo,
     int spins = 0;
     while (true) {
       asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-      if (v == p.ag_epoch) break;
+      if ((int)(v - p.ag_epoch) >= 0) break;   // epochs only grow
       if (++spins == 64) {
         spins = 0;
         if (t0 == 0) t0 = clock64();
@@ -375,10 +377,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int m0 = ti.tm * TM + rank * BM, n0 = ti.tn * tile_n_out;
         const int ez = p.mode == 1 ? ti.e : 0;
         if (p.ag_world > 0) {
-          // B rows [n0, n0 + BN) of a dense [N, ldb = K] matrix occupy one flat range
+          // B rows [n0, n0 + BN) of a dense [N, ldb = K] matrix occupy one flat range; with the SwiGLU
+          // epilogue a tile takes tile_n_out "gate" rows and the same rows of the "up" half
+          const int r1 = swiglu ? min(n_logical, n0 + tile_n_out) : min(p.N, n0 + BN);
           const long long lo = p.ag_b_offset + (long long)n0 * p.K;
-          const long long hi = p.ag_b_offset + (long long)min(p.N, n0 + BN) * p.K - 1;
+          const long long hi = p.ag_b_offset + (long long)r1 * p.K - 1;
           if (!ag_wait_range(p, lo, hi)) { ok = false; break; }
+          if (swiglu) {
+            const long long lo2 = p.ag_b_offset + (long long)(p.b2_off + n0) * p.K;
+            const long long hi2 = p.ag_b_offset + (long long)(p.b2_off + r1) * p.K - 1;
+            if (!ag_wait_range(p, lo2, hi2)) { ok = false; break; }
+          }
         }
         for (int kb = ti.kb0; kb < ti.kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, p.status, kTimeoutStageFree, 1)) {
@@ -618,9 +627,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               const long long flat = p.rs_c_offset + (long long)grow * p.ldc + gcol;
               const long long owner = flat / p.rs_shard_elems;
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.rs_dst[owner]) + (flat - owner * p.rs_shard_elems);
-              asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(o.x),
-                           "r"(o.y), "r"(o.z), "r"(o.w)
-                           : "memory");
+              if (p.rs_store)
+                *reinterpret_cast<uint4*>(dst) = o;
+              else
+                asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(o.x),
+                             "r"(o.y), "r"(o.z), "r"(o.w)
+                             : "memory");
             }
           }
           __syncwarp();
@@ -775,6 +787,8 @@ struct GemmCall {
   void* const* ag_push_dst; unsigned* const* ag_push_flags; void* ag_push_mc;
   int rs_world; void* const* rs_dst; long long rs_shard_elems, rs_c_offset;
   int rs_rank;
+  int rs_store;
+  long long ag_chunk_elems;     // external gather (ag_copiers == 0): elements per flag
 };
 
 static int run_gemm(const GemmCall& g, cudaStream_t stream) {
@@ -829,18 +843,21 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.rs_world = g.rs_world; p.rs_shard_elems = g.rs_shard_elems; p.rs_c_offset = g.rs_c_offset;
   p.tile_rot = 0;
   p.te_stride = 1;
+  p.rs_store = g.rs_store;
+  if (g.ag_world > 0 && g.ag_copiers == 0) p.ag_chunk_elems = g.ag_chunk_elems;   // external gather: the caller's flags
   p.ag_push = (g.ag_world > 0 && g.ag_push_dst != nullptr && g.ag_push_flags != nullptr) ? 1 : 0;
   p.ag_push_mc = p.ag_push ? g.ag_push_mc : nullptr;
   if (p.ag_push) p.ag_chunk_elems = 131072;   // 256 KB per flag: a CTA streams a chunk with one fence at its end
   for (int i = 0; i < 8; ++i) {
     p.ag_push_dst[i] = (p.ag_push && i < g.ag_world) ? g.ag_push_dst[i] : nullptr;
     p.ag_push_flags[i] = (p.ag_push && i < g.ag_world) ? g.ag_push_flags[i] : nullptr;
-    p.ag_src[i] = (g.ag_world > 0 && i < g.ag_world) ? g.ag_src[i] : nullptr;
+    p.ag_src[i] = (g.ag_world > 0 && g.ag_src != nullptr && i < g.ag_world) ? g.ag_src[i] : nullptr;
     p.rs_dst[i] = (g.rs_world > 0 && i < g.rs_world) ? g.rs_dst[i] : nullptr;
   }
   if (g.ag_world > 0) {
     if (g.ag_world > 8 || g.b_mn || g.mode != 0) return -2;
-    if (g.ldb != g.K || (g.ag_shard_elems % 8) || p.ag_copiers < 1 || p.ag_copiers >= sm_count()) return -2;
+    if (g.ldb != g.K || (g.ag_shard_elems % 8) || p.ag_copiers < 0 || p.ag_copiers >= sm_count()) return -2;
+    if (p.ag_copiers == 0 && (p.ag_chunk_elems <= 0 || p.ag_flags == nullptr || p.ag_push)) return -2;
     if (p.ag_push && (g.ag_local < 0 || g.ag_local >= g.ag_world)) return -2;
   }
   if (g.epi == TPB_EPI_AR_BF16 && ((g.N % 32) || (g.ldc % 8) || g.mode != 0 || g.ag_world > 0)) return -2;
@@ -856,7 +873,8 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   int cap = sm_count() - p.ag_copiers;
   if (g.max_ctas > 0 && g.max_ctas < cap) cap = g.max_ctas;
   const int grid = (tiles > cap ? cap : (int)tiles) + p.ag_copiers;
-  if (g.epi == TPB_EPI_RS_BF16 && g.rs_world > 1 && g.rs_rank > 0)
+  const bool rs_rotate = g.epi == TPB_EPI_RS_BF16 && g.rs_world > 1 && g.rs_rank > 0;
+  if (rs_rotate)
     p.tile_rot = (int)(tiles * g.rs_rank / g.rs_world);   // every rank starts in a different owner's part of C
   cudaError_t e;
   // CTA pairs for dense GEMMs with enough 256 x 256 tiles to fill the machine (TPB_GEMM_PAIR=0
@@ -883,9 +901,13 @@ static int run_gemm(const GemmCall& g, cudaStream_t stream) {
   // grouped modes: rows mode needs expert segments padded to whole 256-row tiles; the per-expert
   // K-range mode (weight gradients) has no such condition
   const bool pair_shape_ok = g.mode == 0 || g.mode == 2 || (g.mode == 1 && g.row_align > 0 && g.row_align % (2 * BM) == 0);
-  if (pair_mode != 0 && max_pairs > 0 && pair_shape_ok && g.ag_world == 0 && g.epi != TPB_EPI_RS_BF16 &&
+  // (the in-kernel copier CTAs of the fused all-gather and the red.add reduce-scatter were tuned on the
+  // single-CTA kernel and stay there; waiting on an external gather and the store-mode scatter run on pairs)
+  const bool pair_coll_ok = (g.ag_world == 0 || p.ag_copiers == 0) && (g.epi != TPB_EPI_RS_BF16 || g.rs_store);
+  if (pair_mode != 0 && max_pairs > 0 && pair_shape_ok && pair_coll_ok &&
       g.max_ctas == 0 && (pair_mode == 2 || pair_tiles >= max_pairs)) {
     p.te_stride = 2;
+    if (rs_rotate) p.tile_rot = (int)(pair_tiles * g.rs_rank / g.rs_world);
     const int pairs = pair_tiles > max_pairs ? max_pairs : (int)pair_tiles;
     const int m_tiles2 = (g.M + 2 * BM - 1) / (2 * BM);
     p.group_m = m_tiles2 < 8 ? m_tiles2 : 8;
@@ -983,5 +1005,45 @@ extern "C" int tpb_gemm_rs_bf16(const void* A, const void* B, int M, int N, int 
   g.mode = 0;
   g.rs_world = world; g.rs_dst = shard_ptrs; g.rs_shard_elems = shard_elems; g.rs_c_offset = c_offset;
   g.rs_rank = rank;
+  return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
+}
+
+// C = A * B^T (+ epilogue) where B is a dense row-major [N, K] matrix `b_offset` elements into a
+// gathered buffer that somebody else (the copy engines, see fsdp_comm.cu) is still filling: the
+// buffer is `world` shards of `shard_elems` elements, every `chunk_elems` elements of a shard have
+// one flag (flags[owner * ceil(shard_elems / chunk_elems) + chunk], local memory) that holds the
+// epoch of the newest gather that has landed there.  The TMA producer waits (bounded) until the flags
+// under its B tile have reached `epoch` before it loads the tile.
+extern "C" int tpb_gemm_ag_wait_bf16(const void* A, void* C, int M, int N, int K, long long lda, long long ldc,
+                                     int epi, const void* aux, long long ldaux, void* c2, long long ldc2,
+                                     const void* gathered, long long b_offset, int world, long long shard_elems,
+                                     long long chunk_elems, unsigned* flags, unsigned epoch, void* stream_) {
+  GemmCall g{};
+  g.A = A; g.B = reinterpret_cast<const __nv_bfloat16*>(gathered) + b_offset; g.B2 = nullptr; g.C = C;
+  g.M = M; g.N = N; g.K = K; g.E = 1;
+  g.lda = lda; g.ldb = K; g.b_expert_stride = 0; g.ldc = ldc;
+  g.a_mn = 0; g.b_mn = 0; g.epi = epi; g.alpha = 1.f;
+  g.aux = aux; g.ldaux = ldaux; g.c2 = c2; g.ldc2 = ldc2; g.max_ctas = 0; g.mode = 0;
+  g.ag_world = world; g.ag_copiers = 0; g.ag_src = nullptr; g.ag_dst = const_cast<void*>(gathered);
+  g.ag_shard_elems = shard_elems; g.ag_b_offset = b_offset; g.ag_flags = flags; g.ag_epoch = epoch;
+  g.ag_local = -1; g.ag_chunk_elems = chunk_elems;
+  return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
+}
+
+// tpb_gemm_rs_bf16 with plain stores: `slot_ptrs[o]` is THIS rank's staging slot inside owner o's memory
+// (shard_elems elements); the tile elements that owner o's shard covers are stored there, nothing is added
+// and nothing needs to be zero.  The owner reduces the slots of all sources afterwards (tpb_rs_reduce_bf16).
+extern "C" int tpb_gemm_rs_store_bf16(const void* A, const void* B, int M, int N, int K, long long lda,
+                                      long long ldb, long long ldc, int a_mn, int b_mn, float alpha,
+                                      void* const* slot_ptrs, int world, long long shard_elems, long long c_offset,
+                                      int rank, void* stream_) {
+  GemmCall g{};
+  g.A = A; g.B = B; g.B2 = nullptr; g.C = slot_ptrs[0];
+  g.M = M; g.N = N; g.K = K; g.E = 1;
+  g.lda = lda; g.ldb = ldb; g.b_expert_stride = 0; g.ldc = ldc;
+  g.a_mn = a_mn; g.b_mn = b_mn; g.epi = TPB_EPI_RS_BF16; g.alpha = alpha;
+  g.mode = 0;
+  g.rs_world = world; g.rs_dst = slot_ptrs; g.rs_shard_elems = shard_elems; g.rs_c_offset = c_offset;
+  g.rs_rank = rank; g.rs_store = 1;
   return run_gemm(g, reinterpret_cast<cudaStream_t>(stream_));
 }

@@ -108,6 +108,24 @@ int tpb_gemm_rs_bf16(const void* A, const void* B, int M, int N, int K, long lon
                      int a_mn, int b_mn, float alpha, void* const* shard_ptrs, int world, long long shard_elems,
                      long long c_offset, int rank, void* stream);
 
+// GEMM whose B operand sits in a gathered buffer that is still being filled by somebody else (copy
+// engines); the TMA producer waits on per-chunk flags.  GEMM whose epilogue stores every tile into this
+// rank's staging slot at the owner of that part of the flat gradient buffer.  See gemm_sm100.cu.
+int tpb_gemm_ag_wait_bf16(const void* A, void* C, int M, int N, int K, long long lda, long long ldc, int epi,
+                          const void* aux, long long ldaux, void* c2, long long ldc2, const void* gathered,
+                          long long b_offset, int world, long long shard_elems, long long chunk_elems,
+                          unsigned* flags, unsigned epoch, void* stream);
+int tpb_gemm_rs_store_bf16(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
+                           long long ldc, int a_mn, int b_mn, float alpha, void* const* slot_ptrs, int world,
+                           long long shard_elems, long long c_offset, int rank, void* stream);
+
+// Flags and the fixed-order reduction of the peer-memory FSDP collectives (fsdp_comm.cu).
+int tpb_flag_set(unsigned* flag, unsigned value, void* stream);
+int tpb_peer_signal(void* const* flag_tables, int world, long long index, unsigned value, void* stream);
+int tpb_flag_wait(const unsigned* flags, int n, long long stride, unsigned value, int site, void* stream);
+int tpb_rs_reduce_bf16(const void* stage, int world, long long stride, long long n, void* out, int out_is_f32,
+                       int accumulate, float scale, void* stream);
+
 // Router: one warp per token.  mode 0 softmax-top-k(-renormalise); mode 1 sigmoid + bias with
 // group-limited selection.  w_out [T,K] fp32, idx_out [T,K] int32, scores_out [T,E] fp32 (optional).
 int tpb_router_topk(const void* logits, int logits_is_bf16, const float* bias, float* w_out, int* idx_out,

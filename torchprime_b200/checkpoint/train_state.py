@@ -53,9 +53,11 @@ def load(path: str, trainer) -> int:
     raise RuntimeError(f"checkpoint {path} was written for mesh {payload['mesh']} / world {payload['world_size']}; "
                        f"current mesh is {dict(trainer.mesh.shape)} / world {rt.world_size()}")
   master = e.flat_master if e.flat_master is not None else e.flat_param
+  e.params_will_change()
   master.copy_(payload["flat_master"].to(master.device))
   if e.master_weights:
     e.flat_param.copy_(master)
+  e.params_changed()
   opt_sd = {k: (v.to(e.device) if isinstance(v, torch.Tensor) else v) for k, v in payload["optimizer"].items()}
   trainer.optimizer.load_state_dict(opt_sd)
   trainer.lr_scheduler.load_state_dict(payload["lr_scheduler"])

@@ -154,6 +154,14 @@ class LlamaDecoderLayer(nn.Module):
     self.input_layernorm = LlamaRMSNorm(config.hidden_size, eps=config.rms_norm_eps)
     self.post_attention_layernorm = LlamaRMSNorm(config.hidden_size, eps=config.rms_norm_eps)
 
+  @property
+  def fsdp_inkernel_gather(self) -> bool:
+    """Tells the FSDP engine that every matrix of this layer is read in the forward pass only through
+    ``ops.linear`` / ``ops.linear_swiglu``, which can wait for a weight that is still being gathered
+    inside the GEMM (not so when the tensor-parallel adaptors or biases take other paths)."""
+    a, m = self.self_attn, self.mlp
+    return a.tp_group is None and m.tp_group is None and a.q_proj.bias is None and a.o_proj.bias is None
+
   def forward(self, hidden_states, rope_cos, rope_sin, position_ids=None, segment_ids=None, cp=None):
     with trace_scope("LlamaDecoderLayer"):
       x, hidden_states = self.input_layernorm.with_residual(hidden_states)

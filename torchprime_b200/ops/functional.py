@@ -88,15 +88,58 @@ def _grad_sink(weights):
 
 
 def _wgrad_into(sink, weights, dy2, x2):
-  """dW = dy2^T @ x2 written into the main_grad sink (overwrite or accumulate)."""
+  """dW = dy2^T @ x2 written into the main_grad sink (overwrite or accumulate).  Under the FSDP
+  engine's peer-memory collectives the parameters carry ``rs_push``: the GEMM epilogue then stores
+  the tiles straight into the staging slots of the ranks that own those rows of the flat gradient
+  buffer (the reduce-scatter's send side) instead of into the local buffer."""
   from . import kernels as k
   overwrite = all(getattr(w, "grad_overwrite", False) for w in weights)
+  push = getattr(weights[0], "rs_push", None)
+  if push is not None:
+    if overwrite and all(getattr(w, "rs_push", None) is not None for w in weights) and push(sink, dy2, x2):
+      for w in weights:
+        w.grad_overwrite = False
+      return
+    if not overwrite:
+      push.func.__self__.check_not_pushed(push.args[0], sink)
   if sink.dtype == torch.float32:
     k.gemm(dy2, x2, a_mn=True, b_mn=True, out=sink, epi=k.EPI_F32 if overwrite else k.EPI_F32_ACC)
   else:
     k.gemm(dy2, x2, a_mn=True, b_mn=True, out=sink, epi=k.EPI_BF16 if overwrite else k.EPI_BF16_ACC)
   for w in weights:
     w.grad_overwrite = False
+
+
+# --------------------------------------------------------------------------- gathers in flight
+# The FSDP engine's copy-engine all-gather of the unit whose forward is running (parallel/fsdp_comm.py):
+# while it is set, GEMMs whose weight lies in that unit's gathered buffer wait for the weight's shards
+# inside the kernel; any other reader of such a weight first orders the stream after the whole gather.
+_AG_CTX = [None]
+
+
+def set_gather_context(ctx):
+  _AG_CTX[0] = ctx
+
+
+def get_gather_context():
+  return _AG_CTX[0]
+
+
+def _inflight(w):
+  """(context, element offset) when ``w`` belongs to a gather that is still in flight."""
+  ctx = _AG_CTX[0]
+  if ctx is None:
+    return None, None
+  off = ctx.offset_of(w)
+  return (ctx, off) if off is not None else (None, None)
+
+
+def _settle(*weights):
+  """For readers that cannot wait in-kernel: the whole gather must have landed."""
+  ctx = _AG_CTX[0]
+  if ctx is not None and any(w is not None and ctx.offset_of(w) is not None for w in weights):
+    ctx.wait_all()
+    set_gather_context(None)
 
 
 # --------------------------------------------------------------------------- linear
@@ -107,6 +150,10 @@ class _LinearFn(torch.autograd.Function):
     w = _fused_view(list(weights))
     x2 = x.reshape(-1, x.shape[-1])
     out_reduce, ctx.grad_reduce = reducers if reducers is not None else (None, None)
+    ag, ag_off = _inflight(weights[0])
+    if ag is not None and out_reduce is not None:
+      _settle(weights[0])
+      ag = None
     if out_reduce is not None:
       # row-parallel linear of tensor parallelism: the all-reduce over the tensor group happens in
       # the GEMM epilogue (rank 0 also adds the residual)
@@ -120,7 +167,12 @@ class _LinearFn(torch.autograd.Function):
     # in-place operators such as RoPE may modify it
     y = torch.empty(*x.shape[:-1], w.shape[0], dtype=x.dtype, device=x.device)
     y2 = y.view(-1, w.shape[0])
-    if residual is not None:
+    if ag is not None:
+      from ..parallel.fsdp_comm import gemm_ag_wait
+      res2 = residual.reshape(-1, w.shape[0]) if residual is not None else None
+      gemm_ag_wait(ag, x2, ag_off, w.shape[0], w.shape[1], y2, k.EPI_BF16_RES if res2 is not None else k.EPI_BF16,
+                   aux=res2)
+    elif residual is not None:
       k.gemm(x2, w, out=y2, epi=k.EPI_BF16_RES, aux=residual.reshape(-1, w.shape[0]))
     else:
       k.gemm(x2, w, out=y2)
@@ -195,6 +247,7 @@ def linear(x, weights, bias=None, residual=None, tp_reduce=None, tp_reduce_grad=
     return _LinearFn.apply(x, residual, len(ws), reducers, *ws)
   if tp_reduce is not None or tp_reduce_grad is not None:
     raise RuntimeError("fused tensor-parallel all-reduce requested on a path without kernels")
+  _settle(*ws)
   if len(ws) == 1:
     y = F.linear(x, ws[0], bias)
   else:
@@ -214,7 +267,12 @@ class _LinearSwigluFn(torch.autograd.Function):
     need_grad = any(ctx.needs_input_grad)
     gu = torch.empty(x2.shape[0], w.shape[0], dtype=x.dtype, device=x.device) if need_grad else None
     act = torch.empty(*x.shape[:-1], w_gate.shape[0], dtype=x.dtype, device=x.device)
-    k.gemm(x2, w, out=act.view(-1, w_gate.shape[0]), epi=k.EPI_SWIGLU, c2=gu)
+    ag, ag_off = _inflight(w_gate)
+    if ag is not None:
+      from ..parallel.fsdp_comm import gemm_ag_wait
+      gemm_ag_wait(ag, x2, ag_off, w.shape[0], w.shape[1], act.view(-1, w_gate.shape[0]), k.EPI_SWIGLU, c2=gu)
+    else:
+      k.gemm(x2, w, out=act.view(-1, w_gate.shape[0]), epi=k.EPI_SWIGLU, c2=gu)
     if need_grad:
       ctx.save_for_backward(x2, gu, w_gate, w_up)
     ctx.x_shape = x.shape
@@ -252,6 +310,7 @@ def linear_swiglu(x, w_gate, w_up, tp_reduce_grad=None):
     return _LinearSwigluFn.apply(x, w_gate, w_up, tp_reduce_grad)
   if tp_reduce_grad is not None:
     raise RuntimeError("fused tensor-parallel gradient all-reduce requested on a path without kernels")
+  _settle(w_gate, w_up)
   return F.silu(F.linear(x, w_gate)) * F.linear(x, w_up)
 
 

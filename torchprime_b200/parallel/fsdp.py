@@ -24,6 +24,7 @@ parameters themselves).  On CPU ranks (gloo) everything is synchronous.
 
 from __future__ import annotations
 
+import functools
 import logging
 import math
 import os
@@ -87,7 +88,8 @@ class FSDPEngine:
                grad_dtype=None, master_weights: bool = True, remat_classes=(), offload_tensors=(),
                init_std: float | None = None, seed: int = 42, materialize: bool | None = None,
                fused_collectives: bool = False, remat_policy: str | int = "all",
-               fused_expert_exchange: bool = False):
+               fused_expert_exchange: bool = False, collectives: str = "nccl",
+               keep_gathered: str | bool = "auto"):
     self.model = model
     self.mesh = mesh
     self.plan = plan
@@ -129,6 +131,15 @@ class FSDPEngine:
     self._slot_free_events = {}
     self._grad_slot_events = {}
     self._pending_rs: list[Unit] = []
+    # How the parameter all-gather and the gradient reduce-scatter over the fsdp axis are done:
+    # "nccl" (library collectives on the communication stream: the baseline mode) or "peer" (copy-engine
+    # gathers with in-kernel waits and weight-gradient GEMMs that store into the owners' staging slots,
+    # parallel/fsdp_comm.py).  "auto" takes "peer" where it applies.
+    self.collectives = self._resolve_collectives(collectives)
+    self.comm = None
+    self._keep_gathered_req = keep_gathered
+    self.keep_gathered = False
+    self._param_version = 0
     self._build_units()
     self._allocate()
     needs_init = materialize if materialize is not None else any(
@@ -136,8 +147,24 @@ class FSDPEngine:
     self._adopt_parameters(initialize=needs_init)
     self._wrap_forwards()
     self.attach_parallel_adaptors()
+    if self.comm is not None:
+      self.comm.params_changed()      # every rank's initial shards are in place before the first gather
 
   # ------------------------------------------------------------------ construction
+  def _resolve_collectives(self, want: str) -> str:
+    want = str(want or "nccl").lower()
+    assert want in ("nccl", "peer", "auto"), f"engine.fsdp_collectives must be nccl | peer | auto, got {want}"
+    applies = (self.is_cuda and self.fsdp > 1 and self.param_dtype == torch.bfloat16
+               and self.grad_dtype == torch.bfloat16)
+    if applies:
+      from ..dist import symm
+      from ..ops import functional as ops
+      applies = symm.is_supported(self.device) and ops.get_backend() != "torch"
+    if want == "peer" and not applies:
+      raise ValueError("engine.fsdp_collectives=peer needs CUDA ranks with fsdp > 1, bf16 parameters and gradients, "
+                       "the sm_100a kernels and peer-mapped memory")
+    return "peer" if (applies and want in ("peer", "auto")) else "nccl"
+
   def _init_kind(self, module: nn.Module, pname: str, full_name: str) -> str:
     custom = getattr(self.model, "param_init_kind", None)
     if custom is not None:
@@ -228,7 +255,13 @@ class FSDPEngine:
     self.sharded_total = total_shard
     total_shard += self.local_total
     self.total_shard = total_shard
-    self.flat_param = torch.zeros(total_shard, dtype=self.param_dtype, device=dev)
+    if self.collectives == "peer":
+      from .fsdp_comm import PeerFsdpComm
+      self.comm = PeerFsdpComm(self)
+      self.flat_param = self.comm.param_sb.local[:total_shard]
+      self.flat_param.zero_()
+    else:
+      self.flat_param = torch.zeros(total_shard, dtype=self.param_dtype, device=dev)
     self.flat_grad = torch.zeros(total_shard, dtype=self.grad_dtype, device=dev)
     if self.master_weights:
       self.flat_master = torch.zeros(total_shard, dtype=torch.float32, device=dev)
@@ -236,13 +269,31 @@ class FSDPEngine:
       self.flat_master = self.flat_param if self.param_dtype == torch.float32 else None
     self._gather_pool, self._grad_pool = [], []
     if self.fsdp > 1:
+      # Gathered parameters stay resident from a unit's forward to its backward when the whole model
+      # fits comfortably (one gather per unit and step instead of two); otherwise layer-sized units
+      # share two buffers.  Gradient buffers are zero-filled once: the padding between and behind
+      # parameters is never written and takes part in the reductions.
+      elem = torch.empty(0, dtype=self.param_dtype).element_size()
+      all_bytes = sum(u.total for u in self.units) * elem
+      keep = self._keep_gathered_req
+      if isinstance(keep, str):
+        keep = keep.lower()
+        keep = {"true": True, "false": False}.get(keep, keep)
+      if keep == "auto":
+        keep = False
+        if self.is_cuda and self.collectives == "peer":
+          _free, total_mem = torch.cuda.mem_get_info(dev)
+          keep = all_bytes <= 0.15 * total_mem
+      self.keep_gathered = bool(keep)
       if self.pool_size:
-        self._gather_pool = [torch.empty(self.pool_size, dtype=self.param_dtype, device=dev) for _ in range(2)]
-        self._grad_pool = [torch.empty(self.pool_size, dtype=self.grad_dtype, device=dev) for _ in range(2)]
+        if not self.keep_gathered:
+          self._gather_pool = [torch.empty(self.pool_size, dtype=self.param_dtype, device=dev) for _ in range(2)]
+        self._grad_pool = [torch.zeros(self.pool_size, dtype=self.grad_dtype, device=dev) for _ in range(2)]
       for u in self.units:
-        if u.big:
+        if u.big or self.keep_gathered:
           u._own_gather = torch.empty(u.total, dtype=self.param_dtype, device=dev)
-          u._own_grad = torch.empty(u.total, dtype=self.grad_dtype, device=dev)
+        if u.big:
+          u._own_grad = torch.zeros(u.total, dtype=self.grad_dtype, device=dev)
 
   def unit_shard(self, u: Unit, flat: torch.Tensor) -> torch.Tensor:
     return flat[u.shard_offset:u.shard_offset + u.shard_size]
@@ -345,6 +396,13 @@ class FSDPEngine:
           mod.ep = ExpertParallelMLP(self.mesh, mod.num_experts,
                                      fused_exchange=self.fused_expert_exchange and self.is_cuda)
 
+  def close(self):
+    """Collective: give back the peer-mapped buffers (they are not owned by torch's allocator)."""
+    if self.comm is not None:
+      self.comm.close()
+      self.comm = None
+      self.collectives = "closed"
+
   def unwrap(self):
     for u in self.units:
       if u.orig_forward is not None:
@@ -352,7 +410,7 @@ class FSDPEngine:
 
   # ------------------------------------------------------------------ gather / release
   def _gather_buffer(self, u: Unit):
-    return u._own_gather if u.big else self._gather_pool[u.index % 2][:u.total]
+    return u._own_gather if (u.big or self.keep_gathered) else self._gather_pool[u.index % 2][:u.total]
 
   def _grad_buffer(self, u: Unit):
     return u._own_grad if u.big else self._grad_pool[u.index % 2][:u.total]
@@ -360,18 +418,33 @@ class FSDPEngine:
   def _buf_key(self, u: Unit):
     return ("big", u.index) if u.big else ("pool", u.index % 2)
 
+  def _gbuf_key(self, u: Unit):
+    return ("big", u.index) if (u.big or self.keep_gathered) else ("pool", u.index % 2)
+
+  def _fresh(self, u: Unit) -> bool:
+    """The unit's gathered buffer holds the current parameter values."""
+    return u.gathered is not None and getattr(u, "_gathered_version", -1) == self._param_version
+
   def _issue_gather(self, u: Unit):
-    if self.fsdp == 1 or u.gathered is not None or u.gather_work is not None or u.shard_size == 0:
+    if self.fsdp == 1 or u.gather_work is not None or u.shard_size == 0:
       return
+    if u.gathered is not None:
+      if self._fresh(u):
+        return
+      u.gathered = None            # kept from a forward whose backward never ran: the values are stale
     buf = self._gather_buffer(u)
     shard = self.unit_shard(u, self.flat_param)
     if self.is_cuda:
-      ev = self._slot_free_events.get(self._buf_key(u))
+      ev = self._slot_free_events.get(self._gbuf_key(u))
       self.comm_stream.wait_stream(torch.cuda.current_stream())
       if ev is not None:
         self.comm_stream.wait_event(ev)
-      with torch.cuda.stream(self.comm_stream):
-        u.gather_work = dist.all_gather_into_tensor(buf, shard, group=self.fsdp_group, async_op=True)
+      if self.comm is not None:
+        self.comm.issue_gather(u, buf)
+        u.gather_work = True
+      else:
+        with torch.cuda.stream(self.comm_stream):
+          u.gather_work = dist.all_gather_into_tensor(buf, shard, group=self.fsdp_group, async_op=True)
     else:
       parts = [torch.empty_like(shard) for _ in range(self.fsdp)]
       dist.all_gather(parts, shard, group=self.fsdp_group)
@@ -379,14 +452,26 @@ class FSDPEngine:
       u.gather_work = True
     u._pending_buf = buf
 
-  def _ensure_gathered(self, u: Unit, with_grads: bool):
+  def _ensure_gathered(self, u: Unit, with_grads: bool, in_kernel_wait: bool = False):
     if self.fsdp == 1:
       return
-    if u.gathered is None:
+    if not self._fresh(u):
       self._issue_gather(u)
       if self.is_cuda and u.gather_work is not None:
-        u.gather_work.wait()
+        if self.comm is not None:
+          ctx = self.comm.gather_context(u) if in_kernel_wait else None
+          if ctx is not None:
+            # GEMMs wait for their weights' shards inside the kernel; the few parameters that other
+            # kernels read (norm weights, biases) have been copied first
+            self.comm.wait_small(u)
+            from ..ops import functional as ops
+            ops.set_gather_context(ctx)
+          else:
+            self.comm.wait_gather(u)
+        else:
+          u.gather_work.wait()
       u.gathered = u._pending_buf
+      u._gathered_version = self._param_version
       u.gather_work = None
     grads = None
     if with_grads:
@@ -398,13 +483,25 @@ class FSDPEngine:
       u.grad_full = grads
     self._point_params(u, u.gathered, grads)
 
-  def _release(self, u: Unit):
+  def _end_inflight(self, u: Unit):
+    """Readers after this point may touch any parameter of the unit without looking at flags."""
+    if self.comm is not None:
+      from ..ops import functional as ops
+      ctx = ops.get_gather_context()
+      if ctx is not None and ctx.unit is u:
+        ops.set_gather_context(None)
+        self.comm.wait_gather(u)
+
+  def _release(self, u: Unit, keep: bool = False):
     if self.fsdp == 1 or u.gathered is None:
+      return
+    self._end_inflight(u)
+    if keep and self.keep_gathered:
       return
     if self.is_cuda:
       ev = torch.cuda.Event()
       ev.record(torch.cuda.current_stream())
-      self._slot_free_events[self._buf_key(u)] = ev
+      self._slot_free_events[self._gbuf_key(u)] = ev
     u.gathered = None
     empty = torch.empty(0, dtype=self.param_dtype, device=self.device)
     for s in u.slots:
@@ -463,18 +560,28 @@ class FSDPEngine:
 
   # ------------------------------------------------------------------ hooks used by the unit function
   def pre_forward(self, u: Unit):
-    self._ensure_gathered(u, with_grads=False)
+    self._ensure_gathered(u, with_grads=False, in_kernel_wait=True)
     nxt = self._neighbor(u, +1)
     if nxt is not None:
       self._issue_gather(nxt)
 
-  def post_forward(self, u: Unit):
-    self._release(u)
+  def post_forward(self, u: Unit, backward_follows: bool = False):
+    self._release(u, keep=backward_follows)
 
   def pre_backward(self, u: Unit):
     self._ensure_gathered(u, with_grads=True)
+    # under fsdp a unit's gradients land in a buffer that is reduced and handed on after the unit's
+    # backward, so they are always overwritten there; accumulation happens in the reduction
+    overwrite = True if self.fsdp > 1 else self._overwrite_next
     for s in u.slots:
-      s.param.grad_overwrite = self._overwrite_next
+      s.param.grad_overwrite = self._overwrite_next if s.local else overwrite
+    if self.comm is not None and u.shard_size:
+      self.comm.begin_unit_backward(u)
+      if not u.terminal:     # (the head accumulates its weight gradient over row chunks in the local buffer)
+        push = functools.partial(self.comm.try_push_wgrad, u)
+        for s in u.slots:
+          if not s.local:
+            s.param.rs_push = push
     prv = self._neighbor(u, -1)
     if prv is not None:
       self._issue_gather(prv)
@@ -497,7 +604,12 @@ class FSDPEngine:
       return
     out = self.unit_shard(u, self.flat_grad)
     full = u.grad_full
-    if self.is_cuda:
+    if self.comm is not None:
+      ev = self.comm.reduce_scatter(u, out, accumulate=not self._overwrite_next)
+      self._grad_slot_events[self._buf_key(u)] = ev
+      u.rs_work = None
+      self._pending_rs.append(u)
+    elif self.is_cuda:
       self.comm_stream.wait_stream(torch.cuda.current_stream())
       with torch.cuda.stream(self.comm_stream):
         if self._overwrite_next:
@@ -519,6 +631,9 @@ class FSDPEngine:
       piece = red[lo:lo + u.shard_size] / self.fsdp
       out.copy_(piece) if self._overwrite_next else out.add_(piece)
     u.grad_full = None
+    for s in u.slots:
+      if getattr(s.param, "rs_push", None) is not None:
+        s.param.rs_push = None
 
   # ------------------------------------------------------------------ step-level API
   _overwrite_next = True
@@ -565,9 +680,22 @@ class FSDPEngine:
       batch_shards = self.mesh.size(("data", "fsdp")) * (1 if self.ep_folded else self.ep)
       local.mul_(1.0 / (batch_shards * self.mesh.size("context")))
 
+  def params_will_change(self):
+    """Call before anything overwrites the bf16 parameter shards (optimizer step, state loading)."""
+    if self.comm is not None:
+      self.comm.params_will_change()
+
+  def params_changed(self):
+    """Call after the bf16 parameter shards were overwritten: gathered copies are stale from here."""
+    self._param_version += 1
+    if self.comm is not None:
+      self.comm.params_changed()
+
   def sync_params_from_master(self):
     if self.master_weights:
+      self.params_will_change()
       self.flat_param.copy_(self.flat_master)
+      self.params_changed()
 
   # ------------------------------------------------------------------ state dict helpers
   def _gather_unit_full(self, u: Unit, flat: torch.Tensor) -> torch.Tensor:
@@ -625,6 +753,7 @@ class FSDPEngine:
       if missing or unexpected:
         raise RuntimeError(f"Error(s) in loading state_dict: missing keys {sorted(missing)}, "
                            f"unexpected keys {sorted(unexpected)}")
+    self.params_will_change()
     for u in self.units:
       full = torch.zeros(u.total, dtype=torch.float32, device=self.device)
       for s in u.slots:
@@ -648,6 +777,7 @@ class FSDPEngine:
       if self.master_weights:
         self.unit_shard(u, self.flat_master).copy_(full[lo:lo + u.shard_size])
       self.unit_shard(u, self.flat_param).copy_(full[lo:lo + u.shard_size].to(self.param_dtype))
+    self.params_changed()
 
   def num_parameters(self) -> int:
     return sum(math.prod(s.full_shape) for u in self.units for s in u.slots)
@@ -700,7 +830,7 @@ def _run_unit_saved(engine: FSDPEngine, u: Unit, args, kwargs):
   before = torch.cuda.memory_allocated(engine.device) if measure else 0
   engine.pre_forward(u)
   out = u.orig_forward(*call, **kwargs)
-  engine.post_forward(u)
+  engine.post_forward(u, backward_follows=True)
   if measure:
     engine.note_saved_unit_bytes(torch.cuda.memory_allocated(engine.device) - before)
   outs = out if isinstance(out, tuple) else (out,)
@@ -763,7 +893,7 @@ class _RematFn(torch.autograd.Function):
     engine.pre_forward(u)
     with torch.no_grad():
       out = u.orig_forward(*args, **kwargs)
-    engine.post_forward(u)
+    engine.post_forward(u, backward_follows=True)
     ctx.out_is_tuple = isinstance(out, tuple)
     return out
 

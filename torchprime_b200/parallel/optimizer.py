@@ -148,6 +148,7 @@ class ShardedAdamW(ShardedOptimizerBase):
     self.step_count += 1
     master = e.flat_master if e.flat_master is not None else e.flat_param
     p16 = e.flat_param if e.master_weights else None
+    e.params_will_change()
     if e.is_cuda and ops.get_backend() != "torch" and master.dtype == torch.float32 and master.numel() % 4 == 0:
       from ..ops import kernels as k
       k.adamw_(master, self.exp_avg, self.exp_avg_sq, e.flat_grad, p16, lr, self.betas[0], self.betas[1],
@@ -163,6 +164,7 @@ class ShardedAdamW(ShardedOptimizerBase):
           master[sl].copy_(p32)
         if p16 is not None:
           p16[sl].copy_(master[sl])
+    e.params_changed()
 
   def state_dict(self):
     return {"exp_avg": self.exp_avg, "exp_avg_sq": self.exp_avg_sq, "step": self.step_count}
@@ -240,6 +242,7 @@ class ShardedAdafactor(ShardedOptimizerBase):
     coef = self._coef
     dev = e.flat_grad.device
     grp = e.fsdp_group if e.fsdp > 1 else None
+    e.params_will_change()
 
     def apply(sl, upd, n):
       rms = upd.norm(2) / math.sqrt(n)
@@ -296,6 +299,7 @@ class ShardedAdafactor(ShardedOptimizerBase):
       apply(slice(pc["start"], pc["start"] + upd.numel()), upd, upd.numel())
     if e.master_weights:
       e.flat_param.copy_(master)
+    e.params_changed()
 
   def state_dict(self):
     return {"step": self.step_count, "pieces": [{k: v for k, v in p.items() if k in ("v", "vr", "vc")}

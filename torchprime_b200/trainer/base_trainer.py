@@ -94,7 +94,8 @@ class Trainer:
       remat_classes=self.remat_plan.remat_classes, offload_tensors=self.remat_plan.offload_tensors,
       seed=int(self.config.get("seed", 42)), fused_collectives=bool(eng.get("fused_collectives", False)),
       remat_policy=_remat_policy(eng.get("remat_layers", "auto")),
-      fused_expert_exchange=bool(eng.get("fused_expert_exchange", False)))
+      fused_expert_exchange=bool(eng.get("fused_expert_exchange", False)),
+      collectives=str(eng.get("fsdp_collectives", "auto")), keep_gathered=eng.get("keep_gathered", "auto"))
     _move_buffers(model, self.device)
     if hasattr(model, "return_logits"):
       model.return_logits = not bool(eng.get("chunked_ce", True))
