@@ -131,6 +131,15 @@ def test_mixtral_expert_parallel_folded_matches_single():
   close(ep, single)
 
 
+def test_mixtral_expert_parallel_orthogonal_matches_single():
+  """An orthogonal expert axis is also a batch axis: dense gradients must be averaged over it and
+  the gradient norm must count every expert rank's slices once."""
+  single = run(1, MIX + ["ici_mesh.fsdp=1"])["traj"]
+  ep = run(2, MIX + ["ici_mesh.fsdp=1", "ici_mesh.expert=2", "expert_axis_mode=orthogonal",
+                     "model/sharding=mixtral-fsdp-ep"])["traj"]
+  close(ep, single)
+
+
 def test_resume_from_training_state(tmp_path):
   ov = LLAMA + ["ici_mesh.fsdp=2"]
   full = run(2, ov, steps=4, extra_action=f"save_at_2:{tmp_path}/ckpt")["traj"]

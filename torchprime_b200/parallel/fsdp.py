@@ -109,7 +109,10 @@ class FSDPEngine:
       assert self.ep == mesh.size(("data", "fsdp")), (
         "a folded expert axis must span all data x fsdp ranks (expert == data * fsdp)")
     self.local_total = 0
-    self.replica_axes = ("data", "context")
+    # Axes over which dense parameters are replicas that saw different tokens: their gradients are
+    # averaged there after the fsdp reduce-scatter.  An orthogonal expert axis is one more
+    # batch-sharding axis for everything that is not an expert weight.
+    self.replica_axes = ("data", "context") if (self.ep == 1 or self.ep_folded) else ("data", "expert", "context")
     self.replica_group = mesh.group(self.replica_axes) if mesh is not None else None
     self.replica_size = mesh.size(self.replica_axes) if mesh is not None else 1
     self.master_weights = master_weights and param_dtype != torch.float32

@@ -87,6 +87,17 @@ class ShardedOptimizerBase:
         for lo in range(0, t.numel(), _CHUNK):   # bounded temporaries
           acc.add_(torch.linalg.vector_norm(t[lo:lo + _CHUNK], dtype=torch.float32).pow(2))
 
+    # Dense shards are disjoint over the fsdp group; expert-parallel slices (the tail of the flat
+    # buffers) are disjoint over the expert group, which need not be the same set of ranks.
+    n_dense = getattr(e, "sharded_total", g.numel())
+    local_sq = None
+    if n_dense < g.numel():
+      local_sq = torch.zeros_like(self._sumsq)
+      sumsq_into(local_sq, g[n_dense:])
+      ep_grp = e.mesh.group("expert") if (dist.is_initialized() and e.mesh is not None) else None
+      if ep_grp is not None:
+        dist.all_reduce(local_sq, group=ep_grp)
+      g = g[:n_dense]
     self._sumsq.zero_()
     sumsq_into(self._sumsq, g)
     if dist.is_initialized() and e.mesh is not None:
@@ -103,6 +114,8 @@ class ShardedOptimizerBase:
       fsdp_grp = e.mesh.group("fsdp")
       if fsdp_grp is not None:
         dist.all_reduce(self._sumsq, group=fsdp_grp)
+    if local_sq is not None:
+      self._sumsq.add_(local_sq)
     if use_k:
       from ..ops import kernels as k
       k.clip_coef_(self._sumsq, max_norm or 0.0, self._coef, self._norm)
