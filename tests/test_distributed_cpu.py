@@ -50,6 +50,17 @@ def _train_worker(rank, world, port, overrides, steps, out, extra_action):
     if extra_action == "state_dict":
       sd = tr.engine.full_state_dict()
       result["norm"] = {k: v.float().norm().item() for k, v in sd.items()}
+    if extra_action and extra_action.startswith("dcp:"):
+      from torchprime_b200.checkpoint import dcp_io
+      folder = extra_action[4:]
+      dcp_io.save_distributed_checkpoint(None, folder, engine=tr.engine)
+      rt.barrier()
+      want = tr.engine.full_state_dict()
+      if rank == 0:
+        got = dcp_io.load_full_state_from_distcp(folder)
+        assert got.keys() == want.keys(), (sorted(got)[:4], sorted(want)[:4])
+        result["dcp_max_diff"] = max((got[k].float() - want[k].float()).abs().max().item() for k in want)
+        result["dcp_files"] = sorted(os.listdir(folder))
     if rank == 0:
       out.update(result)
     rt.barrier()
@@ -153,3 +164,16 @@ def test_full_state_dict_gathers_all_parameters():
   assert one.keys() == two.keys() and "model.layers.1.mlp.down_proj.weight" in one
   for k in one:
     assert abs(one[k] - two[k]) < 1e-4 * max(1.0, one[k]), k
+
+
+@pytest.mark.parametrize("ov", [LLAMA + ["ici_mesh.fsdp=2"],
+                                MIX + ["ici_mesh.fsdp=2", "ici_mesh.expert=2", "expert_axis_mode=folded",
+                                       "model/sharding=mixtral-fsdp-ep"]], ids=["llama_fsdp2", "mixtral_fsdp2_ep2"])
+def test_distributed_checkpoint_is_a_dcp_directory(tmp_path, ov):
+  """Format B is readable by torch.distributed.checkpoint and holds every parameter whole, also with
+  expert-parallel slices (which live outside the fsdp-sharded region of the flat buffers)."""
+  res = run(2, ov, steps=1, extra_action=f"dcp:{tmp_path}/ckpt")
+  assert res["dcp_max_diff"] == 0.0
+  files = res["dcp_files"]
+  assert ".metadata" in files and all(any(f.startswith(f"__{r}_") and f.endswith(".distcp") for f in files)
+                                      for r in range(2)), files

@@ -2,19 +2,26 @@
 
 The reference saves ``{"model": state_dict}`` with ``torch.distributed.checkpoint`` from
 every host and converts on rank 0 (torchprime/torch_xla_models/model/model_utils.py:
-284-351).  Here every rank writes its flat parameter shard plus the shard layout as one
-``__<rank>_0.distcp`` file, rank 0 writes ``.metadata``; conversion reassembles full
-tensors on CPU from those files, deletes them and writes the sharded safetensors.
+284-351).  This module writes the same kind of directory (``.metadata`` plus
+``__<rank>_<n>.distcp`` files that ``torch.distributed.checkpoint.load`` reads, top-level
+key ``"model"``, one entry per parameter under its state-dict name).
+
+The engine's shards are slices of flat per-unit buffers, which cut parameters at arbitrary
+element offsets, so they are not expressible as sharded tensors of the checkpoint format.
+Instead every parameter is written whole by exactly one rank: the ranks walk the model unit
+by unit, all take part in the gathers (over the fsdp, tensor and expert groups), and rank
+``i`` keeps the parameters whose position in the model is ``i`` modulo the world size.  Host
+memory per rank is therefore 1/world of the model, and the files are written in parallel.
 """
 
 from __future__ import annotations
 
 import glob
-import json
 import logging
 import os
 
 import torch
+import torch.distributed.checkpoint as dcp
 
 from ..dist import runtime as rt
 from . import safetensors_io
@@ -22,56 +29,40 @@ from . import safetensors_io
 logger = logging.getLogger(__name__)
 
 
-def save_distributed_checkpoint(state: dict, save_dir: str, engine=None) -> None:
+def _owned_state(engine) -> dict:
+  """This rank's share of the un-sharded parameters (whole tensors on CPU)."""
+  names = [s.name for u in engine.units for s in u.slots]
+  world, rank = rt.world_size(), rt.rank()
+  owner = {n: i % world for i, n in enumerate(names)}
+  return engine.full_state_dict(to_cpu=True, keep=lambda name: owner[name] == rank)
+
+
+def save_distributed_checkpoint(state: dict | None, save_dir: str, engine=None) -> None:
+  """Collective.  ``state`` is a plain ``{name: tensor}`` dict for an un-sharded model (then only
+  rank 0 holds data); with ``engine`` the parameters come from its shards."""
   os.makedirs(save_dir, exist_ok=True)
-  if engine is None:
-    # un-sharded model: rank 0 writes everything
-    if rt.is_main():
-      torch.save({"model": {k: v.detach().cpu() for k, v in state.items()}, "kind": "full"},
-                 os.path.join(save_dir, "__0_0.distcp"))
-      with open(os.path.join(save_dir, ".metadata"), "w") as f:
-        json.dump({"kind": "full", "world_size": 1}, f)
-    return
-  payload = {"kind": "flat", "flat_param": state["flat_param"].detach().cpu(), "layout": state["layout"],
-             "fsdp": state["fsdp"], "fsdp_rank": state["fsdp_rank"], "tp": state["tp"], "tp_rank": state["tp_rank"]}
-  # replicas along data/context hold identical shards: only the first replica writes
-  if engine.mesh.index(("data", "context")) == 0:
-    torch.save(payload, os.path.join(save_dir, f"__{rt.rank()}_0.distcp"))
-  if rt.is_main():
-    with open(os.path.join(save_dir, ".metadata"), "w") as f:
-      json.dump({"kind": "flat", "world_size": rt.world_size(), "fsdp": state["fsdp"], "tp": state["tp"]}, f)
+  if engine is not None:
+    model_state = _owned_state(engine)
+  else:
+    model_state = {k: v.detach().cpu() for k, v in state.items()} if rt.is_main() else {}
+  import torch.distributed as dist
+  dcp.save({"model": model_state}, storage_writer=dcp.FileSystemWriter(save_dir, thread_count=4),
+           no_dist=not dist.is_initialized())
 
 
 def load_full_state_from_distcp(ckpt_dir: str) -> dict:
-  files = sorted(glob.glob(os.path.join(ckpt_dir, "__*_0.distcp")))
-  if not files:
-    raise FileNotFoundError(f"no *.distcp files in {ckpt_dir}")
-  parts = [torch.load(f, map_location="cpu", weights_only=False) for f in files]
-  if parts[0]["kind"] == "full":
-    return parts[0]["model"]
-  fsdp, tp = parts[0]["fsdp"], parts[0]["tp"]
-  by_coord = {(p["tp_rank"], p["fsdp_rank"]): p for p in parts}
-  out = {}
-  layout = parts[0]["layout"]
-  for t in range(tp):
-    for u in layout:
-      pieces = [by_coord[(t, r)]["flat_param"][u["shard_offset"]:u["shard_offset"] + u["shard_size"]]
-                for r in range(fsdp)]
-      full = torch.cat(pieces)
-      for s in u["slots"]:
-        n = 1
-        for d in s["shape"]:
-          n *= d
-        val = full[s["offset"]:s["offset"] + n].view(s["shape"]).clone()
-        if s["tp_dim"] is None:
-          out[s["name"]] = val
-        else:
-          out.setdefault(s["name"], [None] * tp)[t] = val
-  for u in layout:
-    for s in u["slots"]:
-      if s["tp_dim"] is not None:
-        out[s["name"]] = torch.cat(out[s["name"]], dim=s["tp_dim"])
-  return out
+  """Read every tensor under ``"model"`` into CPU memory (single process, no process group)."""
+  if not os.path.exists(os.path.join(ckpt_dir, ".metadata")):
+    raise FileNotFoundError(f"no distributed checkpoint (.metadata) in {ckpt_dir}")
+  reader = dcp.FileSystemReader(ckpt_dir)
+  meta = reader.read_metadata()
+  state = {}
+  for key, tm in meta.state_dict_metadata.items():
+    if not key.startswith("model.") or not hasattr(tm, "size"):
+      continue
+    state[key] = torch.empty(tuple(tm.size), dtype=tm.properties.dtype)
+  dcp.load(state, storage_reader=reader, no_dist=True)
+  return {k[len("model."):]: v for k, v in state.items()}
 
 
 def convert_to_safetensors_on_cpu(ckpt_dir: str, save_dir: str) -> None:

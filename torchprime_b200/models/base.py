@@ -92,7 +92,7 @@ class BaseCausalLM(nn.Module):
       safetensors_io.copy_hf_config_files(config.model.get("pretrained_model", None), save_dir)
       safetensors_io.save_hf_tokenizer(config.model.get("tokenizer_name", None), save_dir)
     rt.barrier()
-    state = engine.sharded_state_dict() if engine is not None else {k: v for k, v in self.state_dict().items()}
+    state = None if engine is not None else {k: v for k, v in self.state_dict().items()}
     dcp_io.save_distributed_checkpoint(state, save_dir, engine=engine)
     rt.barrier()
     if config.task.get("convert_to_safetensors", False) and rt.rank() == 0:

@@ -714,8 +714,9 @@ class FSDPEngine:
       torch.cat(parts, out=out)
     return out
 
-  def full_state_dict(self, to_cpu: bool = True, dtype=None, source: str = "param") -> dict:
-    """Un-sharded ``{name: tensor}`` (collective over fsdp and tensor groups)."""
+  def full_state_dict(self, to_cpu: bool = True, dtype=None, source: str = "param", keep=None) -> dict:
+    """Un-sharded ``{name: tensor}`` (collective over fsdp, tensor and expert groups).  ``keep(name)``
+    limits what this rank retains; every rank still takes part in every gather."""
     flat = {"param": self.flat_param, "master": self.flat_master, "grad": self.flat_grad}[source]
     tp_group = self.mesh.group("tensor") if (self.mesh is not None and self.tp > 1) else None
     out = {}
@@ -734,6 +735,8 @@ class FSDPEngine:
           parts = [torch.empty_like(t) for _ in range(self.tp)]
           dist.all_gather(parts, t.contiguous(), group=tp_group)
           t = torch.cat(parts, dim=s.tp_dim)
+        if keep is not None and not keep(s.name):
+          continue
         t = t.to(dtype) if dtype is not None else t
         out[s.name] = t.detach().cpu().clone() if to_cpu else t.detach().clone()
     return out
