@@ -230,3 +230,39 @@ def test_sft_trainer_loads_and_exports(tmp_path):
   m2.from_pretrained(str(exp))
   after = tr.engine.full_state_dict()
   assert torch.allclose(m2.state_dict()["lm_head.weight"], after["lm_head.weight"], atol=1e-6)
+
+
+def test_multicast_switch_and_abort_guard(tmp_path, monkeypatch):
+  """engine.multicast=false turns every multicast binding off through the switches the fused kernels
+  read; a watchdog that may end the process refuses to run with multicast bindings on several ranks."""
+  import os
+  from torchprime_b200.dist import runtime as rt
+  for key in ("TPB_AG_MULTICAST", "TPB_TP_FUSED", "TPB_CP_MULTICAST"):
+    monkeypatch.delenv(key, raising=False)
+  tr, _ = make_trainer(tmp_path, ["engine.multicast=false"])
+  assert not tr.multicast
+  assert all(os.environ[k] == "0" for k in ("TPB_AG_MULTICAST", "TPB_TP_FUSED", "TPB_CP_MULTICAST"))
+  with monkeypatch.context() as m:
+    m.setattr(rt, "world_size", lambda: 2)
+    with pytest.raises(ValueError, match="engine.multicast=false"):
+      make_trainer(tmp_path, ["engine.watchdog_seconds=5", "engine.watchdog_abort=true"])
+  tr, _ = make_trainer(tmp_path, ["engine.watchdog_seconds=5", "engine.watchdog_abort=true", "engine.multicast=false"])
+  assert tr.watchdog.abort
+  tr.watchdog.stop()
+
+
+def test_device_timeout_is_raised_at_the_step_it_is_seen(tmp_path, monkeypatch):
+  """A bounded device wait that gave up must stop the run at once (with the step number), not after the
+  last step: consumers of that kernel read partial data."""
+  from torchprime_b200.ops import _lib
+  tr, _ = make_trainer(tmp_path, ["task.max_steps=6"])
+  calls = {"n": 0}
+
+  def fake_check(step, synchronize):
+    calls["n"] += 1
+    if step == 2:
+      raise _lib.KernelError(f"at training step {step}: device-side bounded wait gave up")
+  monkeypatch.setattr(tr, "_check_device_status", fake_check)
+  with pytest.raises(_lib.KernelError, match="at training step 2"):
+    tr.train_loop()
+  assert calls["n"] >= 3

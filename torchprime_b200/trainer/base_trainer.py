@@ -72,6 +72,17 @@ class Trainer:
     eng = self.config.get("engine", {}) or {}
     if eng.get("kernels", "sm100") == "torch":
       ops.set_backend("torch")
+    # One switch for every NVSwitch multicast binding (multimem stores of the fused all-gather and the
+    # context-parallel K/V push, multimem reductions of the tensor-parallel GEMM epilogues).  A rank that
+    # dies while its memory is bound to a multicast object can fault its peers' GPUs, so any mode that
+    # ends a rank abruptly (a watchdog that aborts, elastic exit) has to run with it off.
+    self.multicast = bool(eng.get("multicast", True))
+    if not self.multicast:
+      for key in ("TPB_AG_MULTICAST", "TPB_TP_FUSED", "TPB_CP_MULTICAST"):
+        os.environ[key] = "0"
+    if bool(eng.get("watchdog_abort", False)) and self.multicast and rt.world_size() > 1:
+      raise ValueError("engine.watchdog_abort=true ends a rank without tearing down its peers: set "
+                       "engine.multicast=false (and NCCL_NVLS_ENABLE=0 in the environment) with it")
 
     # -- model transformations (same order as the reference's constructor) --
     model = auto_trace(model)
@@ -120,7 +131,9 @@ class Trainer:
     self.watchdog = None
     if float(eng.get("watchdog_seconds", 0) or 0) > 0:
       from ..dist.watchdog import StepWatchdog
-      self.watchdog = StepWatchdog(float(eng.watchdog_seconds))
+      # abort=False: a late step is logged with a stack dump and raised at the END of that step, which
+      # cannot end a step that never finishes; engine.watchdog_abort=true exits the process instead
+      self.watchdog = StepWatchdog(float(eng.watchdog_seconds), abort=bool(eng.get("watchdog_abort", False)))
     if eng.get("resume_from", None):
       from ..checkpoint import train_state
       self.start_step = train_state.load(eng.resume_from, self)
@@ -226,6 +239,7 @@ class Trainer:
       t0 = time.perf_counter()
       loss, grad_norm = self.train_step(batch)
       t1 = time.perf_counter()
+      self._check_device_status(step, synchronize=False)
 
       if step % self.config.logging_steps == 0:
         lr = self.lr_scheduler.get_last_lr()[0]
@@ -235,6 +249,7 @@ class Trainer:
         self._log_to_tensorboard(step / steps_per_epoch, step, loss_v, lr, gn_v)
         if math.isnan(loss_v):
           raise ValueError(f"Loss is NaN at step {step}")
+        self._check_device_status(step, synchronize=False)   # loss.item() above synchronised the device
 
       if step == self.config.profile_start_step:
         self._start_profile()
@@ -242,6 +257,7 @@ class Trainer:
         self._stop_profile()
       if ckpt_every and (step + 1) % ckpt_every == 0:
         from ..checkpoint import train_state
+        self._check_device_status(step, synchronize=True)    # never checkpoint a state a timed-out wait produced
         train_state.save(os.path.join(self.config.output_dir, "checkpoints", f"step_{step + 1}"), self, step + 1)
       if self.watchdog is not None:
         self.watchdog.end_step(step)
@@ -256,6 +272,22 @@ class Trainer:
     if self.watchdog is not None:
       self.watchdog.stop()
     logger.info("Finished training run")
+
+  def _check_device_status(self, step: int, synchronize: bool):
+    """Raise if a bounded device-side wait (peer flag, barrier, mbarrier) gave up.  The status block is
+    host-mapped memory, so reading it costs no device round trip and is done every step; a kernel that
+    gave up let its consumers read partial data, so the run must not continue or be checkpointed."""
+    if self.device.type != "cuda":
+      return
+    from ..ops import _lib
+    if not _lib.available():
+      return
+    if synchronize:
+      torch.cuda.synchronize()
+    try:
+      _lib.raise_on_device_timeout()
+    except _lib.KernelError as e:
+      raise _lib.KernelError(f"at training step {step}: {e}") from e
 
   def _start_profile(self):
     if self._profiler is not None:
