@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import json
 import logging
+import contextlib
 import os
 import shutil
 import tempfile
@@ -116,17 +117,20 @@ def local_path_from_gcs(path_or_repo: str, temp_dir: str | None = None):
     shutil.rmtree(local, ignore_errors=True)
 
 
-def resolve_model_dir(path_or_repo: str) -> str:
-  """Local directory, ``gs://`` prefix or HF hub repo id -> local directory with the files."""
+@contextlib.contextmanager
+def model_dir(path_or_repo: str):
+  """Context manager yielding a local directory with the model files of a local directory, a
+  ``gs://`` prefix (copied to a temporary directory that is removed on exit) or an HF hub repo id."""
   if os.path.isdir(path_or_repo):
-    return path_or_repo
-  if str(path_or_repo).startswith("gs://"):
-    ctx = local_path_from_gcs(path_or_repo)
-    return ctx.__enter__()
-  from ..utils.retry import retry
-  import huggingface_hub
-  return retry(lambda: huggingface_hub.snapshot_download(
-    repo_id=path_or_repo, allow_patterns=["*.safetensors*", "config.json", "generation_config.json"]))
+    yield path_or_repo
+  elif str(path_or_repo).startswith("gs://"):
+    with local_path_from_gcs(path_or_repo) as local:
+      yield local
+  else:
+    from ..utils.retry import retry
+    import huggingface_hub
+    yield retry(lambda: huggingface_hub.snapshot_download(
+      repo_id=path_or_repo, allow_patterns=["*.safetensors*", "config.json", "generation_config.json"]))
 
 
 def copy_hf_config_files(pretrained: str | None, save_dir: str) -> None:
@@ -134,14 +138,13 @@ def copy_hf_config_files(pretrained: str | None, save_dir: str) -> None:
   if not pretrained:
     return
   try:
-    src = resolve_model_dir(pretrained)
+    with model_dir(pretrained) as src:
+      for name in ("config.json", "generation_config.json"):
+        p = os.path.join(src, name)
+        if os.path.exists(p):
+          shutil.copy(p, os.path.join(save_dir, name))
   except Exception as e:  # noqa: BLE001 - offline boxes cannot reach the hub
     logger.warning("could not fetch HF config files of %s: %s", pretrained, e)
-    return
-  for name in ("config.json", "generation_config.json"):
-    p = os.path.join(src, name)
-    if os.path.exists(p):
-      shutil.copy(p, os.path.join(save_dir, name))
 
 
 def save_hf_tokenizer(tokenizer_name: str | None, save_dir: str) -> None:

@@ -63,8 +63,8 @@ class BaseCausalLM(nn.Module):
 
   def from_pretrained(self, model_path_or_repo: str):
     from ..checkpoint import safetensors_io
-    model_dir = safetensors_io.resolve_model_dir(model_path_or_repo)
-    state = safetensors_io.load_safetensors_to_state_dict(model_dir)
+    with safetensors_io.model_dir(model_path_or_repo) as model_dir:
+      state = safetensors_io.load_safetensors_to_state_dict(model_dir)
     state = self.convert_loaded_state_dict(state)
     self.load_state_dict(state, strict=True)
     return self

@@ -19,8 +19,8 @@ class SFTTrainer(Trainer):
     if pretrained:
       from ..checkpoint import safetensors_io
       logger.info("Loading pretrained weights from %s", pretrained)
-      model_dir = safetensors_io.resolve_model_dir(pretrained)
-      state = model.convert_loaded_state_dict(safetensors_io.load_safetensors_to_state_dict(model_dir))
+      with safetensors_io.model_dir(pretrained) as model_dir:
+        state = model.convert_loaded_state_dict(safetensors_io.load_safetensors_to_state_dict(model_dir))
     else:
       logger.warning("No pretrained checkpoint specified; training from scratch")
     super().__init__(model, config, train_dataset)
