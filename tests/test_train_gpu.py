@@ -45,6 +45,17 @@ def test_llama_kernels_track_torch_backend(cuda_lib, tmp_path):
     assert abs(ga - gb) / gb < 0.08, (mine, base)
 
 
+def test_host_offload_of_layer_inputs_is_exact(cuda_lib, tmp_path):
+  """Layer inputs parked in pinned host memory between forward and backward (reference:
+  torchprime/torch_xla_models/offloading.py:41-146) give the same trajectory, bit for bit, as keeping
+  them on the device; the pinned buffers are allocated once and reused every step."""
+  plain, _ = _run("auto", tmp_path, extra=["engine.remat_layers=all"])
+  off, tr = _run("auto", tmp_path, extra=["model/remat=llama-scan-offload"])
+  assert plain == off, (plain, off)
+  assert len(tr.engine._offload_pool) == 2 and not tr.engine._offloaded
+  assert all(h.is_pinned() for h in tr.engine._offload_pool.values())
+
+
 def test_train_loop_writes_metrics_and_profile(cuda_lib, tmp_path):
   import json, os
   from torchprime_b200.config import compose

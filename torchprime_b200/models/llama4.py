@@ -70,6 +70,9 @@ class Llama4TextExperts(nn.Module):
     self.expert_dim = self.intermediate_size
     self.gate_up_proj = nn.Parameter(torch.empty(self.num_experts, self.hidden_size, 2 * self.expert_dim))
     self.down_proj = nn.Parameter(torch.empty(self.num_experts, self.expert_dim, self.hidden_size))
+    for w in (self.gate_up_proj, self.down_proj):
+      if not w.is_meta:
+        nn.init.normal_(w, mean=0.0, std=float(config.get("initializer_range", 0.02)))
 
   def forward(self, hidden_states):
     """hidden_states: [E * T, D] (expert-major) -> [E * T, D]."""

@@ -131,6 +131,9 @@ class FSDPEngine:
     self.units: list[Unit] = []
     self._dummy = None
     self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+    self.offload_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
+    self._offload_pool = {}      # (unit, shape, dtype) -> pinned host buffer, allocated once
+    self._offloaded = {}         # unit index -> the copy that is in host memory for this step's backward
     self._slot_free_events = {}
     self._grad_slot_events = {}
     self._pending_rs: list[Unit] = []
@@ -520,6 +523,8 @@ class FSDPEngine:
     """True when unit ``u`` keeps its activations for backward instead of recomputing them."""
     if not u.remat_class:
       return self.fsdp > 1          # not asked to recompute; under fsdp the saved path re-gathers
+    if u.offload:
+      return False                  # host offload keeps only the unit's input: the unit is recomputed
     pol = self.remat_policy
     if pol == "all":
       return False
@@ -892,7 +897,7 @@ class _RematFn(torch.autograd.Function):
     ctx.other_args = [None if isinstance(a, torch.Tensor) else a for a in args]
     ctx.offloaded = None
     if u.offload and tensors and engine.is_cuda:
-      ctx.offloaded = _offload_to_host(engine, tensors[0])
+      ctx.offloaded = _offload_to_host(engine, u, tensors[0])
       ctx.save_for_backward(*tensors[1:])
     else:
       ctx.save_for_backward(*tensors)
@@ -908,7 +913,7 @@ class _RematFn(torch.autograd.Function):
     engine, u = ctx.engine, ctx.unit
     saved = list(ctx.saved_tensors)
     if ctx.offloaded is not None:
-      saved.insert(0, _reload_from_host(engine, ctx.offloaded))
+      saved.insert(0, _reload_from_host(engine, u, ctx.offloaded))
     args = list(ctx.other_args)
     live = []
     for pos, i in enumerate(ctx.tensor_idx):
@@ -986,19 +991,49 @@ def _collect_leaf_grads(u: Unit):
       p.grad = None
 
 
-def _offload_to_host(engine: FSDPEngine, t: torch.Tensor):
-  """Copy a saved layer input to pinned host memory on the communication stream."""
-  host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
-  engine.comm_stream.wait_stream(torch.cuda.current_stream())
-  with torch.cuda.stream(engine.comm_stream):
+def _offload_to_host(engine: FSDPEngine, u: Unit, t: torch.Tensor):
+  """Copy a saved layer input into the unit's pinned host buffer on the offload stream.  The buffer
+  is allocated once per unit and shape (page-locking memory is a driver call that costs more than
+  the copy) and reused every step; copies of one buffer are ordered by that stream."""
+  key = (u.index, tuple(t.shape), t.dtype)
+  host = engine._offload_pool.get(key)
+  if host is None:
+    host = torch.empty(t.shape, dtype=t.dtype, device="cpu", pin_memory=True)
+    engine._offload_pool[key] = host
+  s = engine.offload_stream
+  s.wait_stream(torch.cuda.current_stream())
+  with torch.cuda.stream(s):
     host.copy_(t, non_blocking=True)
+  t.record_stream(s)
+  packed = {"host": host, "device": t.device, "reloaded": None, "event": None}
+  engine._offloaded[u.index] = packed
+  return packed
+
+
+def _start_reload(engine: FSDPEngine, packed):
+  """Enqueue the host -> device copy on the offload stream (behind the device -> host copy of the
+  same buffer) and remember the event that the compute stream will wait on."""
+  if packed["reloaded"] is not None:
+    return
+  s = engine.offload_stream
+  with torch.cuda.stream(s):
+    out = torch.empty(packed["host"].shape, dtype=packed["host"].dtype, device=packed["device"])
+    out.copy_(packed["host"], non_blocking=True)
     ev = torch.cuda.Event()
-    ev.record(engine.comm_stream)
-  t.record_stream(engine.comm_stream)
-  return host, ev, t.device
+    ev.record(s)
+  packed["reloaded"], packed["event"] = out, ev
 
 
-def _reload_from_host(engine: FSDPEngine, packed):
-  host, ev, dev = packed
-  ev.synchronize()
-  return host.to(dev, non_blocking=True)
+def _reload_from_host(engine: FSDPEngine, u: Unit, packed):
+  """The saved input back on the device.  Nothing blocks the host: the compute stream waits for the
+  copy's event, and the copy for the unit that runs its backward next is started right away so that
+  it overlaps this unit's recomputation."""
+  _start_reload(engine, packed)
+  torch.cuda.current_stream().wait_event(packed["event"])
+  out = packed["reloaded"]
+  out.record_stream(torch.cuda.current_stream())
+  engine._offloaded.pop(u.index, None)
+  nxt = engine._offloaded.get(u.index - 1)
+  if nxt is not None:
+    _start_reload(engine, nxt)
+  return out
