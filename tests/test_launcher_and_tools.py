@@ -89,3 +89,59 @@ def test_aux_scripts_parse_arguments(tmp_path):
   log = tmp_path / "train.log"
   log.write_text("step 1 loss: 1.25\nstep 2 loss: 0.75 lr: 1e-4\n")
   assert draw.losses_from_log(str(log)) == [1.25, 0.75]
+
+
+def test_interactive_mode_reruns_on_file_change(tmp_path):
+  """``tp run -i``: a change to a watched source file stops the running workload and starts it again;
+  ignored paths (.gitignore) and other file types do not."""
+  from torchprime_b200.launcher import cli
+  (tmp_path / ".gitignore").write_text("outputs/\n*.log\n")
+  (tmp_path / "train.py").write_text("x = 1\n")
+  (tmp_path / "outputs").mkdir()
+  (tmp_path / "outputs" / "gen.py").write_text("ignored\n")
+  w = cli.FileChangeWatcher(str(tmp_path))
+  assert w.changed() == []
+  (tmp_path / "outputs" / "gen.py").write_text("still ignored\n")
+  (tmp_path / "notes.txt").write_text("not a source file\n")
+  assert w.changed() == []
+  os.utime(tmp_path / "train.py", ns=(1, 1))
+  (tmp_path / "cfg.yaml").write_text("a: 1\n")
+  assert w.changed() == ["cfg.yaml", "train.py"]
+
+  class FakeProc:
+    def __init__(self):
+      self.returncode, self.stopped, self.pid = None, False, None
+    def poll(self):
+      return self.returncode
+    def terminate(self):
+      self.stopped, self.returncode = True, -15
+    def wait(self, timeout=None):
+      return self.returncode
+    def kill(self):
+      self.returncode = -9
+  procs, ticks = [], [0]
+
+  def start():
+    procs.append(FakeProc())
+    return procs[-1]
+
+  def fake_sleep(_s):
+    ticks[0] += 1
+    if ticks[0] == 2:
+      (tmp_path / "train.py").write_text("x = 2\n")     # edit while the first run is still going
+    if ticks[0] == 4:
+      procs[-1].returncode = 0                           # the second run finishes
+  rc = cli.run_interactive(start, w, poll_s=0.0, max_runs=2, sleep=fake_sleep)
+  assert rc == 0 and len(procs) == 2 and procs[0].stopped and not procs[1].stopped
+
+
+def test_save_hf_verbs_call_the_asset_tool(tmp_path, monkeypatch):
+  from torchprime_b200.launcher import cli, save_hf_assets
+  calls = []
+  monkeypatch.setattr(save_hf_assets, "save_repo", lambda repo, dest, types, token=None: calls.append(("repo", repo, dest, tuple(types))) or dest)
+  monkeypatch.setattr(save_hf_assets, "save_dataset", lambda name, cfg, dest, split, tok, bs: calls.append(("ds", name, cfg, split, tok, bs)) or dest)
+  assert cli.main(["save-hf-model-files", "--repo-id", "org/model", "--dest", str(tmp_path), "--file-type", "tokenizer"]) == 0
+  assert cli.main(["save-hf-dataset", "--dataset-name", "wikitext", "--dataset-config", "wikitext-2-raw-v1",
+                   "--dest", str(tmp_path), "--tokenizer", "org/model", "--block-size", "128"]) == 0
+  assert calls == [("repo", "org/model", str(tmp_path), ("tokenizer",)),
+                   ("ds", "wikitext", "wikitext-2-raw-v1", "train", "org/model", 128)]
