@@ -151,6 +151,13 @@ def test_mixtral_expert_parallel_orthogonal_matches_single():
   close(ep, single)
 
 
+def test_mixtral_tensor_parallel_matches_single():
+  """Attention heads and the experts' FFN dimension split over two ranks (router replicated)."""
+  single = run(1, MIX + ["ici_mesh.fsdp=1"])["traj"]
+  tp = run(2, MIX + ["ici_mesh.fsdp=1", "ici_mesh.tensor=2", "model/sharding=mixtral-fsdp-tp-ep"])["traj"]
+  close(tp, single)
+
+
 def test_resume_from_training_state(tmp_path):
   ov = LLAMA + ["ici_mesh.fsdp=2"]
   full = run(2, ov, steps=4, extra_action=f"save_at_2:{tmp_path}/ckpt")["traj"]

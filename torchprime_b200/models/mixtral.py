@@ -25,6 +25,7 @@ import torch.nn.functional as F
 from ..ops import functional as ops
 from ..ops import moe as moe_ops
 from ..ops import reference as ref
+from ..parallel.collectives import copy_to_tp, reduce_from_tp
 from ..utils.profiling import trace_scope
 from . import rope
 from .base import BaseCausalLM
@@ -83,6 +84,7 @@ class MixtralMoeBlock(nn.Module):
     else:
       raise NotImplementedError(f"Unsupported moe implementation {self.moe_implementation}")
     self.ep = None   # expert-parallel adaptor, set by the engine
+    self.tp_group = None   # set by the engine: experts split along the FFN dimension (w1/w3 columns, w2 rows)
 
   def load_balance_loss(self, top_k_indices, probs):
     """Switch-Transformer auxiliary loss: mean(fraction routed * mean probability) * E^2.
@@ -99,6 +101,11 @@ class MixtralMoeBlock(nn.Module):
       router_logits = ops.linear(x, self.gate.weight)
       weights, idx, probs = moe_ops.router_topk(router_logits, self.top_k, mode="softmax")
       weights = weights.to(x.dtype)
+      if self.tp_group is not None:
+        # every rank of the tensor group computes the experts on its slice of the FFN dimension: the
+        # outputs are partial sums (reduced below), and so are the gradients that flow back into the
+        # tokens and into the routing weights (summed by the backward of copy_to_tp)
+        x, weights = copy_to_tp(x, self.tp_group), copy_to_tp(weights, self.tp_group)
       loss = hidden_states.new_zeros((), dtype=torch.float32)
       impl = self.moe_implementation
       if impl == "static":
@@ -121,6 +128,8 @@ class MixtralMoeBlock(nn.Module):
           out = self.ep.grouped_mlp(x, weights, idx, w1, w3, w2, capacity=capacity, rows_per_group=s)
         else:
           out = moe_ops.grouped_mlp(x, weights, idx, w1, w3, w2, capacity=capacity, rows_per_group=s)
+      if self.tp_group is not None:
+        out = reduce_from_tp(out, self.tp_group)
       return out.reshape(b, s, d), router_logits, loss
 
 
@@ -186,6 +195,17 @@ class MixtralForCausalLM(BaseCausalLM):
   def param_init_kind(self, full_name, module, pname):
     if isinstance(module, MixtralStackedExperts):
       return "normal"
+    return None
+
+  def tp_layout(self, name: str):
+    """Dimension along which a tensor-parallel weight is split (None: replicated).  Attention: q/k/v
+    by heads (rows), o_proj by its input columns; stacked experts [E, D, F] / [E, F, D] along F."""
+    if ".self_attn." in name and name.endswith("_proj.weight"):
+      return 1 if ".o_proj." in name else 0
+    if name.endswith(("experts.w1", "experts.w3")):
+      return 2
+    if name.endswith("experts.w2"):
+      return 1
     return None
 
   def forward(self, input_ids, labels=None, attention_mask=None, position_ids=None, segment_ids=None,

@@ -43,6 +43,23 @@ def _round_up(x: int, m: int) -> int:
   return (x + m - 1) // m * m
 
 
+def tp_slice(val: torch.Tensor, dim: int, tp: int, rank: int, blocks: int = 1) -> torch.Tensor:
+  """Rank ``rank``'s tensor-parallel slice of ``val`` along ``dim``.  ``blocks`` > 1: the dimension holds
+  that many equal blocks back to back (a fused [gate | up] projection) and every rank takes its slice of
+  each block, so that the local tensor is again [gate_r | up_r]."""
+  if blocks == 1:
+    return val.chunk(tp, dim=dim)[rank]
+  return torch.cat([b.chunk(tp, dim=dim)[rank] for b in val.chunk(blocks, dim=dim)], dim=dim)
+
+
+def tp_unslice(parts, dim: int, blocks: int = 1) -> torch.Tensor:
+  """Inverse of :func:`tp_slice` given every rank's slice in rank order."""
+  if blocks == 1:
+    return torch.cat(parts, dim=dim)
+  per = [p.chunk(blocks, dim=dim) for p in parts]
+  return torch.cat([torch.cat([pr[b] for pr in per], dim=dim) for b in range(blocks)], dim=dim)
+
+
 @dataclass
 class _ParamSlot:
   name: str            # full name in the model state dict
@@ -56,6 +73,7 @@ class _ParamSlot:
   owner: nn.Module | None = None
   attr: str = ""
   ep_dim: int | None = None
+  tp_blocks: int = 1         # fused blocks along tp_dim that are sliced one by one (see tp_slice)
   local: bool = False        # expert-parallel slice owned by this rank only (not gathered)
   local_offset: int = 0      # offset inside the engine-wide local region
 
@@ -184,6 +202,8 @@ class FSDPEngine:
     return "normal" if pname != "bias" else "zeros"
 
   def _tp_sliceable(self, name: str) -> bool:
+    if getattr(self.model, "tp_layout", None) is not None:
+      return True                  # the model's tp_layout decides per parameter
     fn = getattr(self.model, "tp_sliceable", None)
     if fn is not None:
       return bool(fn(name))
@@ -206,14 +226,25 @@ class FSDPEngine:
             continue
           claimed.add(id(p))
           full_name = name_of.get(id(p), f"{uname}.{sub_name}.{pname}".strip("."))
-          tp_dim = None
+          tp_dim, tp_blocks = None, 1
           if self.plan is not None and self.tp > 1 and self._tp_sliceable(full_name):
             tp_dim = self.plan.tp_dim(full_name)
+            layout = getattr(self.model, "tp_layout", None)
+            if tp_dim is not None and layout is not None:
+              # The sharding config says WHETHER a weight is tensor-parallel.  Models whose configs
+              # describe hidden-dimension sharding (meant for a partitioning compiler) name the
+              # dimension their explicit column- / row-parallel forward splits instead.
+              got = layout(full_name)
+              if got is None:
+                tp_dim = None
+              else:
+                tp_dim, tp_blocks = (got, 1) if isinstance(got, int) else got
           ep_dim = self.plan.ep_dim(full_name) if (self.plan is not None and self.ep > 1) else None
           full_shape = p.shape
           shape = list(p.shape)
           if tp_dim is not None:
-            assert shape[tp_dim] % self.tp == 0, f"{full_name} dim {tp_dim} not divisible by tensor={self.tp}"
+            assert shape[tp_dim] % (self.tp * tp_blocks) == 0, (
+              f"{full_name} dim {tp_dim} not divisible by tensor={self.tp} x {tp_blocks} blocks")
             shape[tp_dim] //= self.tp
           if ep_dim is not None:
             assert shape[ep_dim] % self.ep == 0, f"{full_name} dim {ep_dim} not divisible by expert={self.ep}"
@@ -222,7 +253,7 @@ class FSDPEngine:
           n = math.prod(shape)
           slot = _ParamSlot(full_name, p, shape, n, off, self._init_kind(sub, pname, full_name),
                             tp_dim=tp_dim, full_shape=full_shape, owner=sub, attr=pname, ep_dim=ep_dim,
-                            local=ep_dim is not None)
+                            local=ep_dim is not None, tp_blocks=tp_blocks)
           u.slots.append(slot)
           if slot.local:
             slot.local_offset = self.local_total
@@ -328,7 +359,7 @@ class FSDPEngine:
         else:
           val = s.param.data.to(device=self.device, dtype=torch.float32)
         if s.tp_dim is not None:
-          val = val.chunk(self.tp, dim=s.tp_dim)[self.tp_rank]
+          val = tp_slice(val, s.tp_dim, self.tp, self.tp_rank, s.tp_blocks)
         if s.local:
           val = val.chunk(self.ep, dim=s.ep_dim)[self.ep_rank].reshape(-1)
           lo_l = self.sharded_total + s.local_offset
@@ -739,7 +770,7 @@ class FSDPEngine:
         if s.tp_dim is not None and tp_group is not None:
           parts = [torch.empty_like(t) for _ in range(self.tp)]
           dist.all_gather(parts, t.contiguous(), group=tp_group)
-          t = torch.cat(parts, dim=s.tp_dim)
+          t = tp_unslice(parts, s.tp_dim, s.tp_blocks)
         if keep is not None and not keep(s.name):
           continue
         t = t.to(dtype) if dtype is not None else t
@@ -775,7 +806,7 @@ class FSDPEngine:
           raise RuntimeError(f"size mismatch for {s.name}: checkpoint {tuple(val.shape)} vs model {tuple(s.full_shape)}")
         val = val.to(device=self.device, dtype=torch.float32)
         if s.tp_dim is not None:
-          val = val.chunk(self.tp, dim=s.tp_dim)[self.tp_rank]
+          val = tp_slice(val, s.tp_dim, self.tp, self.tp_rank, s.tp_blocks)
         if s.local:
           val = val.chunk(self.ep, dim=s.ep_dim)[self.ep_rank].reshape(-1)
           lo_l = self.sharded_total + s.local_offset

@@ -97,6 +97,12 @@ class ShardedOptimizerBase:
       ep_grp = e.mesh.group("expert") if (dist.is_initialized() and e.mesh is not None) else None
       if ep_grp is not None:
         dist.all_reduce(local_sq, group=ep_grp)
+      tp_grp = e.mesh.group("tensor") if (dist.is_initialized() and e.mesh is not None) else None
+      if tp_grp is not None and any(s.local and s.tp_dim is not None for u in e.units for s in u.slots):
+        # expert weights are sliced over the tensor group as well (all of them, or none)
+        assert all(s.tp_dim is not None for u in e.units for s in u.slots if s.local), (
+          "expert-parallel parameters must be all tensor-parallel or all replicated over the tensor axis")
+        dist.all_reduce(local_sq, group=tp_grp)
       g = g[:n_dense]
     self._sumsq.zero_()
     sumsq_into(self._sumsq, g)
