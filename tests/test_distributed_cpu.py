@@ -158,6 +158,22 @@ def test_mixtral_tensor_parallel_matches_single():
   close(tp, single)
 
 
+DSK = ["model=deepseek-tiny", "dataset.block_size=64", "task.global_batch_size=4"]
+
+
+def test_deepseek_tensor_parallel_matches_single():
+  """MLA heads, dense / shared MLPs and the grouped experts' FFN dimension split over two ranks; the
+  low-rank projections, their norms and the router stay replicated and must see full gradients."""
+  single = run(1, DSK + ["ici_mesh.fsdp=1"])["traj"]
+  tp = run(2, DSK + ["ici_mesh.fsdp=1", "ici_mesh.tensor=2"])["traj"]
+  close(tp, single)
+  both = run(2, DSK + ["ici_mesh.fsdp=1", "ici_mesh.tensor=2"], steps=1, extra_action="state_dict")["norm"]
+  one = run(1, DSK + ["ici_mesh.fsdp=1"], steps=1, extra_action="state_dict")["norm"]
+  assert one.keys() == both.keys()
+  for k in one:
+    assert abs(one[k] - both[k]) < 2e-4 * max(1.0, one[k]), k
+
+
 def test_resume_from_training_state(tmp_path):
   ov = LLAMA + ["ici_mesh.fsdp=2"]
   full = run(2, ov, steps=4, extra_action=f"save_at_2:{tmp_path}/ckpt")["traj"]

@@ -29,6 +29,7 @@ import torch.nn.functional as F
 from ..ops import functional as ops
 from ..ops import moe as moe_ops
 from ..ops import reference as ref
+from ..parallel.collectives import copy_to_tp, reduce_from_tp
 from ..utils.profiling import trace_scope
 from . import rope
 from .base import BaseCausalLM
@@ -47,10 +48,19 @@ class DeepseekV3MLP(nn.Module):
     self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
     self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
     self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
+    self.tp_group = None   # set by the engine: gate/up column-parallel, down row-parallel
 
-  def forward(self, x, residual=None):
-    act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight)
-    return ops.linear(act, self.down_proj.weight, residual=residual)
+  def forward(self, x, residual=None, partial=False):
+    """``partial`` (tensor parallel only): return this rank's partial sum, the caller reduces."""
+    if self.tp_group is None:
+      act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight)
+      return ops.linear(act, self.down_proj.weight, residual=residual)
+    act = ops.linear_swiglu(copy_to_tp(x, self.tp_group), self.gate_proj.weight, self.up_proj.weight)
+    y = ops.linear(act, self.down_proj.weight)
+    if partial:
+      return y
+    y = reduce_from_tp(y, self.tp_group)
+    return y if residual is None else y + residual
 
 
 class DeepseekV3TopkRouter(nn.Module):
@@ -99,6 +109,7 @@ class DeepseekV3MoE(nn.Module):
     self.use_gmm = bool(config.get("use_gmm_kernel_for_moe", True))
     self.num_experts = config.n_routed_experts
     self.ep = None
+    self.tp_group = None   # set by the engine: routed and shared experts split along their FFN dimension
 
   def forward(self, hidden_states, residual=None):
     with trace_scope("DeepseekV3MoE"):
@@ -106,6 +117,11 @@ class DeepseekV3MoE(nn.Module):
       x = hidden_states.reshape(-1, d)
       idx, w = self.gate(x)
       g = self.grouped
+      tp = self.tp_group
+      if tp is not None:
+        # partial sums over the FFN slices: gradients into the tokens and the routing weights are
+        # summed over the tensor group, routed + shared outputs are reduced once
+        x, w = copy_to_tp(x, tp), copy_to_tp(w, tp)
       if self.ep is not None:
         routed = self.ep.grouped_mlp(x, w, idx, g.W_gate, g.W_up, g.W_down)
       elif self.use_gmm:
@@ -113,6 +129,9 @@ class DeepseekV3MoE(nn.Module):
       else:
         routed = moe_ops.grouped_mlp_reference(x, w, idx, g.W_gate, g.W_up, g.W_down)
       routed = routed.reshape(b, s, d)
+      if tp is not None:
+        out = reduce_from_tp(routed + self.shared_experts(hidden_states, partial=True), tp)
+        return out if residual is None else out + residual
       if residual is not None:
         routed = routed + residual
       return self.shared_experts(hidden_states, residual=routed)
@@ -157,24 +176,31 @@ class DeepseekV3Attention(nn.Module):
       self.scaling = 1.0 / math.sqrt(self.v_head_dim)
     self.rope_interleave = bool(config.get("rope_interleave", True))
     self.attention_kernel = config.get("attention_kernel", None)
+    self.tp_group = None   # set by the engine: heads split (q_proj / q_b_proj / kv_b_proj rows, o_proj columns)
 
   def forward(self, x, rope_cos, rope_sin, residual=None, position_ids=None, segment_ids=None, cp=None):
     with trace_scope("DeepseekV3Attention"):
       b, s, _ = x.shape
-      h, dn, dr, dv = self.num_heads, self.qk_nope_head_dim, self.qk_rope_head_dim, self.v_head_dim
+      dn, dr, dv = self.qk_nope_head_dim, self.qk_rope_head_dim, self.v_head_dim
+      tp = self.tp_group
+      # Tensor parallel: the low-rank "a" projections and their norms are replicated; copy_to_tp sits
+      # right in front of the head-split GEMMs, so that the replicated parameters see gradients that are
+      # already summed over the ranks' heads.
+      to_tp = (lambda t: copy_to_tp(t, tp)) if tp is not None else (lambda t: t)
       if not self.q_lora_rank:
-        q = ops.linear(x, self.q_proj.weight)
+        q = ops.linear(to_tp(x), self.q_proj.weight)
       else:
-        q = ops.linear(self.q_a_layernorm(ops.linear(x, self.q_a_proj.weight, bias=self.q_a_proj.bias)),
+        q = ops.linear(to_tp(self.q_a_layernorm(ops.linear(x, self.q_a_proj.weight, bias=self.q_a_proj.bias))),
                        self.q_b_proj.weight)
+      h = q.shape[-1] // (dn + dr)      # local heads (all of them without tensor parallelism)
       # rotate the last dr columns of every (dn + dr)-wide query head
       q = ops.rope_slices(q, rope_cos, rope_sin, h, dr, s, col0=dn, head_stride=dn + dr, pos=position_ids,
                           interleaved=self.rope_interleave)
       ckv = ops.linear(x, self.kv_a_proj_with_mqa.weight, bias=self.kv_a_proj_with_mqa.bias)
       ckv = ops.rope_slices(ckv, rope_cos, rope_sin, 1, dr, s, col0=self.kv_lora_rank, head_stride=dr,
                             pos=position_ids, interleaved=self.rope_interleave)
-      k_lat, k_rot = ckv[..., : self.kv_lora_rank], ckv[..., self.kv_lora_rank:]
-      kv = ops.linear(self.kv_a_layernorm(k_lat.contiguous()), self.kv_b_proj.weight).view(b, s, h, dn + dv)
+      k_lat, k_rot = ckv[..., : self.kv_lora_rank], to_tp(ckv[..., self.kv_lora_rank:])
+      kv = ops.linear(to_tp(self.kv_a_layernorm(k_lat.contiguous())), self.kv_b_proj.weight).view(b, s, h, dn + dv)
       k_nope, v = kv[..., :dn], kv[..., dn:]
       k = torch.cat([k_nope, k_rot[:, :, None, :].expand(b, s, h, dr)], dim=-1)
       q4 = q.view(b, s, h, dn + dr)
@@ -186,6 +212,11 @@ class DeepseekV3Attention(nn.Module):
       else:
         o = ops.attention(q4, k, v, causal=True, scale=self.scaling, q_segment_ids=segment_ids)
       o = o.reshape(b, s, h * dv)
+      if tp is not None:
+        out = reduce_from_tp(ops.linear(o, self.o_proj.weight), tp)
+        if self.o_proj.bias is not None:
+          out = out + self.o_proj.bias
+        return out if residual is None else out + residual
       if self.o_proj.bias is not None:
         out = ops.linear(o, self.o_proj.weight, bias=self.o_proj.bias)
         return out if residual is None else out + residual
@@ -251,9 +282,26 @@ class DeepseekV3ForCausalLM(BaseCausalLM):
       return "normal"
     return None
 
-  def tp_sliceable(self, name: str) -> bool:
-    """The MLA projections and the MoE block are not tensor-parallel in this implementation."""
-    return False
+  def tp_layout(self, name: str):
+    """Dimension along which a tensor-parallel weight is split (None: replicated over the tensor axis).
+    The sharding configs of the reference describe hidden-dimension sharding for a partitioning
+    compiler (torchprime/torch_xla_models/configs/model/sharding/deepseek-fsdp-tp-ep.yaml:4-17); the
+    explicit forward here is column- / row-parallel: attention by heads (q_proj / q_b_proj / kv_b_proj
+    rows, o_proj columns; the low-rank ``*_a`` projections and their norms stay replicated), dense and
+    shared MLPs and the grouped experts along their FFN dimension."""
+    if ".self_attn." in name:
+      if name.endswith(("q_proj.weight", "q_b_proj.weight", "kv_b_proj.weight")):
+        return 0
+      return 1 if name.endswith("o_proj.weight") else None
+    if name.endswith(("gate_proj.weight", "up_proj.weight")):
+      return 0
+    if name.endswith("down_proj.weight"):
+      return 1
+    if name.endswith(("grouped.W_gate", "grouped.W_up")):
+      return 2
+    if name.endswith("grouped.W_down"):
+      return 1
+    return None
 
   def convert_loaded_state_dict(self, state: dict) -> dict:
     """HF checkpoints store one Linear triple per expert; fold them into the grouped tensors."""
