@@ -174,6 +174,23 @@ def test_deepseek_tensor_parallel_matches_single():
     assert abs(one[k] - both[k]) < 2e-4 * max(1.0, one[k]), k
 
 
+L4 = ["model=llama-4-text-only-dummy", "model.hidden_size=128", "model.num_attention_heads=4",
+      "model.num_key_value_heads=2", "model.head_dim=32", "model.intermediate_size=48",
+      "model.intermediate_size_mlp=96", "model.num_local_experts=4", "model.vocab_size=256",
+      "model.num_hidden_layers=3", "model.moe_layers=[0,2]", "model.no_rope_layers=[1,1,0]",
+      "model.floor_scale=16", "dataset.block_size=64", "task.global_batch_size=4"]
+
+
+@pytest.mark.parametrize("impl", ["original", "sequential", "expert_parallelism"])
+def test_llama4_tensor_parallel_matches_single(impl):
+  """Heads, the shared expert and the fused gate|up expert weights (sliced half by half) split over two
+  ranks, for every MoE formulation; the dense layer's MLP is not named by the config and stays whole."""
+  base = L4 + [f"model.moe_implementation={impl}"]
+  single = run(1, base + ["ici_mesh.fsdp=1"])["traj"]
+  tp = run(2, base + ["ici_mesh.fsdp=1", "ici_mesh.tensor=2", "model/sharding=llama4-fsdp-tp"])["traj"]
+  close(tp, single)
+
+
 def test_resume_from_training_state(tmp_path):
   ov = LLAMA + ["ici_mesh.fsdp=2"]
   full = run(2, ov, steps=4, extra_action=f"save_at_2:{tmp_path}/ckpt")["traj"]

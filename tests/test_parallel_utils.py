@@ -231,3 +231,15 @@ def test_fused_tensor_parallel_request_needs_the_kernel_path():
   with pytest.raises(RuntimeError):
     ops.linear_swiglu(x, w, w.clone(), tp_reduce_grad=Reducer())
   assert ops.linear(x, w).shape == (4, 16)
+
+
+def test_tp_slice_of_fused_blocks_round_trips():
+  """A fused [gate | up] dimension is sliced half by half: every rank holds [gate_r | up_r]."""
+  import torch
+  from torchprime_b200.parallel.fsdp import tp_slice, tp_unslice
+  w = torch.arange(2 * 3 * 8).view(2, 3, 8)              # last dim = [gate(4) | up(4)]
+  parts = [tp_slice(w, 2, 2, r, blocks=2) for r in range(2)]
+  assert parts[0][0, 0].tolist() == [0, 1, 4, 5] and parts[1][0, 0].tolist() == [2, 3, 6, 7]
+  assert torch.equal(tp_unslice(parts, 2, blocks=2), w)
+  plain = [tp_slice(w, 1, 3, r) for r in range(3)]
+  assert plain[1].shape == (2, 1, 8) and torch.equal(tp_unslice(plain, 1), w)

@@ -25,6 +25,7 @@ import torch.nn.functional as F
 from ..ops import functional as ops
 from ..ops import moe as moe_ops
 from ..ops import reference as ref
+from ..parallel.collectives import copy_to_tp, reduce_from_tp
 from ..utils.profiling import trace_scope
 from . import rope
 from .base import BaseCausalLM
@@ -55,10 +56,20 @@ class Llama4TextMLP(nn.Module):
     self.gate_proj = nn.Linear(config.hidden_size, inter, bias=False)
     self.up_proj = nn.Linear(config.hidden_size, inter, bias=False)
     self.down_proj = nn.Linear(inter, config.hidden_size, bias=False)
+    self.tp_group = None
 
-  def forward(self, x):
-    act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight)
-    return ops.linear(act, self.down_proj.weight)
+  def forward(self, x, partial=False):
+    """Tensor parallel (``tp_group`` set by the engine): gate/up column-parallel, down row-parallel;
+    ``partial`` returns this rank's partial sum for a caller that reduces it with other terms."""
+    tp = getattr(self, "tp_group", None)
+    if tp is not None and self.gate_proj.weight.shape[0] == self.gate_proj.out_features:
+      tp = None        # this MLP's weights are not named by the sharding config: replicated, nothing to reduce
+    if tp is None:
+      act = ops.linear_swiglu(x, self.gate_proj.weight, self.up_proj.weight)
+      return ops.linear(act, self.down_proj.weight)
+    act = ops.linear_swiglu(copy_to_tp(x, tp), self.gate_proj.weight, self.up_proj.weight)
+    y = ops.linear(act, self.down_proj.weight)
+    return y if partial else reduce_from_tp(y, tp)
 
 
 class Llama4TextExperts(nn.Module):
@@ -93,6 +104,17 @@ class Llama4TextMoe(nn.Module):
     self.router = nn.Linear(config.hidden_size, config.num_local_experts, bias=False)
     self.shared_expert = Llama4TextMLP(config)
     self.ep = None
+    self.tp_group = None   # set by the engine: experts and the shared expert split along the FFN dimension
+
+  def _to_tp(self, t):
+    """In front of a tensor-parallel GEMM: identity forward, gradient summed over the tensor group."""
+    return t if self.tp_group is None else copy_to_tp(t, self.tp_group)
+
+  def _finish(self, x, routed):
+    """shared expert + routed experts; with tensor parallelism both are partial sums, reduced once."""
+    if self.tp_group is None:
+      return self.shared_expert(x) + routed
+    return reduce_from_tp(self.shared_expert(x, partial=True) + routed, self.tp_group)
 
   def route(self, x):
     logits = F.linear(x, self.router.weight)
@@ -105,10 +127,9 @@ class Llama4TextMoe(nn.Module):
       logits, top_v, top_i = self.route(x)
       scores = torch.full_like(logits, float("-inf")).scatter_(1, top_i, top_v).transpose(0, 1)
       scores = torch.sigmoid(scores.float()).to(x.dtype)
-      routed_in = x.repeat(self.num_experts, 1) * scores.reshape(-1, 1)
+      routed_in = self._to_tp(x.repeat(self.num_experts, 1) * scores.reshape(-1, 1))
       routed_out = self.experts(routed_in)
-      out = self.shared_expert(x)
-      out = out + routed_out.reshape(self.num_experts, -1, self.hidden_dim).sum(dim=0)
+      out = self._finish(x, routed_out.reshape(self.num_experts, -1, self.hidden_dim).sum(dim=0))
       return out, scores
 
 
@@ -118,12 +139,13 @@ class Llama4TextMoeSequential(Llama4TextMoe):
       x = hidden_states.reshape(-1, self.hidden_dim)
       logits, top_v, top_i = self.route(x)
       sparse = torch.sigmoid(torch.full_like(logits, float("-inf")).scatter_(1, top_i, top_v).float()).to(x.dtype)
-      out = self.shared_expert(x)
+      x_tp, sparse_tp = self._to_tp(x), self._to_tp(sparse)
+      routed = 0
       for i in range(self.num_experts):
-        gu = (x @ self.experts.gate_up_proj[i]) * sparse[:, i:i + 1]
+        gu = (x_tp @ self.experts.gate_up_proj[i]) * sparse_tp[:, i:i + 1]
         gate, up = gu.chunk(2, dim=-1)
-        out = out + (up * F.silu(gate)) @ self.experts.down_proj[i]
-      return out, sparse.transpose(0, 1)
+        routed = routed + (up * F.silu(gate)) @ self.experts.down_proj[i]
+      return self._finish(x, routed), sparse.transpose(0, 1)
 
 
 class Llama4TextMoeExpertParallelism(Llama4TextMoe):
@@ -134,10 +156,10 @@ class Llama4TextMoeExpertParallelism(Llama4TextMoe):
       x = hidden_states.reshape(-1, self.hidden_dim)
       logits, top_v, top_i = self.route(x)
       score = torch.sigmoid(top_v.float()).to(x.dtype)                      # [T, K]
-      out = self.shared_expert(x)
+      out = 0
       ones = torch.ones(x.shape[0], 1, dtype=torch.float32, device=x.device)
       for k in range(self.top_k):                                           # Llama-4 uses top-1
-        xin = x * score[:, k:k + 1]
+        xin = self._to_tp(x * score[:, k:k + 1])
         idx = top_i[:, k:k + 1].to(torch.int32)
         if self.ep is not None:
           routed = self.ep.grouped_mlp(xin, ones, idx, self.experts.gate_up_proj, None, self.experts.down_proj,
@@ -147,7 +169,7 @@ class Llama4TextMoeExpertParallelism(Llama4TextMoe):
                                        fused_gate_up=True)
         out = out + routed
       scores = torch.sigmoid(torch.full_like(logits, float("-inf")).scatter_(1, top_i, top_v).float()).to(x.dtype)
-      return out, scores.transpose(0, 1)
+      return self._finish(x, out), scores.transpose(0, 1)
 
 
 _MOE_IMPLS = {"original": Llama4TextMoe, "sequential": Llama4TextMoeSequential,
@@ -180,11 +202,15 @@ class Llama4TextAttention(nn.Module):
     if config.get("use_qk_norm", False) and self.use_rope:
       self.qk_norm = Llama4TextL2Norm(config.rms_norm_eps)
     self.attention_kernel = config.get("attention_kernel", None)
+    self.tp_group = None   # set by the engine: q/k/v column-parallel (heads split), o row-parallel
 
   def forward(self, x, rope_cos, rope_sin, position_ids=None, segment_ids=None):
     with trace_scope("Llama4TextAttention"):
       b, s, _ = x.shape
-      hq, hkv, d = self.num_attention_heads, self.num_key_value_heads, self.head_dim
+      d = self.head_dim
+      hq, hkv = self.q_proj.weight.shape[0] // d, self.k_proj.weight.shape[0] // d   # local heads
+      if self.tp_group is not None:
+        x = copy_to_tp(x, self.tp_group)
       bias = None
       if self.q_proj.bias is not None:
         bias = torch.cat([self.q_proj.bias, self.k_proj.bias, self.v_proj.bias])
@@ -204,6 +230,9 @@ class Llama4TextAttention(nn.Module):
         o = ref.attention(q, k, v, causal=True, scale=self.scaling, q_segment_ids=segment_ids)
       else:
         o = ops.attention(q, k, v, causal=True, scale=self.scaling, q_segment_ids=segment_ids)
+      if self.tp_group is not None:
+        out = reduce_from_tp(ops.linear(o.reshape(b, s, hq * d), self.o_proj.weight), self.tp_group)
+        return out if self.o_proj.bias is None else out + self.o_proj.bias
       return ops.linear(o.reshape(b, s, hq * d), self.o_proj.weight, bias=self.o_proj.bias)
 
 
@@ -275,8 +304,23 @@ class Llama4TextForCausalLM(BaseCausalLM):
       return "normal"
     return None
 
-  def tp_sliceable(self, name: str) -> bool:
-    return False
+  def tp_layout(self, name: str):
+    """Dimension along which a tensor-parallel weight is split (None: replicated over the tensor axis);
+    ``(dim, 2)`` for the fused ``gate_up_proj [E, D, 2F]``, whose gate and up halves are sliced one by
+    one.  The reference's configs (llama4-fsdp-tp-ep.yaml:17-19) put ``tensor`` on the hidden dimension
+    of the expert weights for its partitioning compiler; the explicit forward here splits the FFN
+    dimension, which needs one reduction per block instead of one per GEMM."""
+    if ".self_attn." in name and name.endswith("_proj.weight"):
+      return 1 if ".o_proj." in name else 0
+    if name.endswith("experts.gate_up_proj"):
+      return (2, 2)
+    if name.endswith("experts.down_proj"):
+      return 1
+    if name.endswith(("gate_proj.weight", "up_proj.weight")):
+      return 0
+    if name.endswith("down_proj.weight"):
+      return 1
+    return None
 
   def forward(self, input_ids, labels=None, attention_mask=None, position_ids=None, segment_ids=None,
               labels_are_shifted=False):
