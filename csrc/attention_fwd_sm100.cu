@@ -451,7 +451,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 //   warp 0      TMA producer: both Q tiles once, then 2-stage rings of 128-key K and V tiles.
 //   warp 1      MMA issuer.  Per step j and tile x: O_x += P_x(j) V_j, then S_x(j+1) = Q_x K_{j+1}^T
 //               into the columns P_x(j) has just been read from (S and P share TMEM columns).
-//   warps 2-5   softmax of tile a (thread = query row), warps 6-9 softmax of tile b.
+//   warps 4-7   softmax of tile a (thread = query row), warps 8-11 softmax of tile b (warps 2-3 idle:
+//               roles are laid out by warpgroup so that registers can move between them).
 //   TMEM        S_a [0,128)  S_b [128,256)  O_a [256,384)  O_b [384,512)
 // ------------------------------------------------------------------------------------------
 // 2^x for x <= 0 on the FMA pipe (no MUFU): round-to-nearest split x = n + f with the 1.5 * 2^23
@@ -468,7 +469,9 @@ __device__ __forceinline__ float exp2_fma(float x) {
 }
 
 constexpr int F2_T = 128;                 // tile edge: rows per query tile, keys per step
-constexpr int F2_THREADS = 320;
+constexpr int F2_THREADS = 384;            // warpgroup 0: TMA + MMA warps (two idle), warpgroups 1 / 2: softmax of tile a / b
+// 128 x 56 + 256 x 224 = 64512 registers: within the SM's 65536, so the `inc` below cannot block
+constexpr int F2_REGS_IO = 56, F2_REGS_SOFTMAX = 224;
 constexpr int F2_TILE_BYTES = F2_T * 128 * 2;   // 32 KB
 namespace f2 {
 constexpr int OFF_Q = 0;                          // two tiles
@@ -550,6 +553,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int nblk = any ? blk_hi - blk_lo : 0;
   auto active = [&](int x, int j) { const int blk = blk_lo + j; return blk >= lo[x] && blk < hi[x]; };
 
+  // a softmax thread keeps the 128 scores of its row in registers: the copy / MMA warpgroup hands its
+  // registers over (with 168 per thread for everybody the scores spilled to local memory)
+  if (warp < 4) {
+  setmaxnreg_dec<F2_REGS_IO>();
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0 && nblk > 0) {
@@ -642,9 +649,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (jn < nblk) tc_commit(&k_empty[jn & 1]);
       }
     }
+  }
   } else {
+    setmaxnreg_inc<F2_REGS_SOFTMAX>();
     // ------------------------------------------------------------------ softmax + epilogue
-    const int x = (warp - 2) >> 2;                // query tile of this warp
+    const int x = (warp - 4) >> 2;                // query tile of this warp
     const int q = warp & 3;                       // TMEM lane quarter
     const int r_local = q * 32 + lane;
     const int row = q0 + x * F2_T + r_local;
@@ -728,7 +737,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       // P = exp2(s * c - m), packed bf16 over the first 64 of the 128 score columns (masked scores
       // are -inf and give exactly 0)
       // The exponentials of one step cost 2048 MUFU cycles per scheduler for the two tiles, as much
-      // as the step's MMAs; every fourth one is evaluated on the FMA pipe instead (exp2_fma).
+      // as the step's MMAs; every second one is evaluated on the FMA pipe instead (exp2_fma).
       float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ch = 0; ch < 4; ++ch) {
@@ -737,7 +746,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 0; c < 32; c += 4) {
           const float p0 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c]), p.scale_log2, -m_safe));
           const float p1 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 1]), p.scale_log2, -m_safe));
-          const float p2 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 2]), p.scale_log2, -m_safe));
+          const float p2 = exp2_fma(fmaf(__uint_as_float(r[ch * 32 + c + 2]), p.scale_log2, -m_safe));
           const float p3 = exp2_fma(fmaf(__uint_as_float(r[ch * 32 + c + 3]), p.scale_log2, -m_safe));
           sums[0] += p0; sums[1] += p1; sums[2] += p2; sums[3] += p3;
           pk[c / 2] = pack_bf16(p0, p1);

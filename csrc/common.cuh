@@ -43,6 +43,19 @@ __device__ __forceinline__ void report(int* st, int code, int where) {
   }
 }
 
+// Register re-allocation between the warpgroups (four consecutive, aligned warps) of a CTA: a
+// warpgroup that only issues copies or MMAs gives registers back, the ones that hold a row of
+// scores per thread take them.  Every warp of the warpgroup must execute the same instruction, and
+// the sum over the CTA must stay within the 64 K registers of the SM or `inc` never returns.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }

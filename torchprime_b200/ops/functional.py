@@ -87,13 +87,22 @@ def _grad_sink(weights):
   return _fused_view(mgs)
 
 
+def overwrites_grad(w) -> bool:
+  """Whether the gradient about to be delivered replaces the content of ``w.main_grad`` (first
+  gradient of the step) or adds to it.  A backward pass that is being captured into a CUDA graph is
+  replayed once per step, so what it records is always the overwriting form."""
+  if w.is_cuda and torch.cuda.is_current_stream_capturing():
+    return True
+  return bool(getattr(w, "grad_overwrite", False))
+
+
 def _wgrad_into(sink, weights, dy2, x2):
   """dW = dy2^T @ x2 written into the main_grad sink (overwrite or accumulate).  Under the FSDP
   engine's peer-memory collectives the parameters carry ``rs_push``: the GEMM epilogue then stores
   the tiles straight into the staging slots of the ranks that own those rows of the flat gradient
   buffer (the reduce-scatter's send side) instead of into the local buffer."""
   from . import kernels as k
-  overwrite = all(getattr(w, "grad_overwrite", False) for w in weights)
+  overwrite = all(overwrites_grad(w) for w in weights)
   push = getattr(weights[0], "rs_push", None)
   if push is not None:
     if overwrite and all(getattr(w, "rs_push", None) is not None for w in weights) and push(sink, dy2, x2):
@@ -321,7 +330,7 @@ def _norm_wgrad(w, dw_f32):
   mg = getattr(w, "main_grad", None)
   if mg is None:
     return dw_f32.to(w.dtype)
-  overwrite = getattr(w, "grad_overwrite", False)
+  overwrite = overwrites_grad(w)
   if mg.dtype == torch.float32:
     mg.copy_(dw_f32) if overwrite else mg.add_(dw_f32)
   elif mg.numel() % 4 == 0:

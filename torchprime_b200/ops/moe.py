@@ -259,7 +259,8 @@ def _deliver_wgrad(w, compute):
   """Run ``compute(out, accumulate)`` into ``w.main_grad`` when present, else return a fresh gradient."""
   mg = getattr(w, "main_grad", None)
   if mg is not None:
-    compute(mg, not getattr(w, "grad_overwrite", False))
+    from .functional import overwrites_grad
+    compute(mg, not overwrites_grad(w))
     w.grad_overwrite = False
     return None
   g = torch.empty(w.shape, dtype=torch.bfloat16, device=w.device)

@@ -93,6 +93,7 @@ class Unit:
   terminal: bool = False
   offload: bool = False
   big: bool = False         # has dedicated gather / grad buffers
+  graphable: bool = False   # replayed from CUDA graphs (engine.cuda_graphs)
   orig_forward: object = None
   # runtime state
   gathered: torch.Tensor | None = None
@@ -107,7 +108,7 @@ class FSDPEngine:
                init_std: float | None = None, seed: int = 42, materialize: bool | None = None,
                fused_collectives: bool = False, remat_policy: str | int = "all",
                fused_expert_exchange: bool = False, collectives: str = "nccl",
-               keep_gathered: str | bool = "auto"):
+               keep_gathered: str | bool = "auto", cuda_graphs: bool = False):
     self.model = model
     self.mesh = mesh
     self.plan = plan
@@ -164,6 +165,14 @@ class FSDPEngine:
     self._keep_gathered_req = keep_gathered
     self.keep_gathered = False
     self._param_version = 0
+    # Replay every layer of the homogeneous stack from CUDA graphs (the compile-once layer loop of the
+    # reference, torchprime/torch_xla_models/scan_layers.py:50-81): the first step runs eagerly and
+    # records the layers' argument shapes, then one forward and one backward graph per layer are captured
+    # and every later step launches two graphs per layer instead of a few hundred kernels.
+    self.cuda_graphs = bool(cuda_graphs)
+    self._graphs_ready = False
+    if self.cuda_graphs and self.remat_policy == "auto":
+      self.remat_policy = "none"      # the graphs' memory pool holds the activations of every layer
     self._build_units()
     self._allocate()
     needs_init = materialize if materialize is not None else any(
@@ -269,6 +278,15 @@ class FSDPEngine:
       self.units.append(u)
     if hasattr(model, "fsdp_units") and self.units:
       self.units[-1].terminal = True
+    if self.cuda_graphs:
+      if not (self.is_cuda and self.fsdp == 1 and self.ep == 1 and self.tp == 1 and not self.remat_classes_active()):
+        logger.warning("engine.cuda_graphs needs one CUDA rank per model replica (fsdp = tensor = expert = 1) and "
+                       "activations kept (engine.remat_layers=none): running the layers eagerly")
+        self.cuda_graphs = False
+      else:
+        kinds = [type(u.module).__name__ for u in self.units]
+        for u in self.units[:-1]:
+          u.graphable = kinds.count(type(u.module).__name__) >= 2      # the layers of the stack
     unclaimed = [n for n, p in model.named_parameters() if id(p) not in claimed]
     assert not unclaimed, f"parameters outside every FSDP unit: {unclaimed[:5]}"
     # layer-sized units share a two-slot buffer pool; larger ones get their own buffers
@@ -433,6 +451,27 @@ class FSDPEngine:
           mod.ep = ExpertParallelMLP(self.mesh, mod.num_experts,
                                      fused_exchange=self.fused_expert_exchange and self.is_cuda)
 
+  def capture_unit_graphs(self):
+    """Capture one forward and one backward CUDA graph per graphable unit (all of them at once, so that
+    they share one memory pool).  Runs at the start of the second step: every unit has been called once
+    and has recorded its arguments; the gradient buffers hold last step's values, which the warm-up
+    passes of the capture may overwrite."""
+    units = [u for u in self.units if getattr(u, "graphable", False) and getattr(u, "_graph_module", None) is not None]
+    mods = tuple(u._graph_module for u in units)
+    samples = []
+    for u in units:
+      ts = u._graph_module.tensors_of(u._graph_module._args, u._graph_module._kwargs)
+      samples.append(tuple(torch.zeros_like(t).requires_grad_(t.requires_grad) if t.is_floating_point()
+                           else t.clone() for t in ts))
+    for m in mods:      # the recorded tensors were only needed for their shapes
+      m._args = [None if isinstance(a, torch.Tensor) else a for a in m._args]
+      m._kwargs = {k: (None if isinstance(v, torch.Tensor) else v) for k, v in m._kwargs.items()}
+    graphed = torch.cuda.make_graphed_callables(mods, tuple(samples), allow_unused_input=True)
+    for u, g in zip(units, graphed):
+      u._graphed = g
+    self._graphs_ready = True
+    logger.info("captured CUDA graphs for %d units", len(units))
+
   def close(self):
     """Collective: give back the peer-mapped buffers (they are not owned by torch's allocator)."""
     if self.comm is not None:
@@ -583,6 +622,10 @@ class FSDPEngine:
     kept = sum(1 for x in self.units if x.keep)
     u.keep = (kept + 1) * self._remat_unit_bytes <= usable
     return u.keep
+
+  def remat_classes_active(self) -> bool:
+    """True when some unit will recompute its forward in backward."""
+    return bool(self.remat_classes) and self.remat_policy != "none"
 
   def note_saved_unit_bytes(self, nbytes: int):
     self._remat_unit_bytes = max(int(nbytes), 1)
@@ -847,6 +890,10 @@ def _run_unit(engine: FSDPEngine, u: Unit, args, kwargs):
   if u.terminal and kwargs.get("want_logits", None) is False or (
       u.terminal and len(args) >= 3 and args[2] is False):
     return _TerminalFn.apply(engine, u, kwargs, engine._dummy, *args)
+  if engine.cuda_graphs and getattr(u, "graphable", False):
+    out = _run_unit_graphed(engine, u, args, kwargs)
+    if out is not _NOT_GRAPHED:
+      return out
   if not u.remat:
     # fsdp == 1 and no remat requested: plain autograd through the unit
     for s in u.slots:
@@ -855,6 +902,56 @@ def _run_unit(engine: FSDPEngine, u: Unit, args, kwargs):
   if engine.keep_activations(u) and any(isinstance(a, torch.Tensor) and a.requires_grad for a in args):
     return _run_unit_saved(engine, u, args, kwargs)
   return _RematFn.apply(engine, u, kwargs, engine._dummy, *args)
+
+
+_NOT_GRAPHED = object()
+
+
+class _UnitGraphModule(nn.Module):
+  """What gets captured for one unit: its forward on tensor arguments only (everything else that the
+  first eager call passed is held constant).  Being a Module, its parameters are part of the captured
+  input surface, so their storage (views into the engine's flat buffers) must not move."""
+
+  def __init__(self, unit: Unit, args, kwargs):
+    super().__init__()
+    self.inner = unit.module
+    self._fwd = unit.orig_forward
+    self._args, self._kwargs = list(args), dict(kwargs)
+    self._slots = [("a", i) for i, a in enumerate(args) if isinstance(a, torch.Tensor)]
+    self._slots += [("k", k) for k, v in kwargs.items() if isinstance(v, torch.Tensor)]
+
+  def tensors_of(self, args, kwargs):
+    return tuple(args[i] if kind == "a" else kwargs[i] for kind, i in self._slots)
+
+  def signature_of(self, args, kwargs):
+    sig = []
+    for a in list(args) + [kwargs[k] for k in sorted(kwargs)]:
+      sig.append((tuple(a.shape), a.dtype, a.requires_grad) if isinstance(a, torch.Tensor) else a)
+    return sig
+
+  def forward(self, *tensors):
+    args, kwargs = list(self._args), dict(self._kwargs)
+    for (kind, i), t in zip(self._slots, tensors):
+      if kind == "a":
+        args[i] = t
+      else:
+        kwargs[i] = t
+    return self._fwd(*args, **kwargs)
+
+
+def _run_unit_graphed(engine: FSDPEngine, u: Unit, args, kwargs):
+  """Eager on the first step (recording the call), graphs afterwards.  Returns ``_NOT_GRAPHED`` when the
+  call does not match what was captured (another shape, evaluation with other arguments)."""
+  holder = getattr(u, "_graph_module", None)
+  if holder is None:
+    u._graph_module = _UnitGraphModule(u, args, kwargs)
+    u._graph_sig = u._graph_module.signature_of(args, kwargs)
+    return _NOT_GRAPHED
+  if holder.signature_of(args, kwargs) != u._graph_sig:
+    return _NOT_GRAPHED
+  if not engine._graphs_ready:
+    engine.capture_unit_graphs()
+  return u._graphed(*holder.tensors_of(args, kwargs))
 
 
 def _run_unit_saved(engine: FSDPEngine, u: Unit, args, kwargs):

@@ -106,7 +106,8 @@ class Trainer:
       seed=int(self.config.get("seed", 42)), fused_collectives=bool(eng.get("fused_collectives", False)),
       remat_policy=_remat_policy(eng.get("remat_layers", "auto")),
       fused_expert_exchange=bool(eng.get("fused_expert_exchange", False)),
-      collectives=str(eng.get("fsdp_collectives", "auto")), keep_gathered=eng.get("keep_gathered", "auto"))
+      collectives=str(eng.get("fsdp_collectives", "auto")), keep_gathered=eng.get("keep_gathered", "auto"),
+      cuda_graphs=bool(eng.get("cuda_graphs", False)))
     _move_buffers(model, self.device)
     if hasattr(model, "return_logits"):
       model.return_logits = not bool(eng.get("chunked_ce", True))
