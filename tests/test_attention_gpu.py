@@ -38,6 +38,8 @@ FWD_CASES = [
   (1, 1024, 4, 1, 128, True, None),
   (1, 512, 2, 1, 128, True, 100),
   (1, 256, 2, 2, 192, True, None),
+  (2, 2048, 4, 2, 128, True, None),     # several batch rows at a length with many key blocks
+  (1, 8192, 4, 1, 128, True, None),     # the training sequence length
 ]
 
 
@@ -79,6 +81,8 @@ BWD_CASES = [
   (1, 320, 2, 1, 128, False, None),
   (1, 512, 2, 1, 128, True, 100),
   (1, 256, 2, 2, 192, True, None),
+  (2, 2048, 4, 2, 128, True, None),
+  (1, 8192, 2, 1, 128, True, None),     # the training sequence length
 ]
 
 
