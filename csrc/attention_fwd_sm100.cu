@@ -746,7 +746,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int c = 0; c < 32; c += 4) {
           const float p0 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c]), p.scale_log2, -m_safe));
           const float p1 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 1]), p.scale_log2, -m_safe));
-          const float p2 = exp2_fma(fmaf(__uint_as_float(r[ch * 32 + c + 2]), p.scale_log2, -m_safe));
+          const float p2 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 2]), p.scale_log2, -m_safe));
           const float p3 = exp2_fma(fmaf(__uint_as_float(r[ch * 32 + c + 3]), p.scale_log2, -m_safe));
           sums[0] += p0; sums[1] += p1; sums[2] += p2; sums[3] += p3;
           pk[c / 2] = pack_bf16(p0, p1);
