@@ -24,11 +24,23 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// cuTensorMapEncodeTiled is a driver call and needs the device's primary context to be current on the
+// calling thread.  A thread that has only had its device selected (an autograd worker whose first
+// operation is one of this library's GEMMs) has none yet: a runtime call binds it, once per thread.
+static void bind_context_once() {
+  thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 // 2-D map: dims {inner, outer}, row pitch in elements, box {box_inner, box_outer}, 128B swizzle.
 int make_tmap_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint64_t pitch_elems,
                  uint32_t box_inner, uint32_t box_outer, int elem_bytes) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return -1;
+  bind_context_once();
   cuuint64_t dims[2] = {inner, outer};
   cuuint64_t strides[1] = {pitch_elems * elem_bytes};
   cuuint32_t box[2] = {box_inner, box_outer};
@@ -45,6 +57,7 @@ int make_tmap_3d(CUtensorMap* map, const void* ptr, uint64_t d0, uint64_t d1, ui
                  uint64_t stride2_elems, uint32_t box0, uint32_t box1) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return -1;
+  bind_context_once();
   cuuint64_t dims[3] = {d0, d1, d2};
   cuuint64_t strides[2] = {stride1_elems * 2, stride2_elems * 2};
   cuuint32_t box[3] = {box0, box1, 1};
