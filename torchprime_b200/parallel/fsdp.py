@@ -907,14 +907,16 @@ def _run_unit(engine: FSDPEngine, u: Unit, args, kwargs):
 _NOT_GRAPHED = object()
 
 
-class _UnitGraphModule(nn.Module):
+class _UnitGraphModule:
   """What gets captured for one unit: its forward on tensor arguments only (everything else that the
-  first eager call passed is held constant).  Being a Module, its parameters are part of the captured
-  input surface, so their storage (views into the engine's flat buffers) must not move."""
+  first eager call passed is held constant).  Deliberately a plain callable, not a Module: the unit's
+  parameters must stay out of the captured backward's list of differentiated inputs.  Their gradients are
+  written into the flat gradient buffers by the kernels themselves, and asking autograd for them would
+  make the captured backward visit gradient accumulators that the first, eager step created on another
+  stream (a dependency on uncaptured work, which ends the capture).  The parameters' storage (views
+  into the engine's flat buffers) must not move after capture."""
 
   def __init__(self, unit: Unit, args, kwargs):
-    super().__init__()
-    self.inner = unit.module
     self._fwd = unit.orig_forward
     self._args, self._kwargs = list(args), dict(kwargs)
     self._slots = [("a", i) for i, a in enumerate(args) if isinstance(a, torch.Tensor)]
@@ -929,7 +931,7 @@ class _UnitGraphModule(nn.Module):
       sig.append((tuple(a.shape), a.dtype, a.requires_grad) if isinstance(a, torch.Tensor) else a)
     return sig
 
-  def forward(self, *tensors):
+  def __call__(self, *tensors):
     args, kwargs = list(self._args), dict(self._kwargs)
     for (kind, i), t in zip(self._slots, tensors):
       if kind == "a":
