@@ -27,18 +27,27 @@ MIXTRAL = ["model=mixtral-8x7b", "model.num_hidden_layers=2", "model.hidden_size
            "model.num_local_experts=4", "model.moe_implementation=gmm", "dataset.block_size=512",
            "task.global_batch_size=2"]
 
+DEEPSEEK = ["model=deepseek-v2-lite", "model.num_hidden_layers=2", "model.hidden_size=512",
+            "model.intermediate_size=1024", "model.moe_intermediate_size=256", "model.num_attention_heads=4",
+            "model.num_key_value_heads=4", "model.n_routed_experts=8", "model.num_experts_per_tok=2",
+            "model.kv_lora_rank=128", "model.vocab_size=4096", "dataset.block_size=512", "task.global_batch_size=2"]
+
 CASES_2GPU = {
-  "fsdp2_nccl": LLAMA + ["ici_mesh.fsdp=2", "engine.fsdp_collectives=nccl"],
-  "fsdp2_peer": LLAMA + ["ici_mesh.fsdp=2", "engine.fsdp_collectives=peer"],
-  "fsdp2_peer_remat_pooled": LLAMA + ["ici_mesh.fsdp=2", "engine.fsdp_collectives=peer", "engine.remat_layers=all",
+  "llama_fsdp2_nccl": LLAMA + ["ici_mesh.fsdp=2", "engine.fsdp_collectives=nccl"],
+  "llama_fsdp2_peer": LLAMA + ["ici_mesh.fsdp=2", "engine.fsdp_collectives=peer"],
+  "llama_fsdp2_peer_remat_pooled": LLAMA + ["ici_mesh.fsdp=2", "engine.fsdp_collectives=peer", "engine.remat_layers=all",
                                       "engine.keep_gathered=false"],
-  "tensor2_fused": LLAMA + ["ici_mesh.fsdp=1", "ici_mesh.tensor=2", "model/sharding=llama-fsdp-tp"],
-  "context2_fused_zigzag": LLAMA + ["ici_mesh.fsdp=1", "ici_mesh.context=2", "+model.context=2",
+  "llama_tensor2_fused": LLAMA + ["ici_mesh.fsdp=1", "ici_mesh.tensor=2", "model/sharding=llama-fsdp-tp"],
+  "llama_context2_fused_zigzag": LLAMA + ["ici_mesh.fsdp=1", "ici_mesh.context=2", "+model.context=2",
                                     "+model.load_balance_cp=true", "model/sharding=llama-fsdp-tp-cp"],
   "mixtral_fsdp2_expert2_push": MIXTRAL + ["ici_mesh.fsdp=2", "ici_mesh.expert=2", "expert_axis_mode=folded",
                                            "model/sharding=mixtral-fsdp-ep"],
+  "mixtral_tensor2": MIXTRAL + ["ici_mesh.fsdp=1", "ici_mesh.tensor=2", "model/sharding=mixtral-fsdp-tp-ep"],
+  "deepseek_fsdp2_peer": DEEPSEEK + ["ici_mesh.fsdp=2"],
+  "deepseek_tensor2": DEEPSEEK + ["ici_mesh.fsdp=1", "ici_mesh.tensor=2"],
 }
-CASES_1GPU = {"llama_single": LLAMA + ["ici_mesh.fsdp=1"], "mixtral_single": MIXTRAL + ["ici_mesh.fsdp=1"]}
+CASES_1GPU = {"llama_single": LLAMA + ["ici_mesh.fsdp=1"], "mixtral_single": MIXTRAL + ["ici_mesh.fsdp=1"],
+              "deepseek_single": DEEPSEEK + ["ici_mesh.fsdp=1"]}
 
 
 def _worker(rank, world, port, cases, steps, out):
@@ -106,10 +115,10 @@ def _close(a, b, what, tol_loss=0.03, tol_norm=0.08):
 def test_two_gpu_trajectories_match_single_gpu(cuda_lib):
   single = _run(1, CASES_1GPU, 29671)
   multi = _run(2, CASES_2GPU, 29672)
-  assert multi["fsdp2_peer:collectives"] == "peer" and multi["fsdp2_nccl:collectives"] == "nccl"
+  assert multi["llama_fsdp2_peer:collectives"] == "peer" and multi["llama_fsdp2_nccl:collectives"] == "nccl"
   for name in CASES_2GPU:
-    ref = single["mixtral_single" if name.startswith("mixtral") else "llama_single"]
+    ref = single[name.split("_")[0] + "_single"]
     _close(multi[name], ref, name)
   # the peer path reduces in a fixed order in fp32: it tracks NCCL closely
-  _close(multi["fsdp2_peer"], multi["fsdp2_nccl"], "peer vs nccl", tol_loss=0.01, tol_norm=0.02)
+  _close(multi["llama_fsdp2_peer"], multi["llama_fsdp2_nccl"], "peer vs nccl", tol_loss=0.01, tol_norm=0.02)
   print({k: v for k, v in multi.items() if not k.endswith(":collectives")}, single)

@@ -149,7 +149,8 @@ def build_dispatch_plan(idx: torch.Tensor, num_experts: int, capacity: int | Non
     flat = torch.where(rank_g < capacity, flat, torch.full_like(flat, e))   # dropped pairs go to a sentinel
   order = torch.argsort(flat, stable=True)
   sorted_e = flat[order]
-  counts_all = torch.bincount(flat, minlength=e + 1)
+  # (torch.bincount reads the largest value back to the host; a scatter-add of ones does not)
+  counts_all = torch.zeros(e + 1, dtype=torch.long, device=dev).scatter_add_(0, flat, torch.ones_like(flat))
   counts = counts_all[:e]
   padded = (counts + align - 1) // align * align
   ends_pad = torch.cumsum(padded, 0)
