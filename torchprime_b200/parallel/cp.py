@@ -4,7 +4,7 @@ Same flavour as the reference (K/V replicated along the sequence, Q sharded:
 configs/model/sharding/llama-fsdp-tp-cp.yaml:22-24, utils/kernel_utils.py:287-316), including
 the optional load-balanced (zig-zag) layout in which rank r owns chunks r and 2cp-1-r.  Here
 each rank gathers the other ranks' K/V over NVLink (backward: the matching reduce-scatter of
-dK/dV), restores the natural key order for the zig-zag layout and calls the attention kernel
+dK/dV; on the fused path through per-source staging slots in peer memory and a fixed-order reduction), restores the natural key order for the zig-zag layout and calls the attention kernel
 with the absolute positions of its own query rows, so the kernel's block skipping sees the
 true causal structure.  Works for forward and backward (the reference's custom wrapper is
 forward-only, kernel_utils.py:124-131).
@@ -56,6 +56,9 @@ class _FusedExchangeAttention(torch.autograd.Function):
       dv_all = reorder_sequence(dv_all, cpa.cp, seq_dim=1, to_contiguous=False)
     b, sk, hkv, d = dk_all.shape
     s_local = sk // cpa.cp
+    if cpa.peer_scatter:
+      dk, dv = cpa._peer_reduce_scatter(dk_all, dv_all)
+      return dq, dk, dv, None, None, None
 
     def scatter(g):
       parts = g.view(b, cpa.cp, s_local, hkv, d).transpose(0, 1).contiguous()   # [cp, b, s_local, ...]
@@ -81,6 +84,11 @@ class ContextParallelAttention:
     self.fused_multicast = fused_multicast    # push K/V with one multimem store for all ranks where available
     self._pos_cache = {}
     self._fused = {}
+    # backward of the fused path: dK/dV go back to their owners through per-source staging slots in peer
+    # memory (copy-engine copies, signal, fixed-order fp32 reduction) instead of an NCCL reduce-scatter
+    import os as _os
+    self.peer_scatter = fused_exchange and _os.environ.get("TPB_CP_PEER_SCATTER", "1") != "0"
+    self._scatter = {}
 
   def _fused_state(self, q, k):
     """Symmetric gathered K/V buffers and flags for this shape (allocated once, on every rank)."""
@@ -99,6 +107,51 @@ class ContextParallelAttention:
                           "flags": flags, "epoch": 0}
       flags.barrier()
     return self._fused[key]
+
+  def _peer_reduce_scatter(self, dk_all, dv_all):
+    """dK/dV of all keys ([b, cp * s_local, hkv, d], this rank's contribution, rank-major row order) ->
+    the sum over ranks of the rows this rank owns.  Every rank copies the rows of owner p into its own
+    slot of p's staging buffer (copy engines over NVLink; the own rows by a local copy), signals, and the
+    owner adds the cp slots in rank order in fp32: deterministic, and no SM moves gradient bytes."""
+    from ..dist.symm import SymmetricBuffer
+    from ..ops._lib import check, lib, stream_ptr
+    from . import fsdp_comm  # noqa: F401  (registers the C signatures)
+    dk_all, dv_all = dk_all.contiguous(), dv_all.contiguous()
+    b, sk, hkv, d = dk_all.shape
+    s_local = sk // self.cp
+    n = b * s_local * hkv * d                       # elements of one owner's dK (or dV)
+    key = (b, s_local, hkv, d)
+    st = self._scatter.get(key)
+    dev = dk_all.device
+    if st is None:
+      st = {"stage": SymmetricBuffer(self.cp * 2 * n, dk_all.dtype, dev, group=self.group),
+            "flags": SymmetricBuffer(2 * self.cp, torch.int32, dev, group=self.group), "use": 0}
+      st["flags"].local.zero_()
+      st["table"] = st["flags"].ptr_table()
+      st["flags"].barrier()
+      self._scatter[key] = st
+    L, s = lib(), stream_ptr()
+    st["use"] += 1
+    use = st["use"]
+    flags = st["flags"].local.data_ptr()
+    if use > 1:      # every owner has reduced the previous contents of its staging buffer
+      check(L.tpb_flag_wait(flags + 4 * self.cp, self.cp, 1, use - 1, 93, s), "cp scatter slot wait")
+    row = hkv * d
+    for j in range(self.cp):
+      p = (self.rank + j) % self.cp
+      base = st["stage"].ptrs[p] + 2 * (self.rank * 2 * n)
+      for which, g in enumerate((dk_all, dv_all)):
+        for bi in range(b):
+          src = g.data_ptr() + 2 * ((bi * sk + p * s_local) * row)
+          dst = base + 2 * (which * n + bi * s_local * row)
+          check(L.tpb_symm_copy(dst, src, 2 * s_local * row, s), "cp scatter copy")
+    check(L.tpb_peer_signal(st["table"], self.cp, self.rank, use, s), "cp scatter done signal")
+    check(L.tpb_flag_wait(flags, self.cp, 1, use, 94, s), "cp scatter done wait")
+    out = torch.empty(2, b, s_local, hkv, d, dtype=dk_all.dtype, device=dev)
+    check(L.tpb_rs_reduce_bf16(st["stage"].local.data_ptr(), self.cp, 2 * n, 2 * n, out.data_ptr(), 0, 0, 1.0, s),
+          "cp scatter reduce")
+    check(L.tpb_peer_signal(st["table"], self.cp, self.cp + self.rank, use, s), "cp scatter free signal")
+    return out[0], out[1]
 
   def _can_fuse(self, q, k, v, segment_ids) -> bool:
     if not (self.fused_exchange and q.is_cuda and segment_ids is None and ops.use_kernels(q, k, v)):
