@@ -102,6 +102,33 @@ rs_reduce_kernel(const __nv_bfloat16* __restrict__ stage, int world, long long s
   }
 }
 
+struct PeerShards {
+  const uint4* shard[kMaxPeers];
+};
+
+// out[t, :] = row ids[t] of a [vocab, dim] table that lives, flattened, `base_vec` 16-byte vectors into
+// a buffer sharded `shard_vec` vectors per rank: every vector is loaded from the shard of the rank
+// that owns it (plain peer loads over NVLink; a row may straddle two owners).  Only the rows that are
+// looked up cross the link, instead of the whole table.
+__global__ void embedding_fwd_peer_kernel(PeerShards ps, const long long* __restrict__ ids, uint4* __restrict__ out,
+                                          long long tokens, int nvec, long long vocab, long long shard_vec,
+                                          long long base_vec) {
+  const long long total = tokens * nvec;
+  for (long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long t = idx / nvec;
+    const int c = (int)(idx % nvec);
+    const long long id = ids[t];
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (id >= 0 && id < vocab) {
+      const long long flat = base_vec + id * nvec + c;
+      const long long owner = flat / shard_vec;
+      v = ps.shard[owner][flat - owner * shard_vec];
+    }
+    out[idx] = v;
+  }
+}
+
 int sm_count();  // runtime.cu
 
 }  // namespace tpb
@@ -156,5 +183,24 @@ extern "C" int tpb_rs_reduce_bf16(const void* stage, int world, long long stride
   else
     rs_reduce_kernel<false><<<(int)blocks, 256, 0, s>>>(reinterpret_cast<const __nv_bfloat16*>(stage), world, stride, n,
                                                          out, accumulate, scale);
+  return launch_rc();
+}
+
+// Embedding lookup straight out of the owners' parameter shards (see embedding_fwd_peer_kernel).
+// shards[r]: rank r's shard of the flat buffer that holds the table (peer-mapped), `shard_elems`
+// elements each; the table starts `table_offset` elements into the flat buffer.
+extern "C" int tpb_embedding_fwd_peer(void* const* shards, int world, long long shard_elems, long long table_offset,
+                                      const long long* ids, void* out, int tokens, int dim, long long vocab,
+                                      void* stream) {
+  if (!shards || world < 1 || world > kMaxPeers || (dim % 8) || (shard_elems % 8) || (table_offset % 8)) return -2;
+  if (tokens <= 0) return 0;
+  PeerShards ps;
+  for (int i = 0; i < world; ++i) ps.shard[i] = reinterpret_cast<const uint4*>(shards[i]);
+  const long long total = (long long)tokens * (dim / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  embedding_fwd_peer_kernel<<<(int)blocks, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ps, ids, reinterpret_cast<uint4*>(out), tokens, dim / 8, vocab, shard_elems / 8, table_offset / 8);
   return launch_rc();
 }

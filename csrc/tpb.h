@@ -126,6 +126,10 @@ int tpb_flag_wait(const unsigned* flags, int n, long long stride, unsigned value
 int tpb_rs_reduce_bf16(const void* stage, int world, long long stride, long long n, void* out, int out_is_f32,
                        int accumulate, float scale, void* stream);
 
+// Embedding rows read straight from the owners' (peer-mapped) shards of the flat buffer that holds the table.
+int tpb_embedding_fwd_peer(void* const* shards, int world, long long shard_elems, long long table_offset,
+                           const long long* ids, void* out, int tokens, int dim, long long vocab, void* stream);
+
 // Router: one warp per token.  mode 0 softmax-top-k(-renormalise); mode 1 sigmoid + bias with
 // group-limited selection.  w_out [T,K] fp32, idx_out [T,K] int32, scores_out [T,E] fp32 (optional).
 int tpb_router_topk(const void* logits, int logits_is_bf16, const float* bias, float* w_out, int* idx_out,

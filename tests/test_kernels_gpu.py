@@ -263,3 +263,28 @@ def test_symmetric_runtime_single_rank(cuda_lib):
   assert L.tpb_symm_release(payload) == 0 and L.tpb_symm_live_segments() == before
   assert L.tpb_symm_release(payload) == -2                 # unknown segment
   assert L.tpb_symm_barrier(table, 1, 1, 1, _lib.stream_ptr()) == -2
+
+
+def test_embedding_lookup_from_sharded_table(cuda_lib):
+  """Rows read vector by vector from the shard that owns them (here three shards on one GPU; in training
+  the shards are the fsdp ranks' peer-mapped parameter buffers).  Shard boundaries cut rows."""
+  import ctypes
+  from torchprime_b200.ops._lib import check, lib, ptr, stream_ptr
+  from torchprime_b200.parallel import fsdp_comm  # noqa: F401  (registers the C signature)
+  torch.manual_seed(3)
+  vocab, dim, offset, world = 1000, 136, 48, 3
+  table = torch.randn(vocab, dim, device="cuda", dtype=torch.bfloat16)
+  total = offset + vocab * dim + 40
+  shard = (total + world * 8 - 1) // (world * 8) * 8
+  flat = torch.zeros(shard * world, device="cuda", dtype=torch.bfloat16)
+  flat[offset:offset + vocab * dim] = table.reshape(-1)
+  shards = [flat[r * shard:(r + 1) * shard].clone() for r in range(world)]
+  assert (shard % dim) != 0                                  # rows straddle owners
+  ids = torch.randint(0, vocab, (4, 77), device="cuda")
+  ids[0, 0], ids[0, 1] = 0, vocab - 1
+  out = torch.empty(ids.numel(), dim, device="cuda", dtype=torch.bfloat16)
+  arr = (ctypes.c_void_p * world)(*[s.data_ptr() for s in shards])
+  check(lib().tpb_embedding_fwd_peer(arr, world, shard, offset, ptr(ids.reshape(-1).contiguous()), ptr(out),
+                                     ids.numel(), dim, vocab, stream_ptr()), "embedding_fwd_peer")
+  torch.cuda.synchronize()
+  assert torch.equal(out.view(4, 77, dim), table[ids])

@@ -172,7 +172,14 @@ class LlamaDecoderLayer(nn.Module):
 
 
 class LlamaEmbedding(nn.Embedding):
+  """``peer_lookup``: set by the FSDP engine while the table stays sharded over the fsdp ranks; rows
+  are then read from the owners' shards instead of from a gathered copy of the whole table."""
+  supports_peer_lookup = True
+  peer_lookup = None
+
   def forward(self, ids):
+    if self.peer_lookup is not None:
+      return ops.embedding_peer(ids, self.weight, self.peer_lookup)
     return ops.embedding(ids, self.weight)
 
 

@@ -530,6 +530,37 @@ class _EmbeddingFn(torch.autograd.Function):
     return None, g.to(table.dtype)
 
 
+class _EmbeddingPeerFn(torch.autograd.Function):
+  """Lookup in a table that stays sharded: rows are read straight from the owners' parameter shards
+  over NVLink (``peer``: see parallel/fsdp_comm.PeerLookup).  ``table`` is the parameter, whose storage is
+  empty on this path; it is an input only so that the backward runs and finds ``table.main_grad``."""
+
+  @staticmethod
+  def forward(ctx, ids, table, peer):
+    flat = ids.reshape(-1).contiguous()
+    out = torch.empty(flat.numel(), peer.dim, dtype=torch.bfloat16, device=ids.device)
+    peer.lookup(flat, out)
+    ctx.save_for_backward(ids)
+    ctx.table = table
+    return out.view(*ids.shape, peer.dim)
+
+  @staticmethod
+  def backward(ctx, dout):
+    from . import kernels as k
+    (ids,) = ctx.saved_tensors
+    table = ctx.table
+    mg = table.main_grad
+    if overwrites_grad(table):
+      mg.zero_()
+      table.grad_overwrite = False
+    k.embedding_bwd_(dout.contiguous(), ids.contiguous(), mg)
+    return None, None, None
+
+
+def embedding_peer(ids, table, peer):
+  return _EmbeddingPeerFn.apply(ids, table, peer)
+
+
 def embedding(ids, table):
   if use_kernels(table) and table.shape[1] % 8 == 0:
     return _EmbeddingFn.apply(ids, table)

@@ -502,7 +502,7 @@ class FSDPEngine:
     return u.gathered is not None and getattr(u, "_gathered_version", -1) == self._param_version
 
   def _issue_gather(self, u: Unit):
-    if self.fsdp == 1 or u.gather_work is not None or u.shard_size == 0:
+    if self.fsdp == 1 or u.gather_work is not None or u.shard_size == 0 or getattr(u, "peer_lookup", None) is not None:
       return
     if u.gathered is not None:
       if self._fresh(u):
@@ -530,6 +530,19 @@ class FSDPEngine:
 
   def _ensure_gathered(self, u: Unit, with_grads: bool, in_kernel_wait: bool = False):
     if self.fsdp == 1:
+      return
+    if getattr(u, "peer_lookup", None) is not None:
+      # an embedding table that is read row by row out of the owners' shards: nothing to gather; the
+      # parameter keeps an empty storage and only receives its gradient view
+      u.module.peer_lookup = u.peer_lookup
+      if with_grads:
+        grads = self._grad_buffer(u)
+        ev = self._grad_slot_events.get(self._buf_key(u))
+        if ev is not None:
+          torch.cuda.current_stream().wait_event(ev)
+        u.grad_full = grads
+        for s in u.slots:
+          s.param.main_grad = grads[s.offset:s.offset + s.numel].view(s.shape)
       return
     if not self._fresh(u):
       self._issue_gather(u)

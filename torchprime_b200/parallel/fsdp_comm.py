@@ -51,6 +51,7 @@ _lib.register_signature("tpb_rs_reduce_bf16", [P, I, LL, LL, P, I, I, FL, P])
 _lib.register_signature("tpb_gemm_rs_store_bf16", [P, P, I, I, I, LL, LL, LL, I, I, FL, P, I, LL, LL, I, P])
 _lib.register_signature("tpb_gemm_ag_wait_bf16", [P, P, I, I, I, LL, LL, I, P, LL, P, LL, P, LL, I, LL, LL, P, U, P])
 _lib.register_signature("tpb_symm_copy", [P, P, LL, P])
+_lib.register_signature("tpb_embedding_fwd_peer", [P, I, LL, LL, P, P, I, I, LL, P])
 
 _SITE_DONE, _SITE_FREE = 91, 92
 
@@ -80,6 +81,20 @@ class GatherContext:
   def wait_all(self):
     """Order the current stream after the whole gather (for readers that cannot wait in-kernel)."""
     self.comm.wait_gather(self.unit)
+
+
+class PeerLookup:
+  """Where an embedding table lives while it stays sharded: every rank's shard of its unit's flat buffer
+  (peer-mapped) and the table's offset in that buffer."""
+
+  def __init__(self, comm, unit, slot):
+    self.table = comm.param_sb.ptr_table(unit.shard_offset)
+    self.world, self.shard_elems, self.offset = comm.world, unit.shard_size, slot.offset
+    self.vocab, self.dim = int(slot.shape[0]), int(slot.shape[1])
+
+  def lookup(self, flat_ids, out):
+    check(lib().tpb_embedding_fwd_peer(self.table, self.world, self.shard_elems, self.offset, ptr(flat_ids), ptr(out),
+                                       flat_ids.numel(), self.dim, self.vocab, _lib.stream_ptr()), "embedding_fwd_peer")
 
 
 class PeerFsdpComm:
@@ -113,6 +128,13 @@ class PeerFsdpComm:
     self.slot_use = [0] * self.n_slots
     self.inkernel_wait = os.environ.get("TPB_FSDP_INKERNEL_WAIT", "1") != "0"
     self.push_wgrad = os.environ.get("TPB_FSDP_PUSH_WGRAD", "1") != "0"
+    self.peer_embedding = os.environ.get("TPB_FSDP_PEER_EMBEDDING", "1") != "0"
+    for u in e.units:
+      slots = [s for s in u.slots if not s.local]
+      u.peer_lookup = None
+      if (self.peer_embedding and getattr(u.module, "supports_peer_lookup", False) and len(u.slots) == 1
+          and len(slots) == 1 and len(slots[0].shape) == 2 and slots[0].shape[1] % 8 == 0 and slots[0].tp_dim is None):
+        u.peer_lookup = PeerLookup(self, u, slots[0])     # this unit is never gathered
     for u in e.units:
       u._ag_flags = torch.zeros(self.world, dtype=torch.int32, device=dev)
       u._ag_epoch = 0
