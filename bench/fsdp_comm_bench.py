@@ -4,7 +4,8 @@
 
 Per rank count W, CUDA events on the launching stream, max over ranks, after warm-up:
 
-  gather     copy-engine all-gather of the layer's bf16 shards (own shard + W-1 peer copies, one flag each)
+  gather     copy-engine all-gather of the layer's bf16 shards (own shard + W-1 peer copies, one flag each,
+             copies alternating between two streams; `gather_one_lane_ms`: all on one stream)
   wgrad      gate|up weight-gradient GEMM (28672 x 4096 x 8192 tokens) written locally (the GEMM alone)
   wgrad+rs   the same GEMM with the epilogue that stores every tile into the owners' staging slots
   reduce     fixed-order fp32 reduction of the W staging slots into the gradient shard
@@ -64,12 +65,18 @@ def main():
   params.barrier()
   epoch = [0]
 
-  def gather():
+  lane2 = torch.cuda.Stream()
+
+  def gather(lanes=2):
     epoch[0] += 1
-    for j in range(world):
-      p = (rank + j) % world
-      check(L.tpb_symm_copy(gathered.data_ptr() + 2 * p * shard, params.ptrs[p], 2 * shard, stream_ptr()), "copy")
-      check(L.tpb_flag_set(flags.data_ptr() + 4 * p, epoch[0], stream_ptr()), "flag")
+    main = torch.cuda.current_stream()
+    streams = (main, lane2) if lanes == 2 else (main,)
+    if lanes == 2:
+      lane2.wait_stream(main)
+    fsdp_comm.gather_shards(gathered.data_ptr(), params.ptrs, 2 * shard, flags.data_ptr(), epoch[0], rank, streams)
+    if lanes == 2:
+      main.wait_stream(lane2)
+  out["gather_one_lane_ms"] = round(rt.all_reduce_max_float(timed(lambda: gather(1))) * 1e3, 3)
   t = rt.all_reduce_max_float(timed(gather))
   recv = 2 * shard * (world - 1)
   out["gather_ms"] = round(t * 1e3, 3)

@@ -83,6 +83,21 @@ class GatherContext:
     self.comm.wait_gather(self.unit)
 
 
+def gather_shards(dst_ptr: int, src_ptrs, nbytes: int, flags_ptr: int, epoch: int, rank: int, streams):
+  """Enqueue the copy-engine all-gather of one buffer: shard p (``nbytes`` bytes at ``src_ptrs[p]``, peer
+  memory) lands at ``dst_ptr + p * nbytes``, then flag p becomes ``epoch``.  Own shard first, peers in
+  rotated order (every GPU serves one reader at a time); consecutive copies alternate between the given
+  streams so that one copy engine already moves the next shard while the flag of the previous one is
+  being published.  The caller orders the streams before and joins them after."""
+  L = lib()
+  world = len(src_ptrs)
+  for j in range(world):
+    p = (rank + j) % world
+    s = streams[j % len(streams)].cuda_stream
+    check(L.tpb_symm_copy(dst_ptr + p * nbytes, src_ptrs[p], nbytes, s), "fsdp gather copy")
+    check(L.tpb_flag_set(flags_ptr + 4 * p, epoch, s), "fsdp gather flag")
+
+
 class PeerLookup:
   """Where an embedding table lives while it stays sharded: every rank's shard of its unit's flat buffer
   (peer-mapped) and the table's offset in that buffer."""
@@ -126,6 +141,7 @@ class PeerFsdpComm:
     self.flags_sb.local.zero_()
     self._flag_table = self.flags_sb.ptr_table()
     self.slot_use = [0] * self.n_slots
+    self.copy_stream = torch.cuda.Stream(device=dev)    # second lane of the gathers (see gather_shards)
     self.inkernel_wait = os.environ.get("TPB_FSDP_INKERNEL_WAIT", "1") != "0"
     self.push_wgrad = os.environ.get("TPB_FSDP_PUSH_WGRAD", "1") != "0"
     self.peer_embedding = os.environ.get("TPB_FSDP_PEER_EMBEDDING", "1") != "0"
@@ -178,11 +194,14 @@ class PeerFsdpComm:
         check(L.tpb_symm_copy(buf.data_ptr() + 2 * a, src, 2 * cnt, s), "fsdp gather copy (small)")
       u._ag_small_event = torch.cuda.Event()
       u._ag_small_event.record(e.comm_stream)
-    for j in range(self.world):
-      p = (self.rank + j) % self.world
-      src = self.param_sb.ptrs[p] + u.shard_offset * 2
-      check(L.tpb_symm_copy(buf.data_ptr() + p * nbytes, src, nbytes, s), "fsdp gather copy")
-      check(L.tpb_flag_set(u._ag_flags.data_ptr() + 4 * p, u._ag_epoch, s), "fsdp gather flag")
+    fork = torch.cuda.Event()
+    fork.record(e.comm_stream)
+    self.copy_stream.wait_event(fork)
+    gather_shards(buf.data_ptr(), [p + u.shard_offset * 2 for p in self.param_sb.ptrs], nbytes,
+                  u._ag_flags.data_ptr(), u._ag_epoch, self.rank, (e.comm_stream, self.copy_stream))
+    join = torch.cuda.Event()
+    join.record(self.copy_stream)
+    e.comm_stream.wait_event(join)
     ev = torch.cuda.Event()
     ev.record(e.comm_stream)
     u._ag_event = ev
