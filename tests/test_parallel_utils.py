@@ -243,3 +243,16 @@ def test_tp_slice_of_fused_blocks_round_trips():
   assert torch.equal(tp_unslice(parts, 2, blocks=2), w)
   plain = [tp_slice(w, 1, 3, r) for r in range(3)]
   assert plain[1].shape == (2, 1, 8) and torch.equal(tp_unslice(plain, 1), w)
+
+
+def test_leftover_ranges_of_the_peer_reduce_scatter():
+  """What the weight-gradient GEMMs did not push is copied to the owners, cut at shard boundaries."""
+  from types import SimpleNamespace
+  from torchprime_b200.parallel.fsdp_comm import PeerFsdpComm
+  u = SimpleNamespace(total=400, shard_size=100, _pushed=[(120, 80), (0, 50), (250, 100)])
+  got = PeerFsdpComm._leftover(None, u)
+  assert got == [(0, 50, 50), (1, 100, 20), (2, 200, 50), (3, 350, 50)]
+  covered = sorted([(a, a + n) for _, a, n in got] + [(a, a + n) for a, n in u._pushed])
+  assert covered[0][0] == 0 and covered[-1][1] == 400 and all(x[1] == y[0] for x, y in zip(covered, covered[1:]))
+  u2 = SimpleNamespace(total=200, shard_size=100, _pushed=[])
+  assert PeerFsdpComm._leftover(None, u2) == [(0, 0, 100), (1, 100, 100)]
