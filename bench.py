@@ -148,7 +148,7 @@ def main():
   if args.warmup < 3:
     args.warmup = 3
 
-  device = rt.init()
+  device = rt.init(timeout_s=240.0)     # a rank that died must not keep the others waiting for ten minutes
   # Mesh: all N ranks on the fsdp axis unless overrides put some on tensor / context / expert / data.
   mesh_ov = {}
   for ov in args.override:
