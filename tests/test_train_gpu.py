@@ -50,7 +50,7 @@ def test_host_offload_of_layer_inputs_is_exact(cuda_lib, tmp_path):
   torchprime/torch_xla_models/offloading.py:41-146) give the same trajectory as keeping
   them on the device; the pinned buffers are allocated once and reused every step."""
   plain, _ = _run("auto", tmp_path, extra=["engine.remat_layers=all"])
-  off, tr = _run("auto", tmp_path, extra=["model/remat=llama-scan-offload"])
+  off, tr = _run("auto", tmp_path, extra=["model/remat=llama-scan-offload", "engine.remat_layers=all"])
   for (la, ga), (lb, gb) in zip(plain, off):     # (norm-weight gradients use fp32 atomics: not bit-stable)
     assert abs(la - lb) < 2e-3 and abs(ga - gb) < 5e-3 * max(1.0, gb), (plain, off)
   assert len(tr.engine._offload_pool) == 2 and not tr.engine._offloaded

@@ -606,8 +606,6 @@ class FSDPEngine:
     """True when unit ``u`` keeps its activations for backward instead of recomputing them."""
     if not u.remat_class:
       return self.fsdp > 1          # not asked to recompute; under fsdp the saved path re-gathers
-    if u.offload:
-      return False                  # host offload keeps only the unit's input: the unit is recomputed
     pol = self.remat_policy
     if pol == "all":
       return False
