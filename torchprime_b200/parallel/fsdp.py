@@ -146,7 +146,8 @@ class FSDPEngine:
     # the activations of as many units as fit in free device memory (measured on the first step).
     self.remat_policy = remat_policy
     self._remat_budget = None        # bytes still available for saved activations ("auto", first step)
-    self._remat_unit_bytes = None    # measured activation bytes of one saved unit
+    self._remat_unit_bytes = None    # largest measured activation bytes of one saved unit
+    self._kept_bytes = 0             # measured activation bytes of all units kept so far
     self.units: list[Unit] = []
     self._dummy = None
     self.comm_stream = torch.cuda.Stream(device=self.device) if self.is_cuda else None
@@ -627,11 +628,14 @@ class FSDPEngine:
     if self._remat_unit_bytes is None:
       u.keep = self._remat_budget > (8 << 30)       # measure on the first candidate if there is room at all
       return u.keep
-    # reserve: two more units' worth of transients in backward, the head's logits chunks, fragmentation
-    reserve = int(2.5 * self._remat_unit_bytes) + (8 << 30)
-    usable = int(0.85 * (self._remat_budget - reserve))
-    kept = sum(1 for x in self.units if x.keep)
-    u.keep = (kept + 1) * self._remat_unit_bytes <= usable
+    # Every kept unit is measured on the first step; the next one is assumed to need as much as the
+    # largest so far (a dense first layer says little about the mixture-of-experts layers behind it).
+    # reserve: two more units' worth of transients in backward, the head's logits chunks, fragmentation;
+    # with expert parallelism the number of routed rows a rank receives changes from step to step
+    est = self._remat_unit_bytes
+    reserve = int(2.5 * est) + (8 << 30)
+    usable = int((0.6 if self.ep > 1 else 0.85) * (self._remat_budget - reserve))
+    u.keep = self._kept_bytes + est <= usable
     return u.keep
 
   def remat_classes_active(self) -> bool:
@@ -639,7 +643,9 @@ class FSDPEngine:
     return bool(self.remat_classes) and self.remat_policy != "none"
 
   def note_saved_unit_bytes(self, nbytes: int):
-    self._remat_unit_bytes = max(int(nbytes), 1)
+    n = max(int(nbytes), 1)
+    self._remat_unit_bytes = max(self._remat_unit_bytes or 0, n)
+    self._kept_bytes += n
 
   def remat_summary(self) -> str:
     cands = [x for x in self.units if x.remat_class]
@@ -978,7 +984,8 @@ def _run_unit_saved(engine: FSDPEngine, u: Unit, args, kwargs):
   wrapped = _PostBackwardFn.apply(engine, u, *[args[i] for i in idx])
   for i, t in zip(idx, wrapped):
     call[i] = t
-  measure = engine.is_cuda and engine.remat_policy == "auto" and engine._remat_unit_bytes is None
+  measure = engine.is_cuda and engine.remat_policy == "auto" and not getattr(u, "_measured", False)
+  u._measured = True
   before = torch.cuda.memory_allocated(engine.device) if measure else 0
   engine.pre_forward(u)
   out = u.orig_forward(*call, **kwargs)
