@@ -256,3 +256,41 @@ def test_leftover_ranges_of_the_peer_reduce_scatter():
   assert covered[0][0] == 0 and covered[-1][1] == 400 and all(x[1] == y[0] for x, y in zip(covered, covered[1:]))
   u2 = SimpleNamespace(total=200, shard_size=100, _pushed=[])
   assert PeerFsdpComm._leftover(None, u2) == [(0, 0, 100), (1, 100, 100)]
+
+
+def test_expert_exchange_plan_matches_a_plain_restatement():
+  """The vectorised plan of the expert-parallel exchange against a row-by-row restatement of its layout:
+  send side sorted by expert; receive side expert-major, every segment padded, sources in rank order."""
+  import random
+  from torchprime_b200.parallel.ep import _ExchangePlan
+  random.seed(0)
+  for ep, el, big in ((2, 2, False), (4, 3, False), (2, 4, True)):
+    E = ep * el
+    C = [[random.randint(0, 40) + (1200 if big else 0) for _ in range(E)] for _ in range(ep)]
+    C[0][1] = 0
+    for me in range(ep):
+      p = _ExchangePlan(C, me, ep, el, "cpu")
+      al = p.row_align
+      assert al == (256 if big else 128)
+      tot = [[sum(C[s][r * el + j] for s in range(ep)) for j in range(el)] for r in range(ep)]
+      pad = lambda v: (v + al - 1) // al * al
+      offpad = [[sum(pad(x) for x in tot[r][:j]) for j in range(el + 1)] for r in range(ep)]
+      d = p.dispatch.tolist()
+      start, rank, row0 = d[:E + 1], d[E + 1:2 * E + 1], d[2 * E + 1:]
+      assert start == [sum(C[me][:e]) for e in range(E + 1)] and rank == [e // el for e in range(E)]
+      assert row0 == [offpad[e // el][e % el] + sum(C[s][e] for s in range(me)) for e in range(E)]
+      r = p.ret.tolist()
+      nb = el * (ep + 1)
+      rstart, rrank, rrow0 = r[:nb + 1], r[nb + 1:2 * nb + 1], r[2 * nb + 1:]
+      want_start, want_rank, want_row0, zero = [], [], [], []
+      for j in range(el):
+        e, pos = me * el + j, offpad[me][j]
+        for s in range(ep):
+          want_start.append(pos); want_rank.append(s); want_row0.append(sum(C[s][:e])); pos += C[s][e]
+        want_start.append(pos); want_rank.append(-1); want_row0.append(0)
+        zero.extend(range(pos, offpad[me][j + 1]))
+      want_start.append(offpad[me][el])
+      assert (rstart, rrank, rrow0) == (want_start, want_rank, want_row0)
+      assert (p.zero_rows.tolist() if p.zero_rows is not None else []) == zero
+      assert p.n_pad == offpad[me][el] and p.k_offsets.tolist() == offpad[me]
+      assert p.tile_expert.tolist() == [j for j in range(el) for _ in range((offpad[me][j + 1] - offpad[me][j]) // 128)]

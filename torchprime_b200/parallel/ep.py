@@ -120,42 +120,49 @@ class _ExchangePlan:
   whatever rank they came from, and no expert ids travel."""
 
   def __init__(self, C, me: int, ep: int, el: int, device):
+    import numpy as np
     E = ep * el
-    tot = [[sum(int(C[s][r * el + j]) for s in range(ep)) for j in range(el)] for r in range(ep)]
+    C = np.asarray(C, dtype=np.int64).reshape(ep, E)
+    tot = C.sum(axis=0).reshape(ep, el)                              # rows owner r receives for its expert j
     # 256-row segments (CTA-pair GEMM tiles) when experts see about a thousand rows or more; the
     # choice is made from the whole matrix, so every rank pads every owner's layout the same way
-    total = sum(sum(row) for row in tot)
-    al = 256 if total // E >= 1024 else 128
+    al = 256 if int(tot.sum()) // E >= 1024 else 128
     self.row_align = al
-    offpad = [_prefix([(v + al - 1) // al * al for v in tot[r]]) for r in range(ep)]
-    send_off = [_prefix(C[s]) for s in range(ep)]
+    padded = (tot + al - 1) // al * al
+    offpad = np.zeros((ep, el + 1), dtype=np.int64)
+    offpad[:, 1:] = np.cumsum(padded, axis=1)
+    send_off = np.zeros((ep, E + 1), dtype=np.int64)
+    send_off[:, 1:] = np.cumsum(C, axis=1)
+    before_me = C[:me].sum(axis=0)                                   # rows of lower ranks inside each segment
     # dispatch: one block per global expert, in send order
-    start = send_off[me]
-    rank = [e // el for e in range(E)]
-    row0 = [offpad[e // el][e % el] + sum(int(C[s][e]) for s in range(me)) for e in range(E)]
-    self.dispatch = torch.tensor(start + rank + row0, dtype=torch.int64, device=device)
+    owner = np.arange(E) // el
+    row0 = offpad[owner, np.arange(E) % el] + before_me
+    dispatch = np.concatenate([send_off[me], owner, row0])
     self.dispatch_blocks = E
-    self.n_send = start[-1]
+    self.n_send = int(send_off[me, -1])
     # return: walk the receive layout; padding rows form blocks that go nowhere (rank -1)
-    start, rank, row0, zero = [], [], [], []
-    for j in range(el):
-      e = me * el + j
-      pos = offpad[me][j]
-      for s in range(ep):
-        start.append(pos); rank.append(s); row0.append(send_off[s][e])
-        pos += int(C[s][e])
-      start.append(pos); rank.append(-1); row0.append(0)
-      zero.extend(range(pos, offpad[me][j + 1]))
-    start.append(offpad[me][el])
-    self.ret = torch.tensor(start + rank + row0, dtype=torch.int64, device=device)
-    self.ret_blocks = len(rank)
-    self.n_pad = offpad[me][el]
-    self.zero_rows = torch.tensor(zero, dtype=torch.int64, device=device) if zero else None
-    tiles = []
-    for j in range(el):
-      tiles += [j] * ((offpad[me][j + 1] - offpad[me][j]) // 128)
-    self.tile_expert = torch.tensor(tiles, dtype=torch.int32, device=device)
-    self.k_offsets = torch.tensor(offpad[me], dtype=torch.int32, device=device)
+    mine = C[:, me * el:(me + 1) * el]                               # [source, local expert]
+    within = np.zeros((el, ep + 1), dtype=np.int64)
+    within[:, 1:] = np.cumsum(mine.T, axis=1)
+    start = (offpad[me, :el, None] + within).reshape(-1)             # per expert: ep source blocks + the padding block
+    rank = np.tile(np.concatenate([np.arange(ep), [-1]]), el)
+    src_row0 = np.concatenate([send_off[:, me * el:(me + 1) * el].T, np.zeros((el, 1), dtype=np.int64)], axis=1)
+    ret = np.concatenate([start, [offpad[me, el]], rank, src_row0.reshape(-1)])
+    self.ret_blocks = el * (ep + 1)
+    self.n_pad = int(offpad[me, el])
+    pad_lo, pad_hi = offpad[me, :el] + tot[me], offpad[me, 1:]
+    zero = np.concatenate([np.arange(a, b) for a, b in zip(pad_lo, pad_hi)]) if self.n_pad else np.zeros(0, np.int64)
+    tiles = np.repeat(np.arange(el), (padded[me] // 128))
+    # one host-to-device copy for everything
+    packed = torch.from_numpy(np.concatenate([dispatch, ret, zero, tiles, offpad[me]]).astype(np.int64))
+    if torch.device(device).type == "cuda":
+      packed = packed.pin_memory().to(device, non_blocking=True)
+    n_d, n_r, n_z, n_t = dispatch.size, ret.size, zero.size, tiles.size
+    self.dispatch = packed[:n_d]
+    self.ret = packed[n_d:n_d + n_r]
+    self.zero_rows = packed[n_d + n_r:n_d + n_r + n_z] if n_z else None
+    self.tile_expert = packed[n_d + n_r + n_z:n_d + n_r + n_z + n_t].to(torch.int32)
+    self.k_offsets = packed[n_d + n_r + n_z + n_t:].to(torch.int32)
     self.num_rows = self.n_pad
 
 
