@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from . import _lib
+from . import _debug, _lib
 from ._lib import (EPI_BF16, EPI_BF16_ACC, EPI_BF16_RES, EPI_F32, EPI_F32_ACC, EPI_SWIGLU, check, lib, ptr,
                    stream_ptr)
 
@@ -103,6 +103,7 @@ def rope_(x2d, col0, heads, dim, cos, sin, seq_len, pos=None, inverse=False, int
   assert cos.dtype == torch.float32 and cos.is_contiguous() and cos.shape[-1] == dim // 2
   if pos is not None:
     assert pos.dtype == torch.int32 and pos.numel() == x2d.shape[0]
+    _debug.check_index("rope", "pos", pos, 0, cos.shape[0])
   check(lib().tpb_rope_strided(ptr(x2d), x2d.stride(0), col0, heads, dim, head_stride or dim, ptr(cos), ptr(sin),
                                ptr(pos), x2d.shape[0], seq_len, int(inverse), int(interleaved), stream_ptr()), "rope")
   return x2d
@@ -130,6 +131,7 @@ def ce_fwd_bwd_(logits2d, targets, loss_sum, grad_scale=None):
   """loss_sum += sum of row losses; logits2d becomes d(loss)/d(logits) * grad_scale."""
   assert logits2d.dim() == 2 and logits2d.stride(1) == 1 and logits2d.dtype == torch.bfloat16
   assert targets.dtype == torch.int64 and targets.is_contiguous() and targets.numel() == logits2d.shape[0]
+  _debug.check_index("ce_fwd_bwd", "targets", targets, 0, logits2d.shape[1], also_allowed=-100)
   check(lib().tpb_ce_fwd_bwd(ptr(logits2d), logits2d.stride(0), ptr(targets), ptr(loss_sum), ptr(grad_scale),
                              logits2d.shape[0], logits2d.shape[1], stream_ptr()), "ce_fwd_bwd")
   return logits2d

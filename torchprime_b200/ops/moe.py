@@ -21,7 +21,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
-from . import _lib, reference as ref
+from . import _debug, _lib, reference as ref
 from ._lib import check, lib, ptr, stream_ptr
 
 P, I, LL, FL = c_void_p, c_int, c_longlong, c_float
@@ -197,6 +197,7 @@ def _build_dispatch_plan_kernel(idx: torch.Tensor, e: int, align: int = ROW_ALIG
 def gather_rows(x, src_row, row_scale=None):
   m, d = src_row.numel(), x.shape[-1]
   out = torch.empty(m, d, dtype=x.dtype, device=x.device)
+  _debug.check_index("moe_gather", "src_row", src_row, 0, x.reshape(-1, d).shape[0], also_allowed=-1)
   check(lib().tpb_moe_gather(ptr(x), ptr(src_row), ptr(row_scale), ptr(out), m, d, stream_ptr()), "moe_gather")
   return out
 
@@ -204,6 +205,7 @@ def gather_rows(x, src_row, row_scale=None):
 def combine_rows(rows, dest, w=None):
   t, k = dest.shape
   out = torch.empty(t, rows.shape[-1], dtype=rows.dtype, device=rows.device)
+  _debug.check_index("moe_combine", "dest", dest, 0, rows.shape[0], also_allowed=-1)
   check(lib().tpb_moe_combine(ptr(rows), ptr(dest), ptr(w), ptr(out), t, k, rows.shape[-1], stream_ptr()),
         "moe_combine")
   return out
@@ -212,6 +214,7 @@ def combine_rows(rows, dest, w=None):
 def combine_dw(rows, dest, dout):
   t, k = dest.shape
   dw = torch.empty(t, k, dtype=torch.float32, device=rows.device)
+  _debug.check_index("moe_combine_dw", "dest", dest, 0, rows.shape[0], also_allowed=-1)
   check(lib().tpb_moe_combine_dw(ptr(rows), ptr(dest), ptr(dout), ptr(dw), t, k, rows.shape[-1], stream_ptr()),
         "moe_combine_dw")
   return dw

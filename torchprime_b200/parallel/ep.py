@@ -44,13 +44,21 @@ class PushAllToAll:
     copy of the first ``n_out`` rows of this rank's receive buffer with ``zero_rows`` cleared."""
     import ctypes
 
-    from ..ops import _lib
+    from ..ops import _debug, _lib
     from ..ops._lib import check, lib, ptr, stream_ptr
     assert n_out <= self.max_rows, f"receive buffer holds {self.max_rows} rows, {n_out} needed"
     assert x.shape[1] == self.dim and x.is_contiguous() and desc.numel() == 3 * n_blocks + 1
     P, I, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint
     _lib.register_signature("tpb_a2a_push_blocks", [P, I, I, I, I, I, P, P, P, U, P, P])
     _lib.register_signature("tpb_a2a_wait", [P, I, U, P])
+    if _debug.bounds_enabled():
+      start, dst_rank, dst_row0 = desc[: n_blocks + 1], desc[n_blocks + 1: 2 * n_blocks + 1], desc[2 * n_blocks + 1:]
+      _debug.check_monotone("a2a_push_blocks", "start", start, 0, x.shape[0])
+      _debug.check_index("a2a_push_blocks", "dst_rank", dst_rank, 0, self.world, also_allowed=-1)
+      live = dst_rank >= 0
+      _debug.check_index("a2a_push_blocks", "dst_row0 + block rows", ((dst_row0 + (start[1:] - start[:-1])))[live], 0,
+                         self.max_rows + 1)
+      _debug.check_index("a2a_push_blocks", "dst_row0", dst_row0[live], 0, self.max_rows + 1)
     self.epoch += 1
     self.recv.barrier()            # nobody is still reading its receive buffer from the previous exchange
     check(lib().tpb_a2a_push_blocks(ptr(x), x.shape[0], self.dim, n_blocks, self.world, self.rank, ptr(desc),
