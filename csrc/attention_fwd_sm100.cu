@@ -69,6 +69,62 @@ struct AttnFwdParams {
 
 constexpr int CP_CHUNK = 128;          // keys per flag
 
+// Build with -DTPB_ATTN_PROF to accumulate per-phase cycle counts of one softmax thread and of the
+// MMA thread of every CTA (read back with tpb_attn_fwd_prof_read).  Not part of normal builds.
+#ifdef TPB_ATTN_PROF
+__device__ unsigned long long g_fwd_prof[16];
+#define PROF_DECL_(n) unsigned prof_acc[n] = {}; unsigned prof_t = (unsigned)clock();
+#define PROF_MARK_(i) { const unsigned now_ = (unsigned)clock(); prof_acc[i] += now_ - prof_t; prof_t = now_; }
+#define PROF_FLUSH_(base, n, on) if (on) { for (int i_ = 0; i_ < n; ++i_) atomicAdd(&g_fwd_prof[base + i_], (unsigned long long)prof_acc[i_]); }
+#else
+#define PROF_DECL_(n)
+#define PROF_MARK_(i)
+#define PROF_FLUSH_(base, n, on)
+#endif
+// -DTPB_ATTN_ABLATE=<bits> removes parts of the v2 softmax to see what each costs (results are wrong):
+// 1 no exponentials, 2 no row maximum / exchange barrier, 4 no score loads, 8 no P stores
+#ifndef TPB_ATTN_ABLATE
+#define TPB_ATTN_ABLATE 0
+#endif
+#ifdef TPB_ATTN_PROF
+#define TPB_ATTN_PROF_LEVEL TPB_ATTN_PROF
+#else
+#define TPB_ATTN_PROF_LEVEL 0
+#endif
+// counters of the MMA thread (which has registers to spare) with -DTPB_ATTN_PROF=1 or 2, those of a
+// softmax thread (they cost it registers and perturb what they measure) only with -DTPB_ATTN_PROF=2
+#define PROF_I_DECL(n) PROF_DECL_(n)
+#define PROF_I_MARK(i) PROF_MARK_(i)
+#define PROF_I_FLUSH(base, n, on) PROF_FLUSH_(base, n, on)
+#if defined(TPB_ATTN_PROF) && TPB_ATTN_PROF >= 2
+#define PROF_DECL(n) PROF_DECL_(n)
+#define PROF_MARK(i) PROF_MARK_(i)
+#define PROF_FLUSH(base, n, on) PROF_FLUSH_(base, n, on)
+#define PROF_COUNT(i) prof_acc[i] += 1;
+#else
+#define PROF_DECL(n)
+#define PROF_MARK(i)
+#define PROF_FLUSH(base, n, on)
+#define PROF_COUNT(i)
+#endif
+// -DTPB_ATTN_PROF=3: clocks per MMA issue of tile a's issuer (slots 0-7: P V k-steps, 8-15: Q K^T k-steps)
+#if defined(TPB_ATTN_PROF) && TPB_ATTN_PROF == 3
+#define PROF_K_DECL unsigned kacc[16] = {}; unsigned kt = 0;
+#define PROF_K_START kt = (unsigned)clock();
+#define PROF_K_MARK(i) { const unsigned now_ = (unsigned)clock(); kacc[i] += now_ - kt; kt = now_; }
+#define PROF_K_FLUSH(on) if (on) { for (int i_ = 0; i_ < 16; ++i_) atomicAdd(&g_fwd_prof[i_], (unsigned long long)kacc[i_]); }
+#else
+#define PROF_K_DECL
+#define PROF_K_START
+#define PROF_K_MARK(i)
+#define PROF_K_FLUSH(on)
+#endif
+#ifdef TPB_ATTN_PROF
+#define PROF_I_COUNT(i) prof_acc[i] += 1;
+#else
+#define PROF_I_COUNT(i)
+#endif
+
 // Natural position of local key row t (0 <= t < s_local) of rank r.
 __device__ __forceinline__ int cp_natural_pos(int t, int r, int world, int s_local, int zigzag) {
   if (!zigzag) return r * s_local + t;
@@ -340,8 +396,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kv0 = (blk_lo + j) * FWD_BN;
       const bool need_mask = (p.causal && kv0 + FWD_BN - 1 > qpos_min) || (kv0 + FWD_BN > p.Sk) ||
                              (p.window > 0 && qpos_max - kv0 >= p.window) || p.q_seg != nullptr;
-      float t[64];
-      float m_blk = -INFINITY;
+      // masked scores become -inf (the scale is positive, so masking and the row maximum work on
+      // the raw scores); the maximum runs as four chains of three-input max instructions
+      float m_blk;
       if (need_mask) {
         const int* ks = p.kv_seg ? p.kv_seg + (long long)b * p.Sk : nullptr;
 #pragma unroll
@@ -351,15 +408,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           if (p.causal) keep = keep && kp <= qpos;
           if (p.window > 0) keep = keep && (qpos - kp < p.window);
           if (ks) keep = keep && (kp < p.Sk) && (__ldg(ks + min(kp, p.Sk - 1)) == qseg);
-          t[c] = keep ? __uint_as_float(r[c]) * p.scale_log2 : -INFINITY;
-          m_blk = fmaxf(m_blk, t[c]);
+          r[c] = keep ? r[c] : 0xff800000u;
         }
-      } else {
+      }
+      {
+        float mx[4];
 #pragma unroll
-        for (int c = 0; c < 64; ++c) {
-          t[c] = __uint_as_float(r[c]) * p.scale_log2;
-          m_blk = fmaxf(m_blk, t[c]);
-        }
+        for (int e = 0; e < 4; ++e) mx[e] = fmaxf(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1]));
+#pragma unroll
+        for (int c = 8; c < 64; c += 8)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            mx[e] = fmax3(mx[e], __uint_as_float(r[c + 2 * e]), __uint_as_float(r[c + 2 * e + 1]));
+        m_blk = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2;
       }
       // lazy running maximum
       float alpha = 1.f;
@@ -370,14 +431,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         m_used = m_blk;
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum = 0.f;
+      // P = exp2(s * c - m): the multiply-add and the row sum on packed pairs
+      const f32x2 c2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(-m_safe, -m_safe);
+      f32x2 acc[2] = {0ull, 0ull};
       uint32_t pk[32];
 #pragma unroll
       for (int c = 0; c < 32; ++c) {
-        const float p0 = exp2f(t[2 * c] - m_safe), p1 = exp2f(t[2 * c + 1] - m_safe);
-        sum += p0 + p1;
+        float p0, p1;
+        f2_unpack(f2_fma(f2_pack_bits(r[2 * c], r[2 * c + 1]), c2, nm2), p0, p1);
+        p0 = ex2_approx(p0);
+        p1 = ex2_approx(p1);
+        acc[c & 1] = f2_add(acc[c & 1], f2_pack(p0, p1));
         pk[c] = pack_bf16(p0, p1);
       }
+      float s0, s1;
+      f2_unpack(f2_add(acc[0], acc[1]), s0, s1);
+      const float sum = s0 + s1;
       l = l * alpha + sum;
       if (j > 0) {
         if (!mbar_wait(o_done, (j - 1) & 1, p.status, kTimeoutAccFull, 18)) { ok = false; break; }
@@ -451,8 +520,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 //   warp 0      TMA producer: both Q tiles once, then 2-stage rings of 128-key K and V tiles.
 //   warp 1      MMA issuer.  Per step j and tile x: O_x += P_x(j) V_j, then S_x(j+1) = Q_x K_{j+1}^T
 //               into the columns P_x(j) has just been read from (S and P share TMEM columns).
-//   warps 4-7   softmax of tile a (thread = query row), warps 8-11 softmax of tile b (warps 2-3 idle:
-//               roles are laid out by warpgroup so that registers can move between them).
+//   warps 4-11  softmax of tile a, warps 12-19 softmax of tile b: two threads per query row (TMEM lane),
+//               one for keys [0,64) and one for keys [64,128) of the step; the two exchange their partial
+//               row maximum through shared memory.  Two warps per scheduler and tile hide each other's
+//               TMEM, MUFU and instruction-fetch latencies; every fourth pair of exponentials runs on
+//               the FMA pipe.  (Warps 2-3 idle: roles are laid out by warpgroup so that registers can
+//               move between them.)
 //   TMEM        S_a [0,128)  S_b [128,256)  O_a [256,384)  O_b [384,512)
 // ------------------------------------------------------------------------------------------
 // 2^x for x <= 0 on the FMA pipe (no MUFU): round-to-nearest split x = n + f with the 1.5 * 2^23
@@ -468,17 +541,43 @@ __device__ __forceinline__ float exp2_fma(float x) {
   return __int_as_float(__float_as_int(pl) + (__float_as_int(fl) << 23));
 }
 
+// The same for a packed pair: six packed FMA-pipe instructions, two clamps and two integer
+// multiply-adds for two results.
+__device__ __forceinline__ void exp2_fma_pair(f32x2 x, float& r0, float& r1) {
+  float x0, x1;
+  f2_unpack(x, x0, x1);
+  x = f2_pack(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const f32x2 magic = f2_pack(12582912.f, 12582912.f), neg_magic = f2_pack(-12582912.f, -12582912.f);
+  const f32x2 fl = f2_add(x, magic);
+  const f32x2 f = f2_sub(x, f2_add(fl, neg_magic));
+  f32x2 pl = f2_fma(f2_pack(0.05508868f, 0.05508868f), f, f2_pack(0.24260405f, 0.24260405f));
+  pl = f2_fma(pl, f, f2_pack(0.69327623f, 0.69327623f));
+  pl = f2_fma(pl, f, f2_pack(0.99992895f, 0.99992895f));
+  float p0, p1, n0, n1;
+  f2_unpack(pl, p0, p1);
+  f2_unpack(fl, n0, n1);
+  r0 = __int_as_float(__float_as_int(p0) + (__float_as_int(n0) << 23));
+  r1 = __int_as_float(__float_as_int(p1) + (__float_as_int(n1) << 23));
+}
+
 constexpr int F2_T = 128;                 // tile edge: rows per query tile, keys per step
-constexpr int F2_THREADS = 384;            // warpgroup 0: TMA + MMA warps (two idle), warpgroups 1 / 2: softmax of tile a / b
-// 128 x 56 + 256 x 224 = 64512 registers: within the SM's 65536, so the `inc` below cannot block
-constexpr int F2_REGS_IO = 56, F2_REGS_SOFTMAX = 224;
+constexpr int F2_THREADS = 640;            // warpgroup 0: TMA + MMA warps (two idle), warpgroups 1-2 / 3-4: softmax of tile a / b
+// Registers move from the copy / MMA warpgroup to the softmax warpgroups, whose threads hold 64 scores
+// each (spills go through the same L1 / shared-memory port the MMAs fetch their operands from and stall
+// the whole pipeline).  setmaxnreg.inc can only take what the same CTA released with setmaxnreg.dec (the
+// pool is the CTA's allocation at launch) and blocks for ever when that is less than it asks for, so the
+// budget must balance against the count the kernel is launched with; the host checks that count.
+constexpr int F2_REGS_LAUNCH = 96, F2_REGS_IO = 56, F2_REGS_SOFTMAX = 104;
+static_assert(128 * (F2_REGS_LAUNCH - F2_REGS_IO) >= 512 * (F2_REGS_SOFTMAX - F2_REGS_LAUNCH),
+              "the softmax warpgroups would wait for registers nobody releases");
 constexpr int F2_TILE_BYTES = F2_T * 128 * 2;   // 32 KB
 namespace f2 {
 constexpr int OFF_Q = 0;                          // two tiles
 constexpr int OFF_K = 2 * F2_TILE_BYTES;          // two stages
 constexpr int OFF_V = OFF_K + 2 * F2_TILE_BYTES;
 constexpr int OFF_BAR = OFF_V + 2 * F2_TILE_BYTES;
-constexpr int TOTAL = OFF_BAR + 256 + 1024;
+constexpr int OFF_X = OFF_BAR + 256;              // float [2 tiles][2 step parities][2 halves][128 rows]
+constexpr int TOTAL = OFF_X + 2 * 2 * 2 * F2_T * 4 + 1024;
 }  // namespace f2
 
 __global__ void __launch_bounds__(F2_THREADS, 1)
@@ -494,10 +593,11 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* v_full = bars + 5;    // [2]
   uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;    // [2 tiles]
-  uint64_t* p_full = bars + 11;   // [2 tiles], count 128
+  uint64_t* p_full = bars + 11;   // [2 tiles], count 256
   uint64_t* o_done = bars + 13;   // [2 tiles]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   int* tile_minmax = reinterpret_cast<int*>(bars + 16);  // [2 tiles][2]
+  int* pair_fail = reinterpret_cast<int*>(bars + 18);    // [2 tiles][4 quarters][2 halves]: that softmax warp gave up waiting
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_ctiles = (p.Sq + 2 * F2_T - 1) / (2 * F2_T);
@@ -512,7 +612,8 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
       mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 128); mbar_init(&o_done[i], 1);
+      mbar_init(&s_full[i], 1); mbar_init(&p_full[i], 256); mbar_init(&o_done[i], 1);
+      for (int w = 0; w < 8; ++w) pair_fail[8 * i + w] = 0;
       tile_minmax[2 * i] = 0x7fffffff;
       tile_minmax[2 * i + 1] = -0x7fffffff;
     }
@@ -586,6 +687,10 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
+    // One thread issues for both tiles, alternating.  (One thread per tile was tried: left to
+    // themselves the two fall into step, both tiles in their softmax at the same time; made to take
+    // turns through a pair of mbarriers they were slower than this single thread, 0.655 against
+    // 0.594 ms at S = 8192.)
     if (lane == 0 && nblk > 0) {
       constexpr uint32_t id_qk = make_idesc_bf16(F2_T, F2_T, false, false);
       constexpr uint32_t id_pv = make_idesc_bf16(F2_T, FWD_DV, false, true);
@@ -596,21 +701,27 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       bool ok = mbar_wait(q_full, 0, p.status, kTimeoutTmaFull, 43);
       tc_fence_after();
       int steps[2] = {0, 0};   // steps issued per tile (barrier phases)
+      PROF_K_DECL
       auto issue_s = [&](int x, int j) {   // S_x = Q_x K_j^T
+        PROF_K_START
         const uint32_t klo = smem_desc_lo(k0 + (j & 1) * F2_TILE_BYTES, 16);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t kk = (uint32_t)(((k >> 2) * (F2_T * 128) + (k & 3) * 32) >> 4);
           mma_ss_w(tmem_base + x * F2_T, qlo[x] + kk, hi_w, klo + kk, hi_w, id_qk, k != 0);
+          PROF_K_MARK(8 + k)
         }
         tc_commit(&s_full[x]);
       };
       auto issue_pv = [&](int x, int j, bool first) {   // O_x += P_x V_j
+        PROF_K_START
         const uint32_t vlo = smem_desc_lo(v0 + (j & 1) * F2_TILE_BYTES, F2_T * 128);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
+        for (int k = 0; k < 8; ++k) {
           mma_ts_w(tmem_base + 256 + x * F2_T, tmem_base + x * F2_T + k * 8, vlo + (uint32_t)((k * 2048) >> 4), hi_w,
                    id_pv, (!first) | (k != 0));
+          PROF_K_MARK(k)
+        }
         tc_commit(&o_done[x]);
       };
       if (ok) ok = mbar_wait(&k_full[0], 0, p.status, kTimeoutTmaFull, 44);
@@ -620,41 +731,43 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (active(1, 0)) issue_s(1, 0);
         tc_commit(&k_empty[0]);
       }
+      PROF_I_DECL(7)
       for (int j = 0; j < nblk && ok; ++j) {
         const int jn = j + 1;
-        bool v_ready = false, k_ready = false;
+        // the tiles this step needs were requested a step ago: these waits are off the softmax handshake
+        if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, p.status, kTimeoutTmaFull, 46)) { ok = false; break; }
+        if (jn < nblk && !mbar_wait(&k_full[jn & 1], (jn >> 1) & 1, p.status, kTimeoutTmaFull, 47)) { ok = false; break; }
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (active(x, j)) {
+            PROF_I_MARK(0)
             if (!mbar_wait(&p_full[x], steps[x] & 1, p.status, kTimeoutSoftmax, 45)) { ok = false; break; }
-            if (!v_ready) {
-              if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, p.status, kTimeoutTmaFull, 46)) { ok = false; break; }
-              v_ready = true;
-            }
+            PROF_I_MARK(1)
+            PROF_I_COUNT(2)
             tc_fence_after();
             issue_pv(x, j, steps[x] == 0);
             ++steps[x];
+            PROF_I_MARK(4)
           }
           if (jn < nblk && active(x, jn)) {
-            if (!k_ready) {
-              if (!mbar_wait(&k_full[jn & 1], (jn >> 1) & 1, p.status, kTimeoutTmaFull, 47)) { ok = false; break; }
-              k_ready = true;
-              tc_fence_after();
-            }
             issue_s(x, jn);
+            PROF_I_MARK(6)
           }
         }
         if (!ok) break;
         tc_commit(&v_empty[j & 1]);
         if (jn < nblk) tc_commit(&k_empty[jn & 1]);
       }
+      PROF_I_FLUSH(8, 7, TPB_ATTN_PROF_LEVEL != 3)
+      PROF_K_FLUSH(true)
     }
   }
   } else {
     setmaxnreg_inc<F2_REGS_SOFTMAX>();
     // ------------------------------------------------------------------ softmax + epilogue
-    const int x = (warp - 4) >> 2;                // query tile of this warp
-    const int q = warp & 3;                       // TMEM lane quarter
+    const int x = (warp - 4) >> 3;                // query tile of this warp
+    const int h = ((warp - 4) >> 2) & 1;          // key half of the step / column half of O
+    const int q = warp & 3;                       // TMEM lane quarter (four consecutive warps cover all four)
     const int r_local = q * 32 + lane;
     const int row = q0 + x * F2_T + r_local;
     const bool row_ok = row < p.Sq;
@@ -667,48 +780,73 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int* ks = p.kv_seg ? p.kv_seg + (long long)b * p.Sk : nullptr;
     const int win = p.window > 0 ? p.window : 0x7fffffff;
     const int kmax = p.causal ? min(qpos, p.Sk - 1) : p.Sk - 1;   // keep needs kp <= kmax
+    float* xch = reinterpret_cast<float*>(smem + OFF_X) + x * (4 * F2_T);   // [parity][half][row]
+    // The two warps that share the rows of a TMEM lane quarter (one per key half) synchronise on a named
+    // barrier of their own: 64 threads, so no warp waits for the slowest of the tile's eight.
+    const int pair_bar = 1 + 4 * x + q;
+    int* my_fail = pair_fail + 8 * x + 2 * q;     // [2 halves] of this pair
 
     float m_used = -INFINITY;   // maximum the exponentials are currently taken against (log2 units)
-    float l = 0.f;
+    float l = 0.f;              // sum over this thread's keys
     bool ok = true;
     int step = 0;
+    PROF_DECL(6)
     for (int j = 0; j < nblk && ok; ++j) {
       if (!active(x, j)) continue;
-      if (!mbar_wait(&s_full[x], step & 1, p.status, kTimeoutAccFull, 48)) { ok = false; break; }
+      const bool waited = mbar_wait(&s_full[x], step & 1, p.status, kTimeoutAccFull, 48);
+      if (__any_sync(0xffffffffu, !waited) && lane == 0) my_fail[h] = 1;
       tc_fence_after();
-      const int kv0 = (blk_lo + j) * F2_T;
-      const bool need_mask = (p.causal && kv0 + F2_T - 1 > qpos_min) || (kv0 + F2_T > p.Sk) ||
+      PROF_MARK(0)
+      const int kv0 = (blk_lo + j) * F2_T + 64 * h;
+      const bool need_mask = (p.causal && kv0 + 63 > qpos_min) || (kv0 + 64 > p.Sk) ||
                              (p.window > 0 && qpos_max - kv0 >= p.window) || p.q_seg != nullptr;
-      // all 128 scores of the row into registers with one wait
-      uint32_t r[128];
-      tmem_ld32(tS, r);
-      tmem_ld32(tS + 32, r + 32);
-      tmem_ld32(tS + 64, r + 64);
-      tmem_ld32(tS + 96, r + 96);
-      tmem_wait_ld();
-      float m_blk = -INFINITY;
-      if (need_mask) {
-#pragma unroll
-        for (int c = 0; c < 128; ++c) {
-          const int kp = kv0 + c;
-          bool keep = (kp <= kmax) & (qpos - kp < win) & row_ok;
-          if (ks) keep = keep & (__ldg(ks + min(kp, p.Sk - 1)) == qseg);
-          r[c] = keep ? r[c] : 0xff800000u;   // -inf
-          m_blk = fmaxf(m_blk, __uint_as_float(r[c]));
-        }
+      uint32_t r[64];
+      if (!(TPB_ATTN_ABLATE & 4)) {
+        tmem_ld32(tS + 64 * h, r);
+        tmem_ld32(tS + 64 * h + 32, r + 32);
+        tmem_wait_ld();
       } else {
-        // eight independent chains instead of one 128-long dependent one
-        float mx[8];
 #pragma unroll
-        for (int e = 0; e < 8; ++e) mx[e] = __uint_as_float(r[e]);
-#pragma unroll
-        for (int c = 8; c < 128; c += 8)
-#pragma unroll
-          for (int e = 0; e < 8; ++e) mx[e] = fmaxf(mx[e], __uint_as_float(r[c + e]));
-        m_blk = fmaxf(fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])), fmaxf(fmaxf(mx[4], mx[5]), fmaxf(mx[6], mx[7])));
+        for (int c = 0; c < 64; ++c) r[c] = __float_as_uint(-1.f - c - lane);
       }
-      m_blk *= p.scale_log2;     // scale > 0: max(s) * c == max(s * c)
-      // lazy running maximum
+      PROF_MARK(1)
+      if (need_mask) {
+        // key c of this half is kept iff lo_c < c <= hi_c (causal / window / sequence end / row padding)
+        const int hi_c = row_ok ? kmax - kv0 : -1;
+        const int lo_c = qpos - win - kv0;
+#pragma unroll
+        for (int c = 0; c < 64; ++c) r[c] = (c <= hi_c && c > lo_c) ? r[c] : 0xff800000u;   // -inf
+        if (ks) {
+          const int* kseg = ks + kv0;
+          const int last = p.Sk - 1 - kv0;
+#pragma unroll
+          for (int c = 0; c < 64; ++c) r[c] = (__ldg(kseg + min(c, last)) == qseg) ? r[c] : 0xff800000u;
+        }
+      }
+      float mx[8];   // eight independent chains of three-input max instructions
+#pragma unroll
+      for (int c = 0; c < 64; c += 16)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          const float a0 = __uint_as_float(r[c + 2 * e]), a1 = __uint_as_float(r[c + 2 * e + 1]);
+          mx[e] = (c == 0) ? fmaxf(a0, a1) : fmax3(mx[e], a0, a1);
+        }
+      float m_blk = fmax3(fmax3(mx[0], mx[1], mx[2]), fmax3(mx[3], mx[4], mx[5]), fmaxf(mx[6], mx[7]));
+      // the other half's maximum.  Both warps of a pair reach the barrier in every step they enter and
+      // leave the loop together: a warp whose wait ran out raises its flag before the barrier, and both
+      // read both flags after it.
+      float* slot = xch + (step & 1) * (2 * F2_T);
+      if (!(TPB_ATTN_ABLATE & 2)) {
+        slot[h * F2_T + r_local] = m_blk;
+        PROF_MARK(2)
+        named_bar_sync(pair_bar, 64);
+        if (*reinterpret_cast<volatile int*>(&my_fail[0]) | *reinterpret_cast<volatile int*>(&my_fail[1])) { ok = false; break; }
+        m_blk = fmaxf(m_blk, slot[(h ^ 1) * F2_T + r_local]) * p.scale_log2;   // scale > 0: max(s) * c == max(s * c)
+      } else {
+        m_blk = 0.f;
+      }
+      PROF_MARK(3)
+      // lazy running maximum (both threads of the row take the same decision)
       float alpha = 1.f;
       bool rescale = false;
       if (m_blk > m_used + kRescaleThreshold || (m_used == -INFINITY && m_blk > -INFINITY)) {
@@ -717,65 +855,78 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         m_used = m_blk;
       }
       const float m_safe = (m_used == -INFINITY) ? 0.f : m_used;
-      // the previous P V of this tile must be complete before O is rescaled; the score columns are
-      // free anyway (this S was computed after that P V was issued)
-      if (step > 0) {
-        if (!mbar_wait(&o_done[x], (step - 1) & 1, p.status, kTimeoutAccFull, 49)) { ok = false; break; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, rescale)) {
+      // The previous P V of this tile is complete: its commit precedes the one of this S.  Each thread
+      // rescales its half of the O columns.
+      if (step > 0 && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-          for (int c = 0; c < FWD_DV / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(tO + c * 32, o);
-            tmem_wait_ld();
+        for (int c = 0; c < 2; ++c) {
+          uint32_t o[32];
+          tmem_ld32(tO + 64 * h + c * 32, o);
+          tmem_wait_ld();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-            tmem_st32(tO + c * 32, o);
-          }
+          for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+          tmem_st32(tO + 64 * h + c * 32, o);
         }
       }
-      // P = exp2(s * c - m), packed bf16 over the first 64 of the 128 score columns (masked scores
-      // are -inf and give exactly 0)
-      // The exponentials of one step cost 2048 MUFU cycles per scheduler for the two tiles, as much
-      // as the step's MMAs; every second one is evaluated on the FMA pipe instead (exp2_fma).
-      float sums[4] = {0.f, 0.f, 0.f, 0.f};
+      // P = exp2(s * c - m) as packed bf16 over score columns [32 h, 32 h + 32) (the other thread has
+      // read its scores before the barrier above; masked scores are -inf and give exactly 0).  The
+      // exponentials of a step cost as many MUFU cycles as its MMAs cost tensor cycles, so every
+      // fourth pair is evaluated on the FMA pipe (exp2_fma_pair).
+      const f32x2 c2 = f2_pack(p.scale_log2, p.scale_log2), nm2 = f2_pack(-m_safe, -m_safe);
+      f32x2 acc[2] = {0ull, 0ull};
 #pragma unroll
-      for (int ch = 0; ch < 4; ++ch) {
+      for (int ch = 0; ch < 2; ++ch) {
         uint32_t pk[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 4) {
-          const float p0 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c]), p.scale_log2, -m_safe));
-          const float p1 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 1]), p.scale_log2, -m_safe));
-          const float p2 = exp2f(fmaf(__uint_as_float(r[ch * 32 + c + 2]), p.scale_log2, -m_safe));
-          const float p3 = exp2_fma(fmaf(__uint_as_float(r[ch * 32 + c + 3]), p.scale_log2, -m_safe));
-          sums[0] += p0; sums[1] += p1; sums[2] += p2; sums[3] += p3;
-          pk[c / 2] = pack_bf16(p0, p1);
-          pk[c / 2 + 1] = pack_bf16(p2, p3);
+        for (int c = 0; c < 16; ++c) {
+          const f32x2 t = f2_fma(f2_pack_bits(r[32 * ch + 2 * c], r[32 * ch + 2 * c + 1]), c2, nm2);
+          float p0, p1;
+          if (TPB_ATTN_ABLATE & 1) {
+            f2_unpack(t, p0, p1);
+          } else if ((c & 3) == 3) {
+            exp2_fma_pair(t, p0, p1);
+          } else {
+            f2_unpack(t, p0, p1);
+            p0 = ex2_approx(p0);
+            p1 = ex2_approx(p1);
+          }
+          acc[c & 1] = f2_add(acc[c & 1], f2_pack(p0, p1));
+          pk[c] = pack_bf16(p0, p1);
         }
-        tmem_st16(tS + ch * 16, pk);
+        if (!(TPB_ATTN_ABLATE & 8)) tmem_st16(tS + 32 * h + 16 * ch, pk);
+        else if (pk[3] == 0x12345678u) l += 1.f;
       }
-      const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
-      l = l * alpha + sum;
+      float s0, s1;
+      f2_unpack(f2_add(acc[0], acc[1]), s0, s1);
+      l = l * alpha + (s0 + s1);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[x]);
       ++step;
+      PROF_MARK(4)
+      PROF_COUNT(5)
     }
+    PROF_FLUSH(0, 6, warp == 4 && lane == 0)
 
     // ---- epilogue: O / l, log-sum-exp
     if (ok && step > 0) ok = mbar_wait(&o_done[x], (step - 1) & 1, p.status, kTimeoutAccFull, 50);
     tc_fence_after();
+    // row sum = sum of the two halves (the exchange slots of parity `step` were last read two steps ago)
+    float* slot = xch + (step & 1) * (2 * F2_T);
+    slot[h * F2_T + r_local] = l;
+    named_bar_sync(pair_bar, 64);
+    l += slot[(h ^ 1) * F2_T + r_local];
     const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-    if (row_ok && p.lse) {
+    if (row_ok && p.lse && h == 0) {
       const float lse = (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : INFINITY;
       p.lse[((long long)b * p.Hq + hq) * p.Sq + row] = lse;
     }
-    __nv_bfloat16* orow = p.O + grow * p.ldo + (long long)hq * FWD_DV;
+    __nv_bfloat16* orow = p.O + grow * p.ldo + (long long)hq * FWD_DV + 64 * h;
 #pragma unroll 1
-    for (int c = 0; c < FWD_DV / 32; ++c) {
+    for (int c = 0; c < 2; ++c) {
       uint32_t o[32];
       if (step > 0 && ok) {
-        tmem_ld32(tO + c * 32, o);
+        tmem_ld32(tO + 64 * h + c * 32, o);
         tmem_wait_ld();
       } else {
 #pragma unroll
@@ -830,12 +981,13 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
   if (dv != 128 || (dqk != 128 && dqk != 192) || Hq % Hkv) return -2;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -2;
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
-  // TPB_ATTN_FWD_V2=1 selects the two-tile, 128-key-step kernel.  It is correct but not yet faster
-  // than the 64-key kernel (0.63 ms against 0.59 ms at B=1, S=8192, 32/8 heads): with ten warps per
-  // CTA a thread gets 168 registers, the 128 scores of a row spill, and the softmax of one step
-  // takes about 2500 clocks against 1024 clocks of MMAs per tile.  One softmax warpgroup serving
-  // both tiles (six warps, 210 registers, no spills) was slower still (1.04 ms): a single warp per
-  // scheduler cannot hide the TMEM and MUFU latencies.
+  // TPB_ATTN_FWD_V2=1 selects the two-tile, 128-key-step kernel.  It is correct and level with the
+  // 64-key kernel (0.576 ms against 0.581-0.591 ms at B=1, S=8192, 32/8 heads), not ahead of it: with
+  // its softmax threads doing nothing it still takes 0.513 ms, the time of its MMA stream and of the
+  // handshakes of the single issuing thread.  Earlier forms: one thread per row with 168 registers
+  // spilled the 128 scores (0.66 ms); one softmax warpgroup serving both tiles (six warps, 210
+  // registers) was slower still (1.04 ms), a single warp per scheduler cannot hide the TMEM and
+  // MUFU latencies.
   static const bool use_v2 = []() { const char* v = getenv("TPB_ATTN_FWD_V2"); return v && v[0] == '1'; }();
   if (dqk == 128 && use_v2) {
     // two query tiles per CTA, 128-key steps
@@ -854,6 +1006,11 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
     if (!configured) {
       cudaError_t e = cudaFuncSetAttribute(attn_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, f2::TOTAL);
       if (e != cudaSuccess) return 1000 + (int)e;
+      // the register hand-over inside the kernel is balanced for exactly this launch allocation
+      cudaFuncAttributes fa;
+      e = cudaFuncGetAttributes(&fa, attn_fwd2_kernel);
+      if (e != cudaSuccess) return 1000 + (int)e;
+      if (fa.numRegs != F2_REGS_LAUNCH) return -9;
       configured = true;
     }
     const int n_ctiles = (Sq + 2 * F2_T - 1) / (2 * F2_T);
@@ -937,3 +1094,12 @@ extern "C" int tpb_attn_fwd_cp(const void* q, const void* k_local, const void* v
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
 }
+
+#ifdef TPB_ATTN_PROF
+// Copies the 16 profiling counters to `host16` and clears them.
+extern "C" int tpb_attn_fwd_prof_read(unsigned long long* host16) {
+  unsigned long long zero[16] = {};
+  if (cudaMemcpyFromSymbol(host16, tpb::g_fwd_prof, sizeof(zero)) != cudaSuccess) return 1;
+  return cudaMemcpyToSymbol(tpb::g_fwd_prof, zero, sizeof(zero)) == cudaSuccess ? 0 : 1;
+}
+#endif

@@ -46,7 +46,8 @@ def _compile(src: str, verbose: bool) -> str:
   stamp = max(os.path.getmtime(src), _newest_header())
   if os.path.exists(obj) and os.path.getmtime(obj) >= stamp:
     return obj
-  cmd = [_nvcc(), *NVCC_FLAGS, "-I", CSRC, "-c", src, "-o", obj]
+  # TPB_NVCC_EXTRA: extra compiler flags for instrumented developer builds (e.g. -DTPB_ATTN_PROF)
+  cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("TPB_NVCC_EXTRA", "").split(), "-I", CSRC, "-c", src, "-o", obj]
   if verbose:
     cmd[1:1] = ["-Xptxas", "-v"]
   res = subprocess.run(cmd, capture_output=True, text=True)
