@@ -64,6 +64,7 @@ def main():
   _, rstd, _ = k.rmsnorm_fwd(x, w, 1e-5)
   dwf = torch.zeros(D, device=dev, dtype=torch.float32)
   add("rmsnorm_bwd", lambda: k.rmsnorm_bwd(res, x, w, rstd, dw_f32=dwf), 3 * T * D * 2)
+  add("rmsnorm_bwd + residual grad", lambda: k.rmsnorm_bwd(res, x, w, rstd, dres=res, dw_f32=dwf), 4 * T * D * 2)
 
   qkv = torch.randn(T, HQKV, device=dev, dtype=bf)
   inv = 1.0 / (500000.0 ** (torch.arange(0, 128, 2, device=dev, dtype=torch.float32) / 128))

@@ -174,6 +174,143 @@ rmsnorm_bwd_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, co
   }
 }
 
+// The same backward with its inputs streamed through shared memory by bulk copies.
+//
+// The kernel above is bound by latency, not by bandwidth: a CTA loads a row, reduces across the
+// block, loads the residual gradient, stores, and only then asks for the next row, so an SM has a
+// row or two in flight where HBM needs some 50 KB per SM to stay busy.  Here one thread issues
+// `cp.async.bulk` copies of the rows `stages - 1` iterations ahead into a ring of shared-memory
+// stages (dy | x | dres of one row each, completion counted on an mbarrier per stage); the 256
+// threads read the rows from shared memory.  A stage is handed back by the block-wide barrier that
+// opens every iteration, which also carries the give-up decision of a wait that ran out, so all
+// threads leave the loop together.
+constexpr int NB_MAX_STAGES = 4;
+__device__ __forceinline__ void bulk_row_load(void* smem_dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+template <int VPT>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_bwd_bulk_kernel(const uint4* __restrict__ dy, const uint4* __restrict__ x, const uint4* __restrict__ w,
+                        const float* __restrict__ rstd, const uint4* __restrict__ dres, uint4* __restrict__ dx,
+                        float* __restrict__ dw, int rows, int nvec, int stages, int* status) {
+  extern __shared__ uint8_t nb_smem_raw[];
+  uint8_t* smem = nb_smem_raw + ((128u - (smem_u32(nb_smem_raw) & 127u)) & 127u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem);   // [NB_MAX_STAGES]
+  uint8_t* ring = smem + 128;
+  __shared__ float red[32];
+  const uint32_t row_bytes = (uint32_t)nvec * 16u;
+  const uint32_t stage_bytes = 3u * row_bytes;
+  const int ntens = dres ? 3 : 2;
+  const int my_rows = (rows - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // grid <= rows
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NB_MAX_STAGES; ++s) mbar_init(&full[s], 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  auto issue = [&](int k) {   // thread 0: request row k of this CTA
+    const int s = k % stages;
+    const size_t off = ((size_t)blockIdx.x + (size_t)k * gridDim.x) * nvec;
+    uint8_t* dst = ring + (size_t)s * stage_bytes;
+    mbar_expect_tx(&full[s], (uint32_t)ntens * row_bytes);
+    bulk_row_load(dst, dy + off, row_bytes, &full[s]);
+    bulk_row_load(dst + row_bytes, x + off, row_bytes, &full[s]);
+    if (dres) bulk_row_load(dst + 2 * row_bytes, dres + off, row_bytes, &full[s]);
+  };
+  int issued = 0;
+  if (threadIdx.x == 0)
+    for (; issued < stages - 1 && issued < my_rows; ++issued) issue(issued);
+
+  float dw_acc[VPT][8];
+  float wv[VPT][8];
+#pragma unroll
+  for (int j = 0; j < VPT; ++j) {
+    int i = threadIdx.x + j * NORM_THREADS;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dw_acc[j][e] = 0.f;
+    if (i < nvec) unpack8(w[i], wv[j]);
+  }
+  const float inv_d = 1.0f / (float)(nvec * 8);
+  bool ok = true;
+  int k = 0, drain_from = -1;
+  for (; k < my_rows; ++k) {
+    // every thread is done with the stage the next request goes into (it was read in iteration k - 1)
+    ok = __syncthreads_and(ok);
+    if (!ok) break;
+    if (threadIdx.x == 0 && issued < my_rows) {
+      fence_proxy_async();
+      issue(issued++);
+    }
+    const int s = k % stages;
+    ok = mbar_wait(&full[s], (uint32_t)(k / stages) & 1u, status, kTimeoutTmaFull, 71);
+    if (!ok && drain_from < 0) drain_from = k;
+    const uint4* sdy = reinterpret_cast<const uint4*>(ring + (size_t)s * stage_bytes);
+    const uint4* sx = sdy + nvec;
+    const uint4* sres = sx + nvec;
+    const size_t row = (size_t)blockIdx.x + (size_t)k * gridDim.x;
+    const float rs = rstd[row];
+    float g[VPT][8], xh[VPT][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      int i = threadIdx.x + j * NORM_THREADS;
+      if (i < nvec) {
+        float dyv[8], xv[8];
+        unpack8(sdy[i], dyv);
+        unpack8(sx[i], xv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xh[j][e] = xv[e] * rs;
+          dw_acc[j][e] += dyv[e] * xh[j][e];
+          g[j][e] = dyv[e] * wv[j][e];
+          dot += g[j][e] * xh[j][e];
+        }
+      }
+    }
+    dot = block_sum(dot, red) * inv_d;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      int i = threadIdx.x + j * NORM_THREADS;
+      if (i < nvec) {
+        float o[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] = rs * (g[j][e] - xh[j][e] * dot);
+        if (dres) {
+          float r[8];
+          unpack8(sres[i], r);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] += r[e];
+        }
+        dx[row * nvec + i] = pack8(o);
+      }
+    }
+  }
+  // a wait ran out: the copies that were requested and not consumed still land in this CTA's shared
+  // memory, so the CTA stays until they have (bounded again)
+  if (drain_from < 0 && k < my_rows) drain_from = k;
+  if (drain_from >= 0 && threadIdx.x == 0)
+    for (int kk = drain_from; kk < issued; ++kk)
+      mbar_wait(&full[kk % stages], (uint32_t)(kk / stages) & 1u, status, kTimeoutTmaFull, 72);
+  if (dw) {
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+      int i = threadIdx.x + j * NORM_THREADS;
+      if (i < nvec) {
+        float* dst = dw + i * 8;
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(dw_acc[j][0]), "f"(dw_acc[j][1]),
+                     "f"(dw_acc[j][2]), "f"(dw_acc[j][3])
+                     : "memory");
+        asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4), "f"(dw_acc[j][4]),
+                     "f"(dw_acc[j][5]), "f"(dw_acc[j][6]), "f"(dw_acc[j][7])
+                     : "memory");
+      }
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------
 // RoPE (rotate-half; optional interleaved-pair input layout), in place.
 // One thread handles 8 consecutive elements of the first half and their partners.
@@ -504,11 +641,48 @@ extern "C" int tpb_rmsnorm_fwd(const void* x, const void* res, const void* w, vo
   return rc(cudaGetLastError());
 }
 
+// Streamed form (rmsnorm_bwd_bulk_kernel) when the rows can be bulk-copied: 16-byte aligned bases (the
+// row pitch is a multiple of 16 bytes already) and enough rows to fill the ring.
+static bool launch_rmsnorm_bwd_bulk(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
+                                    void* dx, float* dw_f32, int rows, int dim, cudaStream_t stream) {
+  static const bool disabled = []() { const char* v = getenv("TPB_RMSNORM_BWD_BULK"); return v && v[0] == '0'; }();
+  if (disabled) return false;
+  auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if (!aligned(dy) || !aligned(x) || !aligned(dx) || (dres && !aligned(dres))) return false;
+  const int nvec = dim / 8;
+  const int vpt = (nvec + NORM_THREADS - 1) / NORM_THREADS;
+  const size_t stage_bytes = 3 * (size_t)nvec * 16;
+  int stages = (int)((100 * 1024) / stage_bytes);
+  if (stages > NB_MAX_STAGES) stages = NB_MAX_STAGES;
+  if (stages < 2) return false;
+  const size_t smem = 128 + 128 + stages * stage_bytes;
+  const int per_sm = (int)((220 * 1024) / (smem + 1024)) < 2 ? 1 : 2;
+  if (rows < sm_count() * per_sm * stages) return false;
+  const int grid = sm_count() * per_sm;
+  static bool configured[3] = {false, false, false};
+#define TPB_LAUNCH_NORM_BWD_BULK(V, slot)                                                                              \
+  do {                                                                                                                 \
+    if (!configured[slot]) {                                                                                           \
+      if (cudaFuncSetAttribute(rmsnorm_bwd_bulk_kernel<V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024) != \
+          cudaSuccess)                                                                                                 \
+        return false;                                                                                                  \
+      configured[slot] = true;                                                                                         \
+    }                                                                                                                  \
+    rmsnorm_bwd_bulk_kernel<V><<<grid, NORM_THREADS, smem, stream>>>((const uint4*)dy, (const uint4*)x, (const uint4*)w, \
+                                                                     rstd, (const uint4*)dres, (uint4*)dx, dw_f32,  \
+                                                                     rows, nvec, stages, status_block());              \
+  } while (0)
+  if (vpt <= 1) TPB_LAUNCH_NORM_BWD_BULK(1, 0); else if (vpt == 2) TPB_LAUNCH_NORM_BWD_BULK(2, 1); else TPB_LAUNCH_NORM_BWD_BULK(4, 2);
+#undef TPB_LAUNCH_NORM_BWD_BULK
+  return true;
+}
+
 extern "C" int tpb_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, const void* dres,
                                void* dx, float* dw_f32, int rows, int dim, void* stream) {
   if (dim % 8 || dim > 8 * NORM_THREADS * NORM_VPT) return -2;
   if (rows <= 0) return 0;
-  launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw_f32, rows, dim, STREAM(stream));
+  if (!launch_rmsnorm_bwd_bulk(dy, x, w, rstd, dres, dx, dw_f32, rows, dim, STREAM(stream)))
+    launch_rmsnorm_bwd(dy, x, w, rstd, dres, dx, dw_f32, rows, dim, STREAM(stream));
   return rc(cudaGetLastError());
 }
 

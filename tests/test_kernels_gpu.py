@@ -70,7 +70,9 @@ def test_gemm_swiglu(cuda_lib, M, F, K):
   assert _rel_err(c2, gu) < 1e-2
 
 
-@pytest.mark.parametrize("rows,dim", [(64, 512), (1000, 4096), (33, 2048), (16, 8192)])
+# the larger row counts take the backward that streams its rows through shared memory by bulk copies
+@pytest.mark.parametrize("rows,dim", [(64, 512), (1000, 4096), (33, 2048), (16, 8192), (4099, 4096), (3001, 2048),
+                                      (2500, 8192), (5003, 520)])
 def test_rmsnorm(cuda_lib, rows, dim):
   from torchprime_b200.ops import kernels as k
   torch.manual_seed(3)
@@ -93,6 +95,12 @@ def test_rmsnorm(cuda_lib, rows, dim):
   dx, dw = k.rmsnorm_bwd(dy, x, w, rstd, dres=dres)
   assert _rel_err(dx, xf.grad + dres.float()) < 1e-2
   assert _rel_err(dw, wf.grad) < 1e-2
+  dx2, dw2 = k.rmsnorm_bwd(dy, x, w, rstd)
+  assert _rel_err(dx2, xf.grad) < 1e-2
+  assert _rel_err(dw2, wf.grad) < 1e-2
+  from torchprime_b200.ops import _lib
+  torch.cuda.synchronize()
+  _lib.raise_on_device_timeout()
 
 
 @pytest.mark.parametrize("interleaved", [False, True])
