@@ -737,6 +737,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         // the tiles this step needs were requested a step ago: these waits are off the softmax handshake
         if (!mbar_wait(&v_full[j & 1], (j >> 1) & 1, p.status, kTimeoutTmaFull, 46)) { ok = false; break; }
         if (jn < nblk && !mbar_wait(&k_full[jn & 1], (jn >> 1) & 1, p.status, kTimeoutTmaFull, 47)) { ok = false; break; }
+        PROF_I_MARK(5)
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (active(x, j)) {
@@ -757,6 +758,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (!ok) break;
         tc_commit(&v_empty[j & 1]);
         if (jn < nblk) tc_commit(&k_empty[jn & 1]);
+        PROF_I_MARK(3)
       }
       PROF_I_FLUSH(8, 7, TPB_ATTN_PROF_LEVEL != 3)
       PROF_K_FLUSH(true)
