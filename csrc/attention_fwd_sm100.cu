@@ -567,7 +567,7 @@ constexpr int F2_THREADS = 640;            // warpgroup 0: TMA + MMA warps (two 
 // the whole pipeline).  setmaxnreg.inc can only take what the same CTA released with setmaxnreg.dec (the
 // pool is the CTA's allocation at launch) and blocks for ever when that is less than it asks for, so the
 // budget must balance against the count the kernel is launched with; the host checks that count.
-constexpr int F2_REGS_LAUNCH = 96, F2_REGS_IO = 56, F2_REGS_SOFTMAX = 104;
+constexpr int F2_REGS_LAUNCH = 96, F2_REGS_IO = 64, F2_REGS_SOFTMAX = 104;
 static_assert(128 * (F2_REGS_LAUNCH - F2_REGS_IO) >= 512 * (F2_REGS_SOFTMAX - F2_REGS_LAUNCH),
               "the softmax warpgroups would wait for registers nobody releases");
 constexpr int F2_TILE_BYTES = F2_T * 128 * 2;   // 32 KB
@@ -983,8 +983,8 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
   if (dv != 128 || (dqk != 128 && dqk != 192) || Hq % Hkv) return -2;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -2;
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
-  // TPB_ATTN_FWD_V2=1 selects the two-tile, 128-key-step kernel.  It is correct and level with the
-  // 64-key kernel (0.576 ms against 0.581-0.591 ms at B=1, S=8192, 32/8 heads), not ahead of it: with
+  // TPB_ATTN_FWD_V2=1 selects the two-tile, 128-key-step kernel.  It is correct and 3-4 % ahead of the
+  // 64-key kernel at B=1, S=8192, 32/8 heads (0.565-0.571 against 0.590 ms on one box), no more: with
   // its softmax threads doing nothing it still takes 0.513 ms, the time of its MMA stream and of the
   // handshakes of the single issuing thread.  Earlier forms: one thread per row with 168 registers
   // spilled the 128 scores (0.66 ms); one softmax warpgroup serving both tiles (six warps, 210
