@@ -1,6 +1,8 @@
 """Per-kernel device-time shares of one training step (torch profiler, CUDA activity).
 
   python bench/step_breakdown.py [--model llama-3-8b] [--seq-len 8192] [--top 28] [hydra-style overrides ...]
+  python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 bench/step_breakdown.py \\
+      ici_mesh.fsdp=2 task.global_batch_size=2        # rank 0's step under FSDP
 
 Runs two warm-up steps and profiles the third on one GPU.  The figures are for comparing
 kernels with one another (shares of the step); step time itself is what ``bench.py`` measures
@@ -52,9 +54,13 @@ def main():
   kernels = [(e.key, e.self_device_time_total / 1e3, e.count) for e in prof.key_averages() if e.self_device_time_total > 0]
   kernels.sort(key=lambda r: -r[1])
   total = sum(r[1] for r in kernels)
-  print(f"total device time {total:.1f} ms over {sum(r[2] for r in kernels)} launches")
-  for name, ms, count in kernels[: args.top]:
-    print(f"{ms:9.2f} ms {100 * ms / total:5.1f}%  x{count:<5d} {name[:110]}")
+  if rt.rank() == 0:     # under torchrun (add ici_mesh.fsdp=N task.global_batch_size=N) rank 0 reports its own step
+    print(f"total device time {total:.1f} ms over {sum(r[2] for r in kernels)} launches")
+    for name, ms, count in kernels[: args.top]:
+      print(f"{ms:9.2f} ms {100 * ms / total:5.1f}%  x{count:<5d} {name[:110]}")
+  rt.barrier()
+  tr.engine.close()
+  rt.shutdown()
 
 
 if __name__ == "__main__":
