@@ -49,6 +49,8 @@ constexpr float kLog2e = 1.4426950408889634f;
 struct AttnBwdParams {
   int B, Sq, Sk, Hq, Hkv;
   float scale, scale_log2;
+  float softcap_in;     // logit soft cap: scores become cap * tanh(q.k * scale / cap); this is scale / cap (0: off),
+                        // and scale_log2 is then cap * log2(e)
   int causal, window;
   const int* q_pos;
   const int* q_seg;
@@ -175,6 +177,7 @@ __device__ __forceinline__ uint32_t a_col(int k) { return (uint32_t)((k >> 2) * 
 // ------------------------------------------------------------------------------------------
 // dK / dV
 // ------------------------------------------------------------------------------------------
+template <bool SOFTCAP>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -410,6 +413,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!mbar_wait(s_full, step & 1, p.status, kTimeoutAccFull, 27)) { ok = false; break; }
         tc_fence_after();
         uint32_t pk_p[32];
+        uint32_t pk_f[SOFTCAP ? 32 : 1];   // 1 - tanh^2 of the capped scores (the derivative of the cap)
         uint32_t sreg[64];
         tmem_ld32(tS, sreg);
         tmem_ld32(tS + 32, sreg + 32);
@@ -422,10 +426,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
             for (int c4 = 0; c4 < 8; ++c4) {
               const float4 L = lse4[c4];
-              const float p0 = exp2f(fmaf(__uint_as_float(s[4 * c4]), p.scale_log2, -L.x));
-              const float p1 = exp2f(fmaf(__uint_as_float(s[4 * c4 + 1]), p.scale_log2, -L.y));
-              const float p2 = exp2f(fmaf(__uint_as_float(s[4 * c4 + 2]), p.scale_log2, -L.z));
-              const float p3 = exp2f(fmaf(__uint_as_float(s[4 * c4 + 3]), p.scale_log2, -L.w));
+              float sv[4] = {__uint_as_float(s[4 * c4]), __uint_as_float(s[4 * c4 + 1]), __uint_as_float(s[4 * c4 + 2]),
+                             __uint_as_float(s[4 * c4 + 3])};
+              if (SOFTCAP) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sv[e] = tanh_approx(sv[e] * p.softcap_in);
+                pk_f[ch * 16 + 2 * c4] = pack_bf16(1.f - sv[0] * sv[0], 1.f - sv[1] * sv[1]);
+                pk_f[ch * 16 + 2 * c4 + 1] = pack_bf16(1.f - sv[2] * sv[2], 1.f - sv[3] * sv[3]);
+              }
+              const float p0 = exp2f(fmaf(sv[0], p.scale_log2, -L.x));
+              const float p1 = exp2f(fmaf(sv[1], p.scale_log2, -L.y));
+              const float p2 = exp2f(fmaf(sv[2], p.scale_log2, -L.z));
+              const float p3 = exp2f(fmaf(sv[3], p.scale_log2, -L.w));
               pk_p[ch * 16 + 2 * c4] = pack_bf16(p0, p1);
               pk_p[ch * 16 + 2 * c4 + 1] = pack_bf16(p2, p3);
             }
@@ -440,12 +452,21 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
               const int4 QS = p.q_seg ? qs4[c4] : make_int4(0, 0, 0, 0);
               const float l[4] = {L.x, L.y, L.z, L.w};
               const int qp[4] = {QP.x, QP.y, QP.z, QP.w}, qs[4] = {QS.x, QS.y, QS.z, QS.w};
-              float pv[4];
+              float pv[4], fv[4];
 #pragma unroll
               for (int e = 0; e < 4; ++e) {
                 const bool keep = key_ok & (qp[e] >= cmax) & (qp[e] - kp < win) & (qs[e] == kseg);
-                const float pe = exp2f(fmaf(__uint_as_float(s[4 * c4 + e]), p.scale_log2, -l[e]));
+                float sv = __uint_as_float(s[4 * c4 + e]);
+                if (SOFTCAP) {
+                  sv = tanh_approx(sv * p.softcap_in);
+                  fv[e] = 1.f - sv * sv;
+                }
+                const float pe = exp2f(fmaf(sv, p.scale_log2, -l[e]));
                 pv[e] = keep ? pe : 0.f;
+              }
+              if (SOFTCAP) {
+                pk_f[ch * 16 + 2 * c4] = pack_bf16(fv[0], fv[1]);
+                pk_f[ch * 16 + 2 * c4 + 1] = pack_bf16(fv[2], fv[3]);
               }
               pk_p[ch * 16 + 2 * c4] = pack_bf16(pv[0], pv[1]);
               pk_p[ch * 16 + 2 * c4 + 1] = pack_bf16(pv[2], pv[3]);
@@ -453,6 +474,10 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           }
         }
         tmem_st32(tS, pk_p);
+        if (SOFTCAP) {   // dV takes P^T as it is; dS^T takes P^T times the derivative of the cap
+#pragma unroll
+          for (int c = 0; c < 32; ++c) pk_p[c] = mul_bf16x2(pk_p[c], pk_f[c]);
+        }
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(p_full);
@@ -503,6 +528,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // ------------------------------------------------------------------------------------------
 // dQ
 // ------------------------------------------------------------------------------------------
+template <bool SOFTCAP>
 __global__ void __launch_bounds__(BWD_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
@@ -687,9 +713,17 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const uint32_t* s = sreg + ch * 32;
         if (!need_mask) {
 #pragma unroll
-          for (int c = 0; c < 32; c += 2)
-            pk_p[ch * 16 + c / 2] = pack_bf16(exp2f(fmaf(__uint_as_float(s[c]), p.scale_log2, -lse2)),
-                                              exp2f(fmaf(__uint_as_float(s[c + 1]), p.scale_log2, -lse2)));
+          for (int c = 0; c < 32; c += 2) {
+            float s0 = __uint_as_float(s[c]), s1 = __uint_as_float(s[c + 1]), f0 = 1.f, f1 = 1.f;
+            if (SOFTCAP) {   // P only feeds dS here, so the derivative of the cap is folded into it
+              s0 = tanh_approx(s0 * p.softcap_in);
+              s1 = tanh_approx(s1 * p.softcap_in);
+              f0 = 1.f - s0 * s0;
+              f1 = 1.f - s1 * s1;
+            }
+            pk_p[ch * 16 + c / 2] = pack_bf16(f0 * exp2f(fmaf(s0, p.scale_log2, -lse2)),
+                                              f1 * exp2f(fmaf(s1, p.scale_log2, -lse2)));
+          }
         } else {
           const int kbase = kv0 + half * 64 + ch * 32;
 #pragma unroll
@@ -700,7 +734,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
               const int kp = kbase + c + e;
               bool keep = (kp <= kmax) & (qpos - kp < win);
               if (ks) keep = keep & (__ldg(ks + min(kp, p.Sk - 1)) == qseg);
-              const float pe = exp2f(fmaf(__uint_as_float(s[c + e]), p.scale_log2, -lse2));
+              float sv = __uint_as_float(s[c + e]), fv = 1.f;
+              if (SOFTCAP) {
+                sv = tanh_approx(sv * p.softcap_in);
+                fv = 1.f - sv * sv;
+              }
+              const float pe = fv * exp2f(fmaf(sv, p.scale_log2, -lse2));
               pv[e] = keep ? pe : 0.f;
             }
             pk_p[ch * 16 + c / 2] = pack_bf16(pv[0], pv[1]);
@@ -750,11 +789,13 @@ extern "C" long long tpb_attn_bwd_scratch_floats(int B, int Sq, int Hq) {
   return 2LL * B * Hq * sq_pad;
 }
 
-extern "C" int tpb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o,
-                            const float* lse, float* scratch, void* dq, void* dk, void* dv, int B, int Sq,
-                            int Sk, int Hq, int Hkv, int dqk, int dvd, long long ldq, long long ldk, long long ldv,
-                            long long lddo, long long lddq, long long lddk, long long lddv, float scale, int causal,
-                            int window, const int* q_pos, const int* q_seg, const int* kv_seg, void* stream_) {
+// `softcap` > 0: the scores were capped as softcap * tanh(q.k * scale / softcap) in the forward pass.
+extern "C" int tpb_attn_bwd_softcap(const void* dO, const void* q, const void* k, const void* v, const void* o,
+                                    const float* lse, float* scratch, void* dq, void* dk, void* dv, int B, int Sq,
+                                    int Sk, int Hq, int Hkv, int dqk, int dvd, long long ldq, long long ldk,
+                                    long long ldv, long long lddo, long long lddq, long long lddk, long long lddv,
+                                    float scale, int causal, int window, const int* q_pos, const int* q_seg,
+                                    const int* kv_seg, float softcap, void* stream_) {
   if (dqk != 128 || dvd != 128 || Hq % Hkv) return -2;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (lddo % 8) || (lddq % 8) || (lddk % 8) || (lddv % 8)) return -2;
   if (lddo != (long long)Hq * dvd) return -2;   // dO and O are contiguous [B*Sq, Hq, 128]
@@ -775,7 +816,9 @@ extern "C" int tpb_attn_bwd(const void* dO, const void* q, const void* k, const 
   }
   AttnBwdParams p;
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
-  p.scale = scale; p.scale_log2 = scale * kLog2e;
+  p.scale = scale;
+  p.softcap_in = softcap > 0.f ? scale / softcap : 0.f;
+  p.scale_log2 = (softcap > 0.f ? softcap : scale) * kLog2e;
   p.causal = causal; p.window = window;
   p.q_pos = q_pos; p.q_seg = q_seg; p.kv_seg = kv_seg;
   p.lse2 = lse2; p.delta = delta; p.Sq_pad = sq_pad;
@@ -787,9 +830,13 @@ extern "C" int tpb_attn_bwd(const void* dO, const void* q, const void* k, const 
   p.status = status_block();
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::TOTAL);
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_dkv_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::TOTAL);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(attn_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dqk::TOTAL);
+      e = cudaFuncSetAttribute(attn_bwd_dq_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, dqk::TOTAL);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_bwd_dkv_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv::TOTAL);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attn_bwd_dq_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, dqk::TOTAL);
     if (e != cudaSuccess) return 1000 + (int)e;
     configured = true;
   }
@@ -800,11 +847,22 @@ extern "C" int tpb_attn_bwd(const void* dO, const void* q, const void* k, const 
   if (make_tmap_3d(&tv, v, dvd, (uint64_t)B * Sk, Hkv, ldv, dvd, 64, BWD_T)) return -5;
   if (make_tmap_3d(&tdo, dO, dvd, (uint64_t)B * Sq, Hq, lddo, dvd, 64, BWD_T)) return -5;
   dim3 grid_kv(((Sk + BWD_T - 1) / BWD_T) * Hkv * B, 1, 1);
-  attn_bwd_dkv_kernel<<<grid_kv, BWD_THREADS, dkv::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  if (softcap > 0.f) attn_bwd_dkv_kernel<true><<<grid_kv, BWD_THREADS, dkv::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  else attn_bwd_dkv_kernel<false><<<grid_kv, BWD_THREADS, dkv::TOTAL, stream>>>(tq, tk, tv, tdo, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return 1000 + (int)e;
   dim3 grid_q(((Sq + BWD_T - 1) / BWD_T) * Hq * B, 1, 1);
-  attn_bwd_dq_kernel<<<grid_q, BWD_THREADS, dqk::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  if (softcap > 0.f) attn_bwd_dq_kernel<true><<<grid_q, BWD_THREADS, dqk::TOTAL, stream>>>(tq, tk, tv, tdo, p);
+  else attn_bwd_dq_kernel<false><<<grid_q, BWD_THREADS, dqk::TOTAL, stream>>>(tq, tk, tv, tdo, p);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+
+extern "C" int tpb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, const void* o,
+                            const float* lse, float* scratch, void* dq, void* dk, void* dv, int B, int Sq,
+                            int Sk, int Hq, int Hkv, int dqk, int dvd, long long ldq, long long ldk, long long ldv,
+                            long long lddo, long long lddq, long long lddk, long long lddv, float scale, int causal,
+                            int window, const int* q_pos, const int* q_seg, const int* kv_seg, void* stream_) {
+  return tpb_attn_bwd_softcap(dO, q, k, v, o, lse, scratch, dq, dk, dv, B, Sq, Sk, Hq, Hkv, dqk, dvd, ldq, ldk, ldv, lddo,
+                              lddq, lddk, lddv, scale, causal, window, q_pos, q_seg, kv_seg, 0.f, stream_);
 }

@@ -40,6 +40,8 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 units
 struct AttnFwdParams {
   int B, Sq, Sk, Hq, Hkv;
   float scale_log2;
+  float softcap_in;    // logit soft cap: scores become cap * tanh(q.k * scale / cap); this is scale / cap (0: off)
+                       // and scale_log2 is then cap * log2(e).  Only attn_fwd_kernel applies it.
   int causal, window;
   const int* q_pos;    // [B*Sq] or null
   const int* q_seg;    // [B*Sq] or null
@@ -396,6 +398,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kv0 = (blk_lo + j) * FWD_BN;
       const bool need_mask = (p.causal && kv0 + FWD_BN - 1 > qpos_min) || (kv0 + FWD_BN > p.Sk) ||
                              (p.window > 0 && qpos_max - kv0 >= p.window) || p.q_seg != nullptr;
+      if (p.softcap_in != 0.f) {
+#pragma unroll
+        for (int c = 0; c < 64; ++c) r[c] = __float_as_uint(tanh_approx(__uint_as_float(r[c]) * p.softcap_in));
+      }
       // masked scores become -inf (the scale is positive, so masking and the row maximum work on
       // the raw scores); the maximum runs as four chains of three-input max instructions
       float m_blk;
@@ -976,10 +982,12 @@ using namespace tpb;
 
 
 // q: [B*Sq, ...] with row pitch ldq and head h at column h*dqk; k, v likewise (v heads are 128 wide).
-extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
-                            int Hq, int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv,
-                            long long ldo, float scale, int causal, int window, const int* q_pos, const int* q_seg,
-                            const int* kv_seg, void* stream_) {
+// `softcap` > 0 caps the scores as softcap * tanh(q.k * scale / softcap) before the softmax.
+extern "C" int tpb_attn_fwd_softcap(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq,
+                                    int Sk, int Hq, int Hkv, int dqk, int dv, long long ldq, long long ldk,
+                                    long long ldv, long long ldo, float scale, int causal, int window,
+                                    const int* q_pos, const int* q_seg, const int* kv_seg, float softcap,
+                                    void* stream_) {
   if (dv != 128 || (dqk != 128 && dqk != 192) || Hq % Hkv) return -2;
   if ((ldq % 8) || (ldk % 8) || (ldv % 8) || (ldo % 8)) return -2;
   if (B <= 0 || Sq <= 0 || Sk <= 0) return 0;
@@ -991,7 +999,7 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
   // registers) was slower still (1.04 ms), a single warp per scheduler cannot hide the TMEM and
   // MUFU latencies.
   static const bool use_v2 = []() { const char* v = getenv("TPB_ATTN_FWD_V2"); return v && v[0] == '1'; }();
-  if (dqk == 128 && use_v2) {
+  if (dqk == 128 && use_v2 && !(softcap > 0.f)) {
     // two query tiles per CTA, 128-key steps
     CUtensorMap tq, tk, tv;
     if (make_tmap_3d(&tq, q, dqk, (uint64_t)B * Sq, Hq, ldq, dqk, 64, F2_T)) return -3;
@@ -1026,7 +1034,8 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
   if (make_tmap_3d(&tv, v, dv, (uint64_t)B * Sk, Hkv, ldv, dv, 64, FWD_BN)) return -5;
   AttnFwdParams p{};
   p.B = B; p.Sq = Sq; p.Sk = Sk; p.Hq = Hq; p.Hkv = Hkv;
-  p.scale_log2 = scale * 1.4426950408889634f;
+  p.softcap_in = softcap > 0.f ? scale / softcap : 0.f;
+  p.scale_log2 = (softcap > 0.f ? softcap : scale) * 1.4426950408889634f;
   p.causal = causal; p.window = window;
   p.q_pos = q_pos; p.q_seg = q_seg; p.kv_seg = kv_seg;
   p.O = reinterpret_cast<__nv_bfloat16*>(o); p.ldo = ldo; p.lse = lse;
@@ -1034,6 +1043,14 @@ extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   cudaError_t e = dqk == 128 ? launch_fwd<128>(tq, tk, tv, p, stream) : launch_fwd<192>(tq, tk, tv, p, stream);
   return e == cudaSuccess ? 0 : 1000 + (int)e;
+}
+
+extern "C" int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                            int Hq, int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv,
+                            long long ldo, float scale, int causal, int window, const int* q_pos, const int* q_seg,
+                            const int* kv_seg, void* stream_) {
+  return tpb_attn_fwd_softcap(q, k, v, o, lse, B, Sq, Sk, Hq, Hkv, dqk, dv, ldq, ldk, ldv, ldo, scale, causal, window,
+                              q_pos, q_seg, kv_seg, 0.f, stream_);
 }
 
 // Causal attention forward with the context-parallel K/V exchange fused in (head dim 128).

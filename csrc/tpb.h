@@ -161,6 +161,11 @@ int tpb_a2a_wait(const unsigned* flags, int world, unsigned epoch, void* stream)
 int tpb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk, int Hq,
                  int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv, long long ldo, float scale,
                  int causal, int window, const int* q_pos, const int* q_seg, const int* kv_seg, void* stream);
+// The same with a logit soft cap: scores become softcap * tanh(q.k * scale / softcap) (softcap <= 0: none).
+int tpb_attn_fwd_softcap(const void* q, const void* k, const void* v, void* o, float* lse, int B, int Sq, int Sk,
+                         int Hq, int Hkv, int dqk, int dv, long long ldq, long long ldk, long long ldv, long long ldo,
+                         float scale, int causal, int window, const int* q_pos, const int* q_seg, const int* kv_seg,
+                         float softcap, void* stream);
 // Causal forward with the context-parallel K/V exchange fused in (see attention_fwd_sm100.cu).
 int tpb_attn_fwd_cp(const void* q, const void* k_local, const void* v_local, void* const* k_all, void* const* v_all,
                     unsigned* const* flags, void* o, float* lse, int B, int Sq, int s_local, int Hq, int Hkv,
@@ -174,6 +179,11 @@ int tpb_attn_bwd(const void* dO, const void* q, const void* k, const void* v, co
                  int dqk, int dvd, long long ldq, long long ldk, long long ldv, long long lddo, long long lddq,
                  long long lddk, long long lddv, float scale, int causal, int window, const int* q_pos,
                  const int* q_seg, const int* kv_seg, void* stream);
+int tpb_attn_bwd_softcap(const void* dO, const void* q, const void* k, const void* v, const void* o, const float* lse,
+                 float* scratch, void* dq, void* dk, void* dv, int B, int Sq, int Sk, int Hq, int Hkv,
+                 int dqk, int dvd, long long ldq, long long ldk, long long ldv, long long lddo, long long lddq,
+                 long long lddk, long long lddv, float scale, int causal, int window, const int* q_pos,
+                 const int* q_seg, const int* kv_seg, float softcap, void* stream);
 
 // ---- symmetric-memory runtime (symm_runtime.cu): segments that every rank maps, and a bounded
 // device-side barrier on their signal pads.

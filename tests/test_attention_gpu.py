@@ -119,3 +119,32 @@ def test_attention_autograd_fused_qkv(cuda_lib):
   vf = bf[..., (hq + hkv) * d:].view(b, s, hkv, d)
   ref.attention(qf, kf, vf, causal=True).backward(do.float())
   assert _rel(buf.grad, bf.grad) < 3e-2
+
+
+@pytest.mark.parametrize("b,s,hq,hkv,causal,window,cap", [(1, 384, 4, 2, True, None, 2.0), (2, 300, 2, 1, True, 100, 5.0),
+                                                          (1, 256, 2, 2, False, None, 1.0), (1, 1024, 4, 1, True, None, 30.0)])
+def test_attention_logit_soft_cap(cuda_lib, b, s, hq, hkv, causal, window, cap):
+  """Scores capped as cap * tanh(s / cap) inside the kernels, forward and backward (the reference's
+  splash-attention option attn_logits_soft_cap, torchprime/utils/kernel_utils.py:30-37)."""
+  from torchprime_b200.ops import attention_sm100 as A
+  from torchprime_b200.ops import functional as ops
+  q, k, v = _qkv(b, s, hq, hkv, 128, fused=False, seed=11)
+  q = (q * 2).contiguous()       # scores well into the curved part of the cap
+  do = torch.randn(b, s, hq, 128, device="cuda", dtype=torch.bfloat16)
+  o, lse = A.attn_fwd(q, k, v, causal=causal, window=window, softcap=cap)
+  want, want_lse = ref.attention(q, k, v, causal=causal, window=window, softcap=cap, return_lse=True)
+  assert _rel(o, want) < 2e-2, _rel(o, want)
+  assert torch.allclose(lse, want_lse, atol=2e-2, rtol=1e-3), (lse - want_lse).abs().max()
+  dq, dk, dv = A.attn_bwd(do, q, k, v, o, lse, causal=causal, window=window, softcap=cap)
+  qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+  ref.attention(qf, kf, vf, causal=causal, window=window, softcap=cap).backward(do.float())
+  torch.cuda.synchronize()
+  assert _rel(dv, vf.grad) < 3e-2, ("dv", _rel(dv, vf.grad))
+  assert _rel(dk, kf.grad) < 3e-2, ("dk", _rel(dk, kf.grad))
+  assert _rel(dq, qf.grad) < 3e-2, ("dq", _rel(dq, qf.grad))
+  # the public op takes the kernel path too
+  qa = q.clone().requires_grad_(True)
+  oa = ops.attention(qa, k, v, causal=causal, window=window, softcap=cap)
+  assert ops.attention_impl_in_use().startswith("sm100")
+  oa.backward(do)
+  assert _rel(qa.grad, qf.grad) < 3e-2

@@ -22,6 +22,11 @@ P, I, LL, F = c_void_p, c_int, c_longlong, c_float
 _lib.register_signature("tpb_attn_fwd", [P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, F, I, I, P, P, P, P])
 _lib.register_signature("tpb_attn_bwd", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, LL,
                                          LL, LL, F, I, I, P, P, P, P])
+# the same with a logit soft cap (a float before the stream)
+_lib.register_signature("tpb_attn_fwd_softcap", [P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, F, I, I, P, P, P, F,
+                                                 P])
+_lib.register_signature("tpb_attn_bwd_softcap", [P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, LL, LL, LL, LL, LL,
+                                                 LL, LL, F, I, I, P, P, P, F, P])
 
 
 _lib.register_signature("tpb_attn_fwd_cp", [P, P, P, P, P, P, P, P, I, I, I, I, I, LL, LL, LL, LL, F, P, I, I, I, I,
@@ -62,7 +67,9 @@ def _token_major(t: torch.Tensor) -> bool:
 
 
 def supported(q, k, v, causal, window, q_segment_ids, softcap, q_positions, kv_positions) -> bool:
-  if softcap or kv_positions is not None:
+  if kv_positions is not None:
+    return False
+  if softcap and (softcap <= 0 or q.shape[-1] != 128):   # the capped backward exists for head dim 128 only
     return False
   if q.dtype != torch.bfloat16 or not (q.is_cuda and k.is_cuda and v.is_cuda):
     return False
@@ -78,22 +85,24 @@ def _i32(t):
   return None if t is None else t.reshape(-1).to(torch.int32).contiguous()
 
 
-def attn_fwd(q, k, v, causal=True, scale=None, window=None, q_pos=None, q_seg=None, kv_seg=None):
-  """Returns (o [B,Sq,Hq,128] contiguous, lse [B,Hq,Sq] fp32 in natural-log units)."""
+def attn_fwd(q, k, v, causal=True, scale=None, window=None, q_pos=None, q_seg=None, kv_seg=None, softcap=None):
+  """Returns (o [B,Sq,Hq,128] contiguous, lse [B,Hq,Sq] fp32 in natural-log units).  ``softcap``: the scores
+  become ``softcap * tanh(q.k * scale / softcap)`` before the softmax."""
   b, sq, hq, dqk = q.shape
   sk, hkv, dv = k.shape[1], k.shape[2], v.shape[-1]
   scale = scale if scale is not None else 1.0 / math.sqrt(dqk)
   o = torch.empty(b, sq, hq, dv, dtype=q.dtype, device=q.device)
   lse = torch.empty(b, hq, sq, dtype=torch.float32, device=q.device)
-  rc = lib().tpb_attn_fwd(ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), b, sq, sk, hq, hkv, dqk, dv, q.stride(1),
-                          k.stride(1), v.stride(1), hq * dv, float(scale), int(bool(causal)), int(window or 0),
-                          ptr(q_pos), ptr(q_seg), ptr(kv_seg), stream_ptr())
+  rc = lib().tpb_attn_fwd_softcap(ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), b, sq, sk, hq, hkv, dqk, dv, q.stride(1),
+                                  k.stride(1), v.stride(1), hq * dv, float(scale), int(bool(causal)),
+                                  int(window or 0), ptr(q_pos), ptr(q_seg), ptr(kv_seg), float(softcap or 0.0),
+                                  stream_ptr())
   check(rc, f"attn_fwd q{tuple(q.shape)} k{tuple(k.shape)}")
   return o, lse
 
 
 def attn_bwd(do, q, k, v, o, lse, causal=True, scale=None, window=None, q_pos=None, q_seg=None, kv_seg=None,
-             dq=None, dk=None, dv=None):
+             dq=None, dk=None, dv=None, softcap=None):
   """Gradients of :func:`attn_fwd`.  dq/dk/dv may be preallocated token-major views (for
   example slices of one fused dQKV buffer); they are fully overwritten."""
   b, sq, hq, dqk = q.shape
@@ -105,12 +114,14 @@ def attn_bwd(do, q, k, v, o, lse, causal=True, scale=None, window=None, q_pos=No
   do = do.contiguous()
   o = o.contiguous()
   if dqk != 128:
+    assert not softcap, "the capped backward exists for head dim 128 only"
     return _eager_bwd(do, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk, dv)
   scratch = torch.empty(2 * b * hq * ((sq + 127) // 128 * 128), dtype=torch.float32, device=q.device)
-  rc = lib().tpb_attn_bwd(ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(scratch), ptr(dq),
-                          ptr(dk), ptr(dv), b, sq, sk, hq, hkv, dqk, dvd, q.stride(1), k.stride(1), v.stride(1),
-                          do.stride(1), dq.stride(1), dk.stride(1), dv.stride(1), float(scale), int(bool(causal)),
-                          int(window or 0), ptr(q_pos), ptr(q_seg), ptr(kv_seg), stream_ptr())
+  rc = lib().tpb_attn_bwd_softcap(ptr(do), ptr(q), ptr(k), ptr(v), ptr(o), ptr(lse), ptr(scratch), ptr(dq),
+                                  ptr(dk), ptr(dv), b, sq, sk, hq, hkv, dqk, dvd, q.stride(1), k.stride(1),
+                                  v.stride(1), do.stride(1), dq.stride(1), dk.stride(1), dv.stride(1), float(scale),
+                                  int(bool(causal)), int(window or 0), ptr(q_pos), ptr(q_seg), ptr(kv_seg),
+                                  float(softcap or 0.0), stream_ptr())
   check(rc, f"attn_bwd q{tuple(q.shape)} k{tuple(k.shape)}")
   return dq, dk, dv
 
@@ -151,16 +162,16 @@ def _eager_bwd(do, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk,
 
 class _AttentionFn(torch.autograd.Function):
   @staticmethod
-  def forward(ctx, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg):
-    o, lse = attn_fwd(q, k, v, causal, scale, window, q_pos, q_seg, kv_seg)
+  def forward(ctx, q, k, v, causal, scale, window, q_pos, q_seg, kv_seg, softcap=None):
+    o, lse = attn_fwd(q, k, v, causal, scale, window, q_pos, q_seg, kv_seg, softcap)
     ctx.save_for_backward(q, k, v, o, lse, q_pos, q_seg, kv_seg)
-    ctx.args = (causal, scale, window)
+    ctx.args = (causal, scale, window, softcap)
     return o
 
   @staticmethod
   def backward(ctx, do):
     q, k, v, o, lse, q_pos, q_seg, kv_seg = ctx.saved_tensors
-    causal, scale, window = ctx.args
+    causal, scale, window, softcap = ctx.args
     dq = dk = dv = None
     fused = _fused_qkv_layout(q, k, v)
     if fused is not None:
@@ -173,8 +184,8 @@ class _AttentionFn(torch.autograd.Function):
       dq = buf[..., : hq * d].view(b, s, hq, d)
       dk = buf[..., hq * d: (hq + hkv) * d].view(b, s, hkv, d)
       dv = buf[..., (hq + hkv) * d:].view(b, s, hkv, d)
-    dq, dk, dv = attn_bwd(do, q, k, v, o, lse, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk, dv)
-    return dq, dk, dv, None, None, None, None, None, None
+    dq, dk, dv = attn_bwd(do, q, k, v, o, lse, causal, scale, window, q_pos, q_seg, kv_seg, dq, dk, dv, softcap)
+    return dq, dk, dv, None, None, None, None, None, None, None
 
 
 class _AttentionQKVFn(torch.autograd.Function):
@@ -236,4 +247,4 @@ def attention(q, k, v, causal=True, scale=None, window=None, q_segment_ids=None,
               q_positions=None, kv_positions=None):
   q_seg = _i32(q_segment_ids)
   kv_seg = _i32(kv_segment_ids if kv_segment_ids is not None else q_segment_ids)
-  return _AttentionFn.apply(q, k, v, causal, scale, window, _i32(q_positions), q_seg, kv_seg)
+  return _AttentionFn.apply(q, k, v, causal, scale, window, _i32(q_positions), q_seg, kv_seg, softcap)
