@@ -94,17 +94,16 @@ constexpr int T_DQ = 0, T_S = 128, T_DP = 384;
 __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ dO, const __nv_bfloat16* __restrict__ O,
                                       const float* __restrict__ lse, float* __restrict__ lse2,
                                       float* __restrict__ delta, int B, int Sq, int Sq_pad, int Hq) {
+  // Sixteen lanes per (token, head) row of 128 values: one 16-byte load of dO and of O per lane, two rows
+  // per lane in flight, four shuffle steps.  (One warp per row with 8-byte loads ran at a quarter of the
+  // copy bandwidth.)
   const long long total = (long long)B * Sq * Hq;
-  const int lane = threadIdx.x & 31;
-  for (long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5; w < total;
-       w += ((long long)gridDim.x * blockDim.x) >> 5) {
-    const uint2 a = reinterpret_cast<const uint2*>(dO + w * BWD_D)[lane];
-    const uint2 c = reinterpret_cast<const uint2*>(O + w * BWD_D)[lane];
-    float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), c0 = unpack_bf16(c.x), c1 = unpack_bf16(c.y);
-    float s = a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y;
+  const int sub = threadIdx.x & 15;
+  const long long stride = ((long long)gridDim.x * blockDim.x) >> 4;
+  auto finish = [&](long long w, float s) {
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if (lane == 0) {
+    for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (sub == 0 && w < total) {
       const long long row = w / Hq;
       const int h = (int)(w % Hq);
       const long long b = row / Sq;
@@ -112,6 +111,25 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ dO, cons
       delta[(b * Hq + h) * Sq_pad + q] = s;
       lse2[(b * Hq + h) * Sq_pad + q] = lse[(b * Hq + h) * Sq + q] * kLog2e;
     }
+  };
+  auto dot8 = [](const uint4& a, const uint4& c) {
+    const float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), a2 = unpack_bf16(a.z), a3 = unpack_bf16(a.w);
+    const float2 c0 = unpack_bf16(c.x), c1 = unpack_bf16(c.y), c2 = unpack_bf16(c.z), c3 = unpack_bf16(c.w);
+    return (a0.x * c0.x + a0.y * c0.y + a1.x * c1.x + a1.y * c1.y) +
+           (a2.x * c2.x + a2.y * c2.y + a3.x * c3.x + a3.y * c3.y);
+  };
+  // every lane of a warp runs the same number of iterations (the shuffles need the whole warp)
+  const long long w_first = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 4;
+  const long long warp_first = (blockIdx.x * (long long)blockDim.x + (threadIdx.x & ~31)) >> 4;
+  for (long long base = warp_first, w = w_first; base < total; base += 2 * stride, w += 2 * stride) {
+    const long long w2 = w + stride;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    const uint4 a = w < total ? reinterpret_cast<const uint4*>(dO + w * BWD_D)[sub] : zero;
+    const uint4 c = w < total ? reinterpret_cast<const uint4*>(O + w * BWD_D)[sub] : zero;
+    const uint4 a2 = w2 < total ? reinterpret_cast<const uint4*>(dO + w2 * BWD_D)[sub] : zero;
+    const uint4 c2 = w2 < total ? reinterpret_cast<const uint4*>(O + w2 * BWD_D)[sub] : zero;
+    finish(w, dot8(a, c));
+    finish(w2, dot8(a2, c2));
   }
   const int pad = Sq_pad - Sq;
   const long long n_pad = (long long)B * Hq * pad;
