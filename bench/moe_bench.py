@@ -29,6 +29,7 @@ CONFIGS = {
   "mixtral": dict(T=8192, D=4096, F=14336, E=8, K=2, mode="softmax"),
   "deepseek": dict(T=8192, D=2048, F=1408, E=64, K=6, mode="sigmoid"),
   "small": dict(T=2048, D=2048, F=4096, E=8, K=2, mode="softmax"),
+  "medium": dict(T=8192, D=2048, F=4096, E=8, K=2, mode="softmax"),    # Mixtral's rows per expert at a profiler-sized footprint
 }
 
 
