@@ -114,3 +114,33 @@ def test_experimental_scripts_parse_their_arguments(module, capsys):
   with pytest.raises(SystemExit) as e:
     mod.main([])                      # the required argument is missing
   assert e.value.code == 2
+
+
+def test_setup_sharding_and_mesh_names_the_batch_and_sequence_axes():
+  """Reference: model_rewriting/sharding_initialization.py:22-69 (input sharding spec and minibatch)."""
+  from torchprime_b200.dist.mesh import get_mesh
+  from torchprime_b200.models.model_utils import initialize_model_class
+  from torchprime_b200.rewriting.sharding_initialization import setup_sharding_and_mesh
+  base = ["model=llama-3-8b", "model.num_hidden_layers=1", "model.hidden_size=64", "model.intermediate_size=128",
+          "model.num_attention_heads=4", "model.num_key_value_heads=2", "model.vocab_size=128", "dataset=synthetic"]
+  cfg = compose("default", base + ["ici_mesh.fsdp=4"])
+  model = initialize_model_class(cfg.model, device="meta")
+  s = setup_sharding_and_mesh(model, cfg, mesh=get_mesh(cfg, rank=1, world_size=4))
+  assert s.batch_axes == ("data", "fsdp") and s.seq_axis is None and s.minibatch
+  assert s.input_sharding_spec == (("data", "fsdp"), None)
+  assert s.plan is not None and s.mesh.size("fsdp") == 4
+  # context parallelism names the sequence axis; two axes > 1 is no longer a 1-D sharding
+  cfg = compose("default", base + ["ici_mesh.fsdp=2", "ici_mesh.context=2", "model/sharding=llama-fsdp-tp-cp"])
+  s = setup_sharding_and_mesh(model, cfg, mesh=get_mesh(cfg, rank=0, world_size=4))
+  assert s.seq_axis == "context" and not s.minibatch
+  # an orthogonal expert axis also splits the batch; a folded one does not
+  moe = ["model=mixtral-8x7b", "model.num_hidden_layers=1", "model.hidden_size=64", "model.intermediate_size=128",
+         "model.num_attention_heads=4", "model.num_key_value_heads=2", "model.vocab_size=128", "dataset=synthetic",
+         "model.num_local_experts=4"]
+  cfg = compose("default", moe + ["ici_mesh.fsdp=2", "ici_mesh.expert=2", "expert_axis_mode=orthogonal",
+                                  "model/sharding=mixtral-fsdp-ep"])
+  mm = initialize_model_class(cfg.model, device="meta")
+  assert setup_sharding_and_mesh(mm, cfg, mesh=get_mesh(cfg, rank=0, world_size=4)).batch_axes == ("data", "fsdp", "expert")
+  cfg = compose("default", moe + ["ici_mesh.fsdp=2", "ici_mesh.expert=2", "expert_axis_mode=folded",
+                                  "model/sharding=mixtral-fsdp-ep"])
+  assert setup_sharding_and_mesh(mm, cfg, mesh=get_mesh(cfg, rank=0, world_size=2)).batch_axes == ("data", "fsdp")
