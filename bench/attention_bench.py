@@ -39,6 +39,25 @@ def timed(fn, iters, flush):
   return total / iters
 
 
+def _print_cycle_counters(launch):
+  """A library built with ``TPB_NVCC_EXTRA=-DTPB_ATTN_PROF=<1|2|3> python -m torchprime_b200.build --force``
+  exports the two-tile forward kernel's in-kernel cycle counters (``TPB_ATTN_FWD_V2=1``): print the sums of one
+  launch (slots 0-7: a softmax thread at level 2 or the P V k-steps at level 3; slots 8-15: the MMA thread)."""
+  import ctypes
+  L = _lib.lib()
+  if not hasattr(L, "tpb_attn_fwd_prof_read"):
+    return
+  host = (ctypes.c_ulonglong * 16)()
+  L.tpb_attn_fwd_prof_read.argtypes = [ctypes.c_void_p]
+  L.tpb_attn_fwd_prof_read.restype = ctypes.c_int
+  torch.cuda.synchronize()
+  L.tpb_attn_fwd_prof_read(host)      # clear what the timed launches accumulated
+  launch()
+  torch.cuda.synchronize()
+  L.tpb_attn_fwd_prof_read(host)
+  print("attn_fwd cycle counters of one launch:", list(host))
+
+
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--seq", type=int, default=8192)
@@ -61,6 +80,7 @@ def main():
   if args.only in (None, "fwd"):
     t = timed(lambda: A.attn_fwd(q, k, v, causal=True), args.iters, flush)
     print(f"attn_fwd  {t:8.3f} ms  {fwd_flops / t / 1e9:7.0f} TFLOP/s")
+    _print_cycle_counters(lambda: A.attn_fwd(q, k, v, causal=True))
   if args.only in (None, "bwd"):
     o, lse = A.attn_fwd(q, k, v, causal=True)
     do = torch.randn_like(o)
