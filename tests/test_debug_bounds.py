@@ -36,6 +36,25 @@ def test_wrappers_refuse_bad_indices_before_launch(monkeypatch):
                   pos=torch.tensor([0, 4], dtype=torch.int32))
 
 
+def test_exchange_descriptors(monkeypatch):
+  monkeypatch.setenv("TPB_DEBUG_BOUNDS", "1")
+  # three blocks of 4, 0 and 6 rows: to rank 1 at row 0, skipped, to rank 0 at row 10
+  good = torch.tensor([0, 4, 4, 10, 1, -1, 0, 0, 0, 10])
+  _debug.check_exchange_descriptors("a2a", good, 3, 10, 2, 16)
+  with pytest.raises(IndexError, match="`dst_rank`"):
+    _debug.check_exchange_descriptors("a2a", torch.tensor([0, 4, 4, 10, 2, -1, 0, 0, 0, 10]), 3, 10, 2, 16)
+  with pytest.raises(IndexError, match="block rows"):
+    _debug.check_exchange_descriptors("a2a", good, 3, 10, 2, 15)       # the last block ends at row 16
+  with pytest.raises(IndexError, match="not non-decreasing"):
+    _debug.check_exchange_descriptors("a2a", torch.tensor([0, 5, 4, 10, 1, -1, 0, 0, 0, 10]), 3, 10, 2, 16)
+  with pytest.raises(IndexError, match="`start`"):
+    _debug.check_exchange_descriptors("a2a", good, 3, 9, 2, 16)        # only nine send rows
+  with pytest.raises(IndexError, match="entries"):
+    _debug.check_exchange_descriptors("a2a", good[:-1], 3, 10, 2, 16)
+  monkeypatch.setenv("TPB_DEBUG_BOUNDS", "0")
+  _debug.check_exchange_descriptors("a2a", good[:-1], 3, 10, 2, 16)    # off: nothing is looked at
+
+
 @pytest.mark.gpu
 def test_valid_indices_pass_and_bad_ones_leave_the_context_usable(cuda_lib, monkeypatch):
   monkeypatch.setenv("TPB_DEBUG_BOUNDS", "1")

@@ -180,6 +180,17 @@ def test_expert_exchange_plan_groups_rows_by_expert_and_returns_them(scale, alig
   C[2] = [0] * E                                           # a rank that sends nothing
   plans = [_ExchangePlan(C, me, ep, el, "cpu") for me in range(ep)]
   assert all(p.row_align == align for p in plans)
+  # the range-checked debug mode accepts what the plan produces (receive buffers sized as the engine sizes them)
+  import os
+  from torchprime_b200.ops import _debug
+  pairs = max(sum(row) for row in C)
+  os.environ["TPB_DEBUG_BOUNDS"] = "1"
+  try:
+    for p in plans:
+      _debug.check_exchange_descriptors("dispatch", p.dispatch, p.dispatch_blocks, p.n_send, ep, ep * pairs + el * 256)
+      _debug.check_exchange_descriptors("return", p.ret, p.ret_blocks, p.n_pad, ep, pairs)
+  finally:
+    os.environ.pop("TPB_DEBUG_BOUNDS")
 
   def push(src_rows, desc, nb, dst):
     start, rank, row0 = desc[:nb + 1].tolist(), desc[nb + 1:2 * nb + 1].tolist(), desc[2 * nb + 1:].tolist()

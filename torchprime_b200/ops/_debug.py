@@ -50,3 +50,22 @@ def check_monotone(op: str, name: str, t, lo: int, hi: int) -> None:
   check_index(op, name, t, lo, hi + 1)
   if t.numel() > 1 and bool((t[1:] < t[:-1]).any().item()):
     raise IndexError(f"{op}: `{name}` is not non-decreasing")
+
+
+def check_exchange_descriptors(op: str, desc, n_blocks: int, n_rows: int, world: int, max_rows: int) -> None:
+  """Validate the block descriptors of the expert-exchange push kernel: ``desc`` is int64
+  ``start[n_blocks + 1] | dst_rank[n_blocks] (-1: skip) | dst_row0[n_blocks]``.  Block starts must be
+  non-decreasing inside the ``n_rows`` send rows, destination ranks inside the group, and every
+  block that is sent must fit the ``max_rows`` of the receive buffer."""
+  if not bounds_enabled():
+    return
+  if desc.is_cuda and torch.cuda.is_current_stream_capturing():
+    return
+  if desc.numel() != 3 * n_blocks + 1:
+    raise IndexError(f"{op}: descriptor tensor has {desc.numel()} entries, {3 * n_blocks + 1} expected")
+  start, dst_rank, dst_row0 = desc[: n_blocks + 1], desc[n_blocks + 1: 2 * n_blocks + 1], desc[2 * n_blocks + 1:]
+  check_monotone(op, "start", start, 0, n_rows)
+  check_index(op, "dst_rank", dst_rank, 0, world, also_allowed=-1)
+  live = (dst_rank >= 0) & (dst_rank < world)
+  check_index(op, "dst_row0", dst_row0[live], 0, max_rows + 1)
+  check_index(op, "dst_row0 + block rows", (dst_row0 + (start[1:] - start[:-1]))[live], 0, max_rows + 1)

@@ -51,14 +51,7 @@ class PushAllToAll:
     P, I, U = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint
     _lib.register_signature("tpb_a2a_push_blocks", [P, I, I, I, I, I, P, P, P, U, P, P])
     _lib.register_signature("tpb_a2a_wait", [P, I, U, P])
-    if _debug.bounds_enabled():
-      start, dst_rank, dst_row0 = desc[: n_blocks + 1], desc[n_blocks + 1: 2 * n_blocks + 1], desc[2 * n_blocks + 1:]
-      _debug.check_monotone("a2a_push_blocks", "start", start, 0, x.shape[0])
-      _debug.check_index("a2a_push_blocks", "dst_rank", dst_rank, 0, self.world, also_allowed=-1)
-      live = dst_rank >= 0
-      _debug.check_index("a2a_push_blocks", "dst_row0 + block rows", ((dst_row0 + (start[1:] - start[:-1])))[live], 0,
-                         self.max_rows + 1)
-      _debug.check_index("a2a_push_blocks", "dst_row0", dst_row0[live], 0, self.max_rows + 1)
+    _debug.check_exchange_descriptors("a2a_push_blocks", desc, n_blocks, x.shape[0], self.world, self.max_rows)
     self.epoch += 1
     self.recv.barrier()            # nobody is still reading its receive buffer from the previous exchange
     check(lib().tpb_a2a_push_blocks(ptr(x), x.shape[0], self.dim, n_blocks, self.world, self.rank, ptr(desc),
